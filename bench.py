@@ -1,0 +1,425 @@
+#!/usr/bin/env python
+"""Benchmark of the fused SDPA forward on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one pass of the hot path over one batch of the headline workload: the
+Llama-3-8B-shaped grouped-query prefill (bf16 q [4,32,4096,128], k/v [4,8,4096,128],
+causal, right padding with per-batch key lengths in [2048,4096], seed 2).  With N > 1
+(launched by torchrun, one rank per GPU) every rank owns its own batch of that shape --
+the (batch x kv head) units are independent, so there is no collective on the data
+path -- and the reported value is the sum over ranks divided by the slowest rank's time.
+
+The single JSON line carries: ``value`` (algorithmic TFLOP/s with inputs resident in
+HBM), ``roofline`` for the prefill kernel, ``e2e`` (same metric through the public op
+with pinned host buffers, copies inside the timed region), ``cpu_baseline`` (the CPU
+oracle on this box's cores over a bounded sample), ``clocks`` sampled during the timed
+region, ``gpu_launches``, and under ``extra`` the decode (HBM GB/s) and GPT-2-shaped
+prefill measurements with their own rooflines.
+
+``--impl reference`` times the CPU restatement of upstream's ``_sdpa_math`` path (the
+oracle; the upstream file itself cannot travel to the GPU box) on the host cores.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "attention TFLOP/s (prefill, aggregate over GPUs); decode HBM GB/s under extra"
+L2_BYTES = 126 * 1024 * 1024
+
+
+# ----------------------------------------------------------------------------- workloads
+
+
+def c3_inputs(seed: int, device=None, pinned=False):
+    """Llama-3-8B-shaped GQA prefill with right padding (configuration 3)."""
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(4, 32, 4096, 128, generator=g).to(torch.bfloat16)
+    k = torch.randn(4, 8, 4096, 128, generator=g).to(torch.bfloat16)
+    v = torch.randn(4, 8, 4096, 128, generator=g).to(torch.bfloat16)
+    lens = torch.randint(2048, 4097, (4,), generator=g).to(torch.int32)
+    if pinned:
+        q, k, v, lens = (t.pin_memory() for t in (q, k, v, lens))
+    if device is not None:
+        q, k, v, lens = (t.to(device) for t in (q, k, v, lens))
+    return q, k, v, lens
+
+
+def c3_flops(lens, hq=32, L=4096, e=128) -> float:
+    """4 * E * (visible (query, key) pairs): causal square clipped by the key length."""
+    pairs = 0
+    for n in lens.tolist():
+        n = min(int(n), L)
+        pairs += hq * (n * (n + 1) // 2 + (L - n) * n)
+    return 4.0 * e * pairs
+
+
+def c2_inputs(device):
+    g = torch.Generator().manual_seed(1)
+    return tuple((torch.randn(8, 12, 1024, 64, generator=g) * 0.5).to(torch.bfloat16).to(device) for _ in range(3))
+
+
+def c4_inputs(device):
+    g = torch.Generator().manual_seed(3)
+    q = torch.randn(64, 32, 1, 128, generator=g).to(torch.bfloat16).to(device)
+    # the cache itself is drawn on the device: 2 x 1 GiB of host randn would dominate start-up
+    gd = torch.Generator(device=device).manual_seed(3)
+    k = torch.randn(64, 8, 8192, 128, generator=gd, device=device, dtype=torch.bfloat16)
+    v = torch.randn(64, 8, 8192, 128, generator=gd, device=device, dtype=torch.bfloat16)
+    lens = torch.randint(512, 8193, (64,), generator=g).to(torch.int32)
+    return q, k, v, lens
+
+
+# ----------------------------------------------------------------------------- clocks
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML (read-only) while a
+    timed region runs."""
+
+    REASONS = {
+        0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
+        0x80: "hw_power_brake", 0x2: "applications_clocks_setting",
+    }
+
+    def __init__(self, device_index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            uuid = str(torch.cuda.get_device_properties(device_index).uuid)
+            try:
+                self.h = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid).encode())
+            except Exception:
+                self.h = pynvml.nvmlDeviceGetHandleByIndex(device_index)
+            self.nv = pynvml
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.02)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        s = sorted(self.samples)
+        return {"sm_mhz": (s[len(s) // 2] if s else None), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+# ----------------------------------------------------------------------------- helpers
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            d = json.load(f)
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
+    except Exception:
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def time_steps(fn, steps, stream=None):
+    """Average device time per call (ms) of ``steps`` back-to-back calls, CUDA events on
+    the launching (current) stream, synchronised on both sides."""
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / steps
+
+
+def time_steps_flushed(fn, steps, flush_buf):
+    """Per-call device time with L2 flushed (a write larger than L2) before every call."""
+    times = []
+    for _ in range(steps):
+        flush_buf.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+    times.sort()
+    return times[len(times) // 2]
+
+
+def cpu_prefill_sample(q, k, v, lens, scale, n_slices, threads):
+    """Time the CPU oracle on ``n_slices`` (batch x kv-group) slices of configuration 3,
+    driven as upstream drives its math path (GQA by repeat_interleave, padding as an
+    additive bias).  Returns (TFLOP/s, seconds, flops)."""
+    from oracle import sdpa_oracle as O
+
+    torch.set_num_threads(threads)
+    flops, t = 0.0, 0.0
+    done = 0
+    for b in range(q.shape[0]):
+        for hk in range(k.shape[1]):
+            if done >= n_slices:
+                break
+            qs = q[b : b + 1, hk * 4 : hk * 4 + 4]
+            ks, vs = k[b : b + 1, hk : hk + 1], v[b : b + 1, hk : hk + 1]
+            t0 = time.perf_counter()
+            O.sdpa_forward(qs, ks, vs, is_causal=True, scale=scale, kv_lens=lens[b : b + 1])
+            t += time.perf_counter() - t0
+            flops += c3_flops(lens[b : b + 1], hq=4)
+            done += 1
+    return flops / t / 1e12, t, flops
+
+
+# ----------------------------------------------------------------------------- reference arm
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    q, k, v, lens = c3_inputs(2)
+    scale = 1.0 / math.sqrt(128)
+    n_slices = 2
+    for _ in range(min(args.warmup, 1)):
+        cpu_prefill_sample(q, k, v, lens, scale, 1, threads)
+    t_total, f_total = 0.0, 0.0
+    for _ in range(args.steps):
+        _, t, f = cpu_prefill_sample(q, k, v, lens, scale, n_slices, threads)
+        t_total += t
+        f_total += f
+    val = f_total / t_total / 1e12
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t_total / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "llama3-8b-shaped GQA prefill bf16 q[4,32,4096,128] kv[4,8,4096,128] causal + "
+                               "right padding (configuration 3)"},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                         "sample": f"{n_slices} of 32 (batch x kv-group) slices [1,4,4096,128] per step, CPU oracle "
+                                   "(restatement of upstream _sdpa_math.compute_attention driven with "
+                                   "repeat_interleave GQA and an additive padding bias)"},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------- our arm
+
+
+def run_ours(args, rank, local_rank, world):
+    import torch_neuronx_b200 as T
+    import torch.distributed as dist
+
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    peaks = measured_peaks()
+    scale = 1.0 / math.sqrt(128)
+
+    # ---------------- headline: configuration 3, inputs resident in HBM ----------------
+    q, k, v, lens = c3_inputs(2 + 1000 * rank, device=dev)
+    flops = c3_flops(lens.cpu())
+    out = T.alloc_like_query(q, q.shape)
+    lse = torch.empty(4, 32, 4096, dtype=torch.float32, device=dev)
+
+    def step():
+        T.sdpa_forward(q, k, v, is_causal=True, scale=scale, kv_lens=lens, out=out, lse=lse)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    T.check_device_status()
+    path = T.ops.last_plan.get("path")
+    T.reset_launch_counts()
+    if world > 1:
+        dist.barrier()
+    with ClockSampler(local_rank) as clk:
+        ms = time_steps(step, args.steps)
+    launches = sum(T.launch_counts().values())
+    t_all = torch.tensor([ms], dtype=torch.float64, device=dev)
+    f_all = torch.tensor([flops], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.barrier()
+        dist.all_reduce(t_all, op=dist.ReduceOp.MAX)
+        dist.all_reduce(f_all, op=dist.ReduceOp.SUM)
+    ms_max, flops_total = t_all.item(), f_all.item()
+    value = flops_total / (ms_max * 1e-3) / 1e12
+    achieved = flops / (ms * 1e-3) / 1e12
+    timed_s = ms * args.steps * 1e-3
+    peak_kind = "bf16_tflops_sustained" if timed_s > 1.0 else "bf16_tflops"
+    roofline = {"bound": "tensor", "achieved": achieved, "peak": peaks[peak_kind], "unit": "TFLOP/s",
+                "frac": achieved / peaks[peak_kind], "traffic": None, "kernel": f"{path} (bf16, D=128)",
+                "peak_kind": f"{peak_kind} of {peaks['source']}", "flops_per_launch": flops}
+
+    # ---------------- e2e: public op, pinned host buffers, copies in the timed region ---
+    qh, kh, vh, lh = c3_inputs(2 + 1000 * rank, pinned=True)
+    oh = torch.empty(4, 32, 4096, 128, dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step():
+        qd, kd, vd, ld = (t.to(dev, non_blocking=True) for t in (qh, kh, vh, lh))
+        o = T.scaled_dot_product_attention(qd, kd, vd, is_causal=True, scale=scale, enable_gqa=True, kv_lens=ld)
+        oh.copy_(o, non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e2e_steps = max(3, min(args.steps, 10))
+    e2e_ms = time_steps(e2e_step, e2e_steps)
+    e_all = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(e_all, op=dist.ReduceOp.MAX)
+    h2d = sum(t.numel() * t.element_size() for t in (qh, kh, vh, lh))
+    d2h = oh.numel() * oh.element_size()
+    e2e = {"value": flops_total / (e_all.item() * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+           "d2h_bytes_per_step": d2h, "ms_per_step": e_all.item()}
+    del qh, kh, vh, oh
+
+    extra = {}
+    if rank == 0 and not args.no_extra:
+        flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=dev)
+        # ---------------- decode: configuration 4, HBM bound ----------------
+        dq, dk, dv, dl = c4_inputs(dev)
+        dld = dl.to(dev)
+        dout = torch.empty_like(dq)
+        dlse = torch.empty(64, 32, 1, dtype=torch.float32, device=dev)
+
+        def dstep():
+            T.sdpa_forward(dq, dk, dv, scale=scale, kv_lens=dld, out=dout, lse=dlse)
+
+        for _ in range(3):
+            dstep()
+        torch.cuda.synchronize()
+        T.check_device_status()
+        dpath = T.ops.last_plan.get("path")
+        dms = time_steps_flushed(dstep, max(5, min(args.steps, 20)), flush)
+        kv_bytes = 2 * 8 * 128 * 2 * int(dl.sum().item())          # K and V, Hkv heads, valid rows only
+        io_bytes = kv_bytes + 2 * dq.numel() * 2 + dlse.numel() * 4  # + q, out, lse
+        gbs = io_bytes / (dms * 1e-3) / 1e9
+        extra["decode"] = {
+            "workload": "llama3-8b-shaped GQA decode bf16 q[64,32,1,128] cache[64,8,L<=8192,128], L~U[512,8192] "
+                        "(configuration 4)",
+            "value": gbs, "unit": "GB/s", "ms": dms, "path": dpath, "plan": dict(T.ops.last_plan),
+            "l2": "flushed before every timed call",
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": gbs / peaks["hbm_gbs"], "traffic": None, "bytes_per_launch": io_bytes,
+                         "peak_kind": f"hbm_gbs of {peaks['source']}"},
+        }
+        del dk, dv
+        # ---------------- GPT-2-small-shaped prefill: configuration 2 ----------------
+        gq, gk, gv = c2_inputs(dev)
+        gout = torch.empty_like(gq)
+        glse = torch.empty(8, 12, 1024, dtype=torch.float32, device=dev)
+
+        def gstep():
+            T.sdpa_forward(gq, gk, gv, is_causal=True, scale=0.125, out=gout, lse=glse)
+
+        for _ in range(3):
+            gstep()
+        gms = time_steps_flushed(gstep, max(5, min(args.steps, 20)), flush)
+        gflops = 4.0 * 64 * 8 * 12 * (1024 * 1025 // 2)
+        extra["gpt2_prefill"] = {
+            "workload": "gpt2-small-shaped prefill bf16 [8,12,1024,64] causal (configuration 2)",
+            "value": gflops / (gms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms": gms, "path": T.ops.last_plan.get("path"),
+            "l2": "flushed before every timed call",
+            "roofline": {"bound": "tensor", "achieved": gflops / (gms * 1e-3) / 1e12, "peak": peaks["bf16_tflops"],
+                         "unit": "TFLOP/s", "frac": gflops / (gms * 1e-3) / 1e12 / peaks["bf16_tflops"],
+                         "traffic": None, "peak_kind": f"bf16_tflops of {peaks['source']}"},
+        }
+        # ---------------- fp32 parity configuration: latency only ----------------
+        g = torch.Generator().manual_seed(0)
+        fq, fk, fv = (torch.randn(2, 8, 512, 64, generator=g).to(dev) for _ in range(3))
+        for _ in range(3):
+            T.sdpa_forward(fq, fk, fv, is_causal=True, scale=0.125)
+        fms = time_steps_flushed(lambda: T.sdpa_forward(fq, fk, fv, is_causal=True, scale=0.125), 5, flush)
+        extra["fp32_config1"] = {"workload": "fp32 [2,8,512,64] causal (configuration 1)", "ms": fms,
+                                 "path": T.ops.last_plan.get("path")}
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        threads = os.cpu_count() or 1
+        qc, kc, vc, lc = c3_inputs(2)
+        cpu_prefill_sample(qc, kc, vc, lc, scale, 1, threads)  # warm-up
+        n_slices = 4
+        val, secs, _ = cpu_prefill_sample(qc, kc, vc, lc, scale, n_slices, threads)
+        cpu_baseline = {"value": val, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                        "sample": f"{n_slices} of 32 (batch x kv-group) slices [1,4,4096,128] of the same workload, "
+                                  f"{secs:.1f} s of CPU oracle time"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_max, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "llama3-8b-shaped GQA prefill bf16 q[4,32,4096,128] kv[4,8,4096,128] causal + "
+                                   "right padding kv_lens~U[2048,4096] per GPU (configuration 3)",
+                       "l2": "inputs (337 MB per GPU) larger than L2; no flush", "partition": "batch x kv-head, "
+                       "one batch of 4 per GPU, no collective", "per_gpu_tflops": value / world},
+            "roofline": roofline, "e2e": e2e, "cpu_baseline": cpu_baseline, "clocks": clk.summary(),
+            "gpu_launches": launches, "extra": extra,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extra", action="store_true", help="skip the decode / GPT-2 / fp32 extras")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    run_ours(args, rank, local_rank, world)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,133 @@
+"""CPU-side checks of the C ABI: the library loads, exports every symbol the header
+declares, rejects malformed parameter blocks, and plans kernels -- no GPU needed
+(``b200_sdpa_query_plan`` is host-only)."""
+
+import ctypes as C
+import os
+import re
+
+import pytest
+
+from torch_neuronx_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "b200_sdpa.h")
+
+
+def _declared_symbols():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(b200_sdpa_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = C.CDLL(_lib.LIB_PATH)
+    names = _declared_symbols()
+    assert "b200_sdpa_fwd" in names and "b200_sdpa_decode" in names and "b200_sdpa_merge" in names
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/b200_sdpa.h but not exported"
+    assert set(names) == set(_lib.EXPORTS), "python binding table and header disagree"
+
+
+def test_abi_version_and_strerror():
+    lib = _lib.load()
+    assert lib.b200_sdpa_abi_version() == _lib.ABI_VERSION
+    assert _lib.strerror(0) == "ok"
+    for code in range(1, 12):
+        assert _lib.strerror(code) not in ("ok", "unknown status")
+    assert _lib.strerror(999) == "unknown status"
+
+
+def _params(B=1, Hq=8, Hkv=2, L=256, S=256, E=128, Dv=128, dtype=_lib.BF16, contiguous=True, **kw):
+    p = _lib.Params()
+    p.struct_size = C.sizeof(_lib.Params)
+    p.dtype, p.device = dtype, -1
+    fake = 0x7F0000000000  # never dereferenced by the planner
+    p.q, p.k, p.v, p.out = fake, fake + (1 << 30), fake + (2 << 30), fake + (3 << 30)
+    p.B, p.Hq, p.Hkv, p.L, p.S, p.E, p.Dv = B, Hq, Hkv, L, S, E, Dv
+    p.q_stride[:] = [Hq * L * E, L * E, E, 1]
+    p.k_stride[:] = [Hkv * S * E, S * E, E, 1]
+    p.v_stride[:] = [Hkv * S * Dv, S * Dv, Dv, 1]
+    p.out_stride[:] = [Hq * L * Dv, L * Dv, Dv, 1]
+    p.lse_stride[:] = [Hq * L, L, 1]
+    p.scale = 0.1
+    for k_, v_ in kw.items():
+        setattr(p, k_, v_)
+    return p
+
+
+def _plan(p):
+    plan = _lib.Plan()
+    plan.struct_size = C.sizeof(_lib.Plan)
+    rc = _lib.load().b200_sdpa_query_plan(C.byref(p), C.byref(plan))
+    return rc, plan
+
+
+def test_planner_picks_the_expected_kernel():
+    rc, plan = _plan(_params(B=4, Hq=32, Hkv=8, L=4096, S=4096))
+    assert rc == 0 and plan.path == _lib.PATH_PREFILL
+    assert plan.block_m == 256 and plan.block_n == 128 and plan.threads == 320
+    assert plan.grid_x == 16 * 32 * 4 and plan.smem_bytes > 190 * 1024 and plan.workspace_bytes == 0
+    rc, plan = _plan(_params(B=64, Hq=32, Hkv=8, L=1, S=8192))
+    assert rc == 0 and plan.path == _lib.PATH_DECODE and plan.launches == 2
+    assert plan.workspace_bytes == 64 * 32 * plan.kv_splits * (128 + 2) * 4
+    rc, plan = _plan(_params(dtype=_lib.F32, E=64, Dv=64))
+    assert rc == 0 and plan.path == _lib.PATH_GENERIC
+    rc, plan = _plan(_params(E=96, Dv=96))  # head dim the tensor-core kernel is not built for
+    assert rc == 0 and plan.path == _lib.PATH_GENERIC
+    rc, plan = _plan(_params(scale=-1.0))
+    assert rc == 0 and plan.path == _lib.PATH_GENERIC
+
+
+def test_planner_rejects_bad_blocks():
+    lib = _lib.load()
+    p = _params()
+    p.struct_size = 12
+    assert _plan(p)[0] == _lib.ERR_STRUCT
+    assert _plan(_params(dtype=7))[0] == _lib.ERR_DTYPE
+    assert _plan(_params(Hq=6, Hkv=4))[0] == _lib.ERR_SHAPE
+    assert _plan(_params(L=0))[0] == _lib.ERR_SHAPE
+    p = _params()
+    p.q = None
+    assert _plan(p)[0] == _lib.ERR_NULL
+    # forcing the tensor-core path on a misaligned base is an alignment error, not a crash
+    p = _params(force_path=_lib.PATH_PREFILL)
+    p.q = 0x7F0000000002
+    assert _plan(p)[0] == _lib.ERR_ALIGNMENT
+    assert _plan(_params(force_path=_lib.PATH_DECODE))[0] == _lib.ERR_UNSUPPORTED  # L != 1
+    assert lib.b200_sdpa_query_plan(None, None) == _lib.ERR_NULL
+    assert lib.b200_sdpa_fwd(None, None) == _lib.ERR_NULL
+    assert lib.b200_sdpa_merge(None, None) == _lib.ERR_NULL
+
+
+def test_struct_layout_matches_the_header():
+    """Offsets computed by the C compiler for the header must equal ctypes' (guards the
+    binding against silent drift)."""
+    import shutil
+    import subprocess
+    import tempfile
+
+    cc = shutil.which("gcc") or shutil.which("cc")
+    if cc is None:
+        pytest.skip("no C compiler")
+    src = r"""
+#include <stdio.h>
+#include <stddef.h>
+#include "b200_sdpa.h"
+int main(void) {
+  printf("%zu %zu %zu %zu %zu %zu %zu\n", sizeof(B200SdpaParams), offsetof(B200SdpaParams, q_offset),
+         offsetof(B200SdpaParams, kv_lens), offsetof(B200SdpaParams, bias_stride), offsetof(B200SdpaParams, status),
+         sizeof(B200SdpaPlan), sizeof(B200SdpaMergeParams));
+  return 0;
+}
+"""
+    with tempfile.TemporaryDirectory() as d:
+        open(os.path.join(d, "t.c"), "w").write(src)
+        subprocess.run([cc, "-I", os.path.join(ROOT, "include"), os.path.join(d, "t.c"), "-o", os.path.join(d, "t")],
+                       check=True)
+        got = [int(x) for x in subprocess.run([os.path.join(d, "t")], capture_output=True, text=True,
+                                              check=True).stdout.split()]
+    P = _lib.Params
+    want = [C.sizeof(P), P.q_offset.offset, P.kv_lens.offset, P.bias_stride.offset, P.status.offset,
+            C.sizeof(_lib.Plan), C.sizeof(_lib.MergeParams)]
+    assert got == want

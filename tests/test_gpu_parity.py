@@ -1,0 +1,211 @@
+"""GPU parity: the CUDA path, called through the C ABI, against the CPU oracle.
+
+Bars (stated once in tests/util.py): fp32 rtol/atol 1e-5; bf16/fp16 max-abs <= 2e-2 and
+mean-abs <= 2e-3 against the fp32 oracle; lse abs <= 1e-3 (half) / 1e-5 (fp32); rows
+without a visible key exactly 0 / -inf.
+"""
+
+import math
+
+import pytest
+import torch
+
+from tests.golden_cases import expected_for, inputs_for
+from tests.util import check_against_oracle, make_qkv, run_cuda
+
+pytestmark = pytest.mark.gpu
+
+GENERIC, PREFILL, DECODE = 1, 2, 3
+
+
+def _golden_names():
+    import os
+
+    path = os.path.join(os.path.dirname(__file__), "golden", "sdpa_golden.pt")
+    return sorted(torch.load(path, weights_only=False)["cases"].keys())
+
+
+@pytest.mark.parametrize("name", _golden_names())
+def test_golden_cases(golden, name):
+    """Every committed upstream vector, through the automatic kernel choice."""
+    case = golden[name]
+    q, k, v, mask = inputs_for(name, case)
+    bias = None
+    if mask is not None:
+        bias = torch.where(mask, 0.0, float("-inf")).to(q.dtype) if mask.dtype == torch.bool else mask
+    out, lse = run_cuda(q, k, v, attn_bias=bias, is_causal=case["causal"], scale=case["scale"])
+    check_against_oracle(q, k, v, out, lse, attn_mask=mask, is_causal=case["causal"], scale=case["scale"], tag=name)
+    # and against the stored upstream output itself (computed in the input dtype)
+    for got, want in expected_for(name, case, out, lse):
+        finite = torch.isfinite(want.float())
+        tol = 1e-5 if q.dtype == torch.float32 else 2e-2
+        assert (got.float()[finite] - want.float()[finite]).abs().max().item() <= tol * max(
+            1.0, want.float()[finite].abs().max().item()), name
+
+
+SHAPES = [
+    # B, Hq, Hkv, L, S, D
+    (1, 1, 1, 1, 1, 64),
+    (2, 2, 2, 7, 7, 64),
+    (1, 4, 1, 64, 64, 128),
+    (1, 2, 2, 127, 127, 64),
+    (2, 8, 2, 128, 128, 128),
+    (1, 4, 4, 129, 129, 64),
+    (1, 8, 1, 577, 577, 128),
+    (2, 4, 2, 300, 45, 128),
+    (1, 4, 2, 45, 300, 64),
+    (1, 2, 1, 512, 1024, 128),
+]
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("path", [GENERIC, PREFILL])
+def test_half_paths(shape, causal, dtype, path):
+    B, Hq, Hkv, L, S, D = shape
+    q, k, v = make_qkv(11, B, Hq, Hkv, L, S, D, dtype)
+    out, lse = run_cuda(q, k, v, is_causal=causal, force_path=path)
+    check_against_oracle(q, k, v, out, lse, is_causal=causal, tag=f"{shape} causal={causal} path={path}")
+
+
+@pytest.mark.parametrize("shape", SHAPES[:8])
+@pytest.mark.parametrize("causal", [False, True])
+def test_fp32_generic(shape, causal):
+    B, Hq, Hkv, L, S, D = shape
+    q, k, v = make_qkv(12, B, Hq, Hkv, L, S, D, torch.float32)
+    out, lse = run_cuda(q, k, v, is_causal=causal)
+    check_against_oracle(q, k, v, out, lse, is_causal=causal, tag=f"fp32 {shape}")
+
+
+@pytest.mark.parametrize("path", [GENERIC, PREFILL])
+@pytest.mark.parametrize("causal", [False, True])
+def test_right_padding_lengths(path, causal):
+    q, k, v = make_qkv(13, 4, 8, 2, 384, 384, 128, torch.bfloat16)
+    lens = torch.tensor([384, 1, 200, 0], dtype=torch.int32)
+    out, lse = run_cuda(q, k, v, is_causal=causal, kv_lens=lens, force_path=path)
+    check_against_oracle(q, k, v, out, lse, is_causal=causal, kv_lens=lens, tag=f"kv_lens path={path}")
+
+
+@pytest.mark.parametrize("path", [GENERIC, PREFILL])
+@pytest.mark.parametrize("offsets", [(256, 0), (0, 256), (128, 64), (100, 300), (64, 128)])
+def test_block_offsets(path, offsets):
+    """Causal rule between blocks of a longer sequence (ring steps), incl. blocks the
+    rule hides completely."""
+    qo, ko = offsets
+    q, k, v = make_qkv(14, 1, 4, 2, 256, 256, 64, torch.bfloat16)
+    out, lse = run_cuda(q, k, v, is_causal=True, q_offset=qo, k_offset=ko, force_path=path)
+    check_against_oracle(q, k, v, out, lse, is_causal=True, q_offset=qo, k_offset=ko, tag=f"offsets {offsets}")
+
+
+def test_explicit_scale_and_head_dims_generic():
+    for D, Dv in ((48, 48), (32, 80), (256, 256), (512, 64)):
+        q, k, v = make_qkv(15, 1, 2, 1, 70, 90, D, torch.float32, Dv=Dv)
+        out, lse = run_cuda(q, k, v, scale=0.2)
+        check_against_oracle(q, k, v, out, lse, scale=0.2, tag=f"D={D} Dv={Dv}")
+    q, k, v = make_qkv(15, 1, 2, 2, 64, 64, 64, torch.bfloat16)
+    out, lse = run_cuda(q, k, v, scale=-0.3)  # negative scale is served by the generic kernel
+    check_against_oracle(q, k, v, out, lse, scale=-0.3, tag="negative scale")
+
+
+@pytest.mark.parametrize("path", [GENERIC, PREFILL])
+def test_transposed_storage_and_output_layout(path):
+    """(B,S,H,D) storage seen through transpose(1,2): no copies in, and the output takes
+    the query's strides (upstream tests/python_ops/test_cpp_dispatch.py:283-297)."""
+    import torch_neuronx_b200 as T
+
+    B, H, Hkv, L, D = 2, 8, 2, 320, 128
+    g = torch.Generator().manual_seed(16)
+    qs = torch.randn(B, L, H, D, generator=g).to(torch.bfloat16)
+    ks = torch.randn(B, L, Hkv, D, generator=g).to(torch.bfloat16)
+    vs = torch.randn(B, L, Hkv, D, generator=g).to(torch.bfloat16)
+    dev = torch.device("cuda", 0)
+    q, k, v = (t.to(dev).transpose(1, 2) for t in (qs, ks, vs))
+    assert not q.is_contiguous()
+    out, lse = T.sdpa_forward(q, k, v, is_causal=True, force_path=path)
+    torch.cuda.synchronize()
+    T.check_device_status()
+    assert out.stride() == q.stride() and out.shape == q.shape
+    check_against_oracle(qs.transpose(1, 2), ks.transpose(1, 2), vs.transpose(1, 2), out.cpu(), lse.cpu(),
+                         is_causal=True, tag="transposed")
+
+
+def test_bias_paths_and_dead_rows(golden):
+    case = golden["dead_rows_leftpad10"]
+    q, k, v, mask = case["q"], case["k"], case["v"], case["mask"]
+    bias = torch.where(mask, 0.0, float("-inf"))
+    out, lse = run_cuda(q, k, v, attn_bias=bias, scale=case["scale"])
+    assert torch.all(out[..., :10, :] == 0) and torch.all(lse[..., :10] == float("-inf"))
+    check_against_oracle(q, k, v, out, lse, attn_mask=mask, scale=case["scale"], tag="dead rows")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("group,D", [(1, 64), (4, 128), (8, 128), (3, 64), (16, 128)])
+def test_decode_ragged(dtype, group, D):
+    import torch_neuronx_b200 as T
+
+    B, Hkv, S = 6, 2, 1500
+    q, k, v = make_qkv(17, B, Hkv * group, Hkv, 1, S, D, dtype)
+    lens = torch.tensor([1500, 1, 0, 777, 256, 1023], dtype=torch.int32)
+    T.reset_launch_counts()
+    out, lse = run_cuda(q, k, v, kv_lens=lens, kv_chunk=256)
+    counts = T.launch_counts()
+    assert counts["decode_partial"] == 1 and counts["decode_combine"] == 1 and counts["prefill"] == 0
+    assert T.ops.last_plan["path"] == "decode" and T.ops.last_plan["kv_splits"] == 6
+    check_against_oracle(q, k, v, out, lse, kv_lens=lens, tag=f"decode g={group} D={D} {dtype}")
+    out2, lse2 = run_cuda(q, k, v, kv_lens=lens, kv_chunk=256)
+    assert torch.equal(out, out2) and torch.equal(lse, lse2), "decode must be run-to-run identical"
+
+
+def test_decode_default_chunk_and_no_lens():
+    q, k, v = make_qkv(18, 3, 32, 8, 1, 4096, 128, torch.bfloat16)
+    out, lse = run_cuda(q, k, v)
+    check_against_oracle(q, k, v, out, lse, tag="decode dense")
+
+
+def test_kernel_choice_is_observable():
+    """Launch counters prove which kernel served a call (upstream:
+    tests/utils/neuron_test_utils.py:18-135 assert_op_runs_on_neuron)."""
+    import torch_neuronx_b200 as T
+
+    q, k, v = make_qkv(19, 1, 4, 4, 256, 256, 128, torch.bfloat16)
+    T.reset_launch_counts()
+    run_cuda(q, k, v, is_causal=True)
+    assert T.launch_counts()["prefill"] == 1 and T.launch_counts()["generic"] == 0
+    qf, kf, vf = make_qkv(19, 1, 4, 4, 256, 256, 128, torch.float32)
+    run_cuda(qf, kf, vf, is_causal=True)
+    assert T.launch_counts()["generic"] == 1
+
+
+def test_run_to_run_identical_prefill():
+    q, k, v = make_qkv(20, 2, 8, 2, 640, 640, 128, torch.bfloat16)
+    a = run_cuda(q, k, v, is_causal=True, force_path=PREFILL)
+    b = run_cuda(q, k, v, is_causal=True, force_path=PREFILL)
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+
+
+def test_merge_kernel_matches_oracle():
+    import torch_neuronx_b200 as T
+    from oracle import sdpa_oracle as O
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(21)
+    B, H, L, D = 2, 3, 50, 64
+    pa = torch.randn(B, H, L, D, generator=g).to(torch.bfloat16)
+    pb = torch.randn(B, H, L, D, generator=g).to(torch.bfloat16)
+    la = torch.randn(B, H, L, generator=g) * 3
+    lb = torch.randn(B, H, L, generator=g) * 3
+    la[0, 0, :5] = float("-inf")
+    lb[0, 0, 3:8] = float("-inf")
+    acc = torch.empty(B, H, L, D, dtype=torch.float32, device=dev)
+    acc_l = torch.empty(B, H, L, dtype=torch.float32, device=dev)
+    fin = torch.full((B, H, L, D), float("nan"), dtype=torch.bfloat16, device=dev)
+    T.merge_partials(acc, acc_l, pa.to(dev), la.to(dev), first=True)
+    T.merge_partials(acc, acc_l, pb.to(dev), lb.to(dev), first=False, final_out=fin)
+    torch.cuda.synchronize()
+    ref_o, ref_l = O.merge_partials(pa, la, pb, lb)
+    assert torch.equal(acc_l.cpu() == float("-inf"), ref_l == float("-inf"))
+    live = ref_l != float("-inf")
+    torch.testing.assert_close(acc_l.cpu()[live], ref_l[live], rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(acc.cpu(), ref_o, rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(fin.cpu().float(), ref_o, rtol=1e-2, atol=1e-2)

@@ -1,0 +1,104 @@
+"""In-tree build of ``libb200_sdpa.so`` (sm_100a only) with plain ``nvcc``.
+
+``python -m torch_neuronx_b200.build`` compiles every ``csrc/*.cu`` to an object
+file and links them into one shared library next to this file.  Objects are
+rebuilt only when their source (or a header) changed; the key is a hash of the
+sources, the flags and the nvcc version, which plays the role of the upstream
+compile cache (``torch_neuronx/nki_kernel.py:57-115``) for an ahead-of-time
+build.  There is no JIT and no fallback: if the library is missing the package
+refuses to run.
+"""
+
+from __future__ import annotations
+
+import hashlib
+import json
+import os
+import shutil
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+OBJ_DIR = os.path.join(CSRC, "build")
+LIB_PATH = os.path.join(HERE, "libb200_sdpa.so")
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC",
+    "--expt-relaxed-constexpr",
+    "-Xptxas", "-v",
+]
+
+
+def find_nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.exists(cand):
+            return cand
+    raise RuntimeError("nvcc not found; set NVCC or put CUDA 12.8+ on PATH")
+
+
+def _sources():
+    cu = sorted(f for f in os.listdir(CSRC) if f.endswith(".cu"))
+    hdr = sorted(f for f in os.listdir(CSRC) if f.endswith((".cuh", ".h")))
+    hdr_paths = [os.path.join(CSRC, h) for h in hdr] + [os.path.join(HERE, "..", "include", "b200_sdpa.h")]
+    return cu, hdr_paths
+
+
+def _digest(paths, extra: str) -> str:
+    h = hashlib.sha256(extra.encode())
+    for p in paths:
+        with open(p, "rb") as f:
+            h.update(f.read())
+    return h.hexdigest()
+
+
+def build(verbose: bool = False, force: bool = False) -> str:
+    """Build (if needed) and return the path of the shared library."""
+    nvcc = find_nvcc()
+    version = subprocess.run([nvcc, "--version"], capture_output=True, text=True, check=True).stdout
+    cu, hdrs = _sources()
+    os.makedirs(OBJ_DIR, exist_ok=True)
+    stamp_path = os.path.join(OBJ_DIR, "stamps.json")
+    try:
+        with open(stamp_path) as f:
+            stamps = json.load(f)
+    except (OSError, ValueError):
+        stamps = {}
+    flag_key = " ".join(NVCC_FLAGS) + version
+
+    def compile_one(name: str):
+        src = os.path.join(CSRC, name)
+        obj = os.path.join(OBJ_DIR, name[:-3] + ".o")
+        key = _digest([src] + hdrs, flag_key)
+        if not force and stamps.get(name) == key and os.path.exists(obj):
+            return name, key, False, ""
+        cmd = [nvcc] + NVCC_FLAGS + ["-c", src, "-o", obj]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"nvcc failed for {name}:\n{res.stdout}\n{res.stderr}")
+        return name, key, True, res.stderr
+
+    rebuilt = False
+    with ThreadPoolExecutor(max_workers=min(8, len(cu))) as pool:
+        for name, key, did, log in pool.map(compile_one, cu):
+            stamps[name] = key
+            rebuilt |= did
+            if did and verbose:
+                sys.stderr.write(f"--- {name}\n{log}\n")
+    objs = [os.path.join(OBJ_DIR, n[:-3] + ".o") for n in cu]
+    if rebuilt or not os.path.exists(LIB_PATH):
+        cmd = [nvcc, "-shared", "-o", LIB_PATH] + objs + ["-cudart", "static", "-lpthread", "-ldl", "-lrt"]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
+    with open(stamp_path, "w") as f:
+        json.dump(stamps, f)
+    return LIB_PATH
+
+
+if __name__ == "__main__":
+    path = build(verbose="-v" in sys.argv, force="-f" in sys.argv)
+    print(path)

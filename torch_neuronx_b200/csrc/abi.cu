@@ -1,0 +1,199 @@
+// C ABI of the library: validation, kernel selection and launch bookkeeping.
+// See include/b200_sdpa.h for the contract of every entry point.
+#include "common.cuh"
+
+#include <atomic>
+
+namespace b200 {
+
+namespace {
+
+std::atomic<uint64_t> g_launches[KID_COUNT];
+
+int validate(const B200SdpaParams* a, Problem* p) {
+  if (a == nullptr) return B200_SDPA_ERR_NULL;
+  if (a->struct_size != sizeof(B200SdpaParams)) return B200_SDPA_ERR_STRUCT;
+  if (a->dtype != B200_SDPA_F32 && a->dtype != B200_SDPA_F16 && a->dtype != B200_SDPA_BF16) return B200_SDPA_ERR_DTYPE;
+  if (a->B <= 0 || a->Hq <= 0 || a->Hkv <= 0 || a->L <= 0 || a->S < 0 || a->E <= 0 || a->Dv <= 0)
+    return B200_SDPA_ERR_SHAPE;
+  if (a->Hq % a->Hkv != 0) return B200_SDPA_ERR_SHAPE;
+  if (a->q == nullptr || a->out == nullptr) return B200_SDPA_ERR_NULL;
+  if (a->S > 0 && (a->k == nullptr || a->v == nullptr)) return B200_SDPA_ERR_NULL;
+  if (a->bias != nullptr && a->bias_dtype != B200_SDPA_F32 && a->bias_dtype != B200_SDPA_F16 &&
+      a->bias_dtype != B200_SDPA_BF16)
+    return B200_SDPA_ERR_DTYPE;
+  p->q = a->q;
+  p->k = a->k;
+  p->v = a->v;
+  p->out = a->out;
+  p->lse = a->lse;
+  for (int i = 0; i < 4; ++i) {
+    p->qs[i] = a->q_stride[i];
+    p->ks[i] = a->k_stride[i];
+    p->vs[i] = a->v_stride[i];
+    p->os[i] = a->out_stride[i];
+    p->bs[i] = a->bias_stride[i];
+  }
+  for (int i = 0; i < 3; ++i) p->ls[i] = a->lse_stride[i];
+  p->B = a->B;
+  p->Hq = a->Hq;
+  p->Hkv = a->Hkv;
+  p->L = a->L;
+  p->S = a->S;
+  p->E = a->E;
+  p->Dv = a->Dv;
+  p->group = a->Hq / a->Hkv;
+  p->scale = a->scale;
+  p->causal = a->is_causal != 0;
+  p->causal_shift = a->q_offset - a->k_offset;
+  p->kv_lens = a->kv_lens;
+  p->bias = a->bias;
+  p->bias_dtype = a->bias_dtype;
+  p->status = a->status;
+  return B200_SDPA_OK;
+}
+
+// Kernel selection.  `have_workspace` is false when only planning.
+int choose(const B200SdpaParams* a, const Problem& p, int* path) {
+  const int want = a->force_path;
+  if (want != B200_SDPA_PATH_AUTO && want != B200_SDPA_PATH_GENERIC && want != B200_SDPA_PATH_PREFILL &&
+      want != B200_SDPA_PATH_DECODE)
+    return B200_SDPA_ERR_UNSUPPORTED;
+  if (want == B200_SDPA_PATH_GENERIC) {
+    *path = want;
+    return B200_SDPA_OK;
+  }
+  if (want == B200_SDPA_PATH_DECODE) {
+    if (!decode_eligible(p, a->dtype)) return B200_SDPA_ERR_UNSUPPORTED;
+    *path = want;
+    return B200_SDPA_OK;
+  }
+  bool align_only = false;
+  const bool pre = prefill_eligible(p, a->dtype, &align_only);
+  if (want == B200_SDPA_PATH_PREFILL) {
+    if (!pre) return align_only ? B200_SDPA_ERR_ALIGNMENT : B200_SDPA_ERR_UNSUPPORTED;
+    *path = want;
+    return B200_SDPA_OK;
+  }
+  if (decode_eligible(p, a->dtype)) {
+    *path = B200_SDPA_PATH_DECODE;
+  } else if (pre) {
+    *path = B200_SDPA_PATH_PREFILL;
+  } else {
+    *path = B200_SDPA_PATH_GENERIC;
+  }
+  return B200_SDPA_OK;
+}
+
+int select_device(int device) {
+  if (device < 0) return B200_SDPA_OK;
+  if (cudaSetDevice(device) != cudaSuccess) {
+    cudaGetLastError();
+    return B200_SDPA_ERR_CUDA;
+  }
+  return B200_SDPA_OK;
+}
+
+}  // namespace
+
+void count_launch(int kernel_id) {
+  if (kernel_id >= 0 && kernel_id < KID_COUNT) g_launches[kernel_id].fetch_add(1, std::memory_order_relaxed);
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_sdpa_abi_version(void) { return B200_SDPA_ABI_VERSION; }
+
+const char* b200_sdpa_strerror(int status) {
+  switch (status) {
+    case B200_SDPA_OK: return "ok";
+    case B200_SDPA_ERR_NULL: return "a required pointer is NULL";
+    case B200_SDPA_ERR_STRUCT: return "parameter block size does not match this library (ABI mismatch)";
+    case B200_SDPA_ERR_DTYPE: return "dtype must be float32, float16 or bfloat16";
+    case B200_SDPA_ERR_SHAPE: return "invalid shape (extents must be positive and Hq divisible by Hkv)";
+    case B200_SDPA_ERR_UNSUPPORTED: return "no kernel in this build serves the request on the requested path";
+    case B200_SDPA_ERR_WORKSPACE: return "workspace missing or smaller than b200_sdpa_query_plan() reports";
+    case B200_SDPA_ERR_ALIGNMENT: return "tensor-core path needs unit inner stride and 16-byte aligned bases/strides";
+    case B200_SDPA_ERR_CUDA: return "a CUDA call failed";
+    case B200_SDPA_ERR_DEVICE: return "device is not sm_100";
+    case B200_SDPA_ERR_TIMEOUT: return "a device-side wait gave up (kernel drained and returned)";
+    case B200_SDPA_ERR_TOO_LARGE: return "request exceeds the fixed capacity of this entry point";
+    default: return "unknown status";
+  }
+}
+
+int b200_sdpa_query_plan(const B200SdpaParams* params, B200SdpaPlan* plan) {
+  if (plan == nullptr) return B200_SDPA_ERR_NULL;
+  if (plan->struct_size != sizeof(B200SdpaPlan)) return B200_SDPA_ERR_STRUCT;
+  Problem p;
+  int rc = validate(params, &p);
+  if (rc != B200_SDPA_OK) return rc;
+  int path = 0;
+  rc = choose(params, p, &path);
+  if (rc != B200_SDPA_OK) return rc;
+  if (p.S == 0) path = B200_SDPA_PATH_GENERIC;
+  switch (path) {
+    case B200_SDPA_PATH_DECODE: return plan_decode(p, params->dtype, params->kv_chunk, plan);
+    case B200_SDPA_PATH_PREFILL: return plan_prefill(p, params->dtype, plan);
+    default: return plan_generic(p, params->dtype, plan);
+  }
+}
+
+int b200_sdpa_fwd(const B200SdpaParams* params, void* stream) {
+  Problem p;
+  int rc = validate(params, &p);
+  if (rc != B200_SDPA_OK) return rc;
+  int path = 0;
+  rc = choose(params, p, &path);
+  if (rc != B200_SDPA_OK) return rc;
+  if (p.S == 0) path = B200_SDPA_PATH_GENERIC;  // nothing to attend to: zeros and -inf
+  rc = select_device(params->device);
+  if (rc != B200_SDPA_OK) return rc;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (path == B200_SDPA_PATH_DECODE) {
+    rc = launch_decode(p, params->dtype, params->kv_chunk, params->workspace, params->workspace_bytes, st);
+    // Without scratch an automatic choice falls through to a kernel that needs none.
+    if (rc != B200_SDPA_ERR_WORKSPACE || params->force_path == B200_SDPA_PATH_DECODE) return rc;
+    bool unused = false;
+    path = prefill_eligible(p, params->dtype, &unused) ? B200_SDPA_PATH_PREFILL : B200_SDPA_PATH_GENERIC;
+  }
+  if (path == B200_SDPA_PATH_PREFILL) return launch_prefill(p, params->dtype, st);
+  return launch_generic(p, params->dtype, st);
+}
+
+int b200_sdpa_decode(const B200SdpaParams* params, void* stream) {
+  Problem p;
+  int rc = validate(params, &p);
+  if (rc != B200_SDPA_OK) return rc;
+  if (!decode_eligible(p, params->dtype)) return B200_SDPA_ERR_UNSUPPORTED;
+  rc = select_device(params->device);
+  if (rc != B200_SDPA_OK) return rc;
+  return launch_decode(p, params->dtype, params->kv_chunk, params->workspace, params->workspace_bytes,
+                       reinterpret_cast<cudaStream_t>(stream));
+}
+
+int b200_sdpa_merge(const B200SdpaMergeParams* m, void* stream) {
+  if (m == nullptr) return B200_SDPA_ERR_NULL;
+  if (m->struct_size != sizeof(B200SdpaMergeParams)) return B200_SDPA_ERR_STRUCT;
+  if (m->acc == nullptr || m->acc_lse == nullptr || m->part == nullptr || m->part_lse == nullptr)
+    return B200_SDPA_ERR_NULL;
+  if (m->B < 0 || m->Hq < 0 || m->L < 0 || m->Dv < 0) return B200_SDPA_ERR_SHAPE;
+  int rc = select_device(m->device);
+  if (rc != B200_SDPA_OK) return rc;
+  return launch_merge(*m, reinterpret_cast<cudaStream_t>(stream));
+}
+
+uint64_t b200_sdpa_launch_count(int kernel_id) {
+  if (kernel_id < 0 || kernel_id >= KID_COUNT) return 0;
+  return g_launches[kernel_id].load(std::memory_order_relaxed);
+}
+
+void b200_sdpa_reset_launch_counts(void) {
+  for (int i = 0; i < KID_COUNT; ++i) g_launches[i].store(0, std::memory_order_relaxed);
+}
+
+}  // extern "C"

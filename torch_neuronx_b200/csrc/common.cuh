@@ -1,0 +1,85 @@
+// Shared device-side declarations for the sm_100a SDPA kernels.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <math_constants.h>
+#include <stdint.h>
+
+#include "../../include/b200_sdpa.h"
+
+namespace b200 {
+
+// Problem description handed to kernels by value (a trimmed copy of
+// B200SdpaParams with derived fields).
+struct Problem {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* out;
+  float* lse;
+  int64_t qs[4], ks[4], vs[4], os[4];
+  int64_t ls[3];
+  int B, Hq, Hkv, L, S, E, Dv;
+  int group;            // Hq / Hkv
+  float scale;
+  int causal;
+  int64_t causal_shift; // q_offset - k_offset: key j visible iff j <= i + causal_shift
+  const int* kv_lens;
+  const void* bias;
+  int bias_dtype;
+  int64_t bs[4];
+  int* status;
+};
+
+enum KernelId { KID_GENERIC = 0, KID_PREFILL = 1, KID_DECODE = 2, KID_COMBINE = 3, KID_MERGE = 4, KID_COUNT = 5 };
+
+// Host launchers implemented in the per-kernel translation units.  Each returns
+// a b200_sdpa_status and never synchronises.
+int launch_generic(const Problem& p, int dtype, cudaStream_t stream);
+int plan_generic(const Problem& p, int dtype, B200SdpaPlan* plan);
+
+int launch_decode(const Problem& p, int dtype, int kv_chunk, void* workspace, uint64_t workspace_bytes,
+                  cudaStream_t stream);
+int plan_decode(const Problem& p, int dtype, int kv_chunk, B200SdpaPlan* plan);
+bool decode_eligible(const Problem& p, int dtype);
+
+int launch_prefill(const Problem& p, int dtype, cudaStream_t stream);
+int plan_prefill(const Problem& p, int dtype, B200SdpaPlan* plan);
+bool prefill_eligible(const Problem& p, int dtype, bool* alignment_only_failure);
+
+int launch_merge(const B200SdpaMergeParams& m, cudaStream_t stream);
+
+void count_launch(int kernel_id);
+
+// ---- small device helpers -------------------------------------------------
+
+template <typename T> __device__ __forceinline__ float to_f32(T x);
+template <> __device__ __forceinline__ float to_f32<float>(float x) { return x; }
+template <> __device__ __forceinline__ float to_f32<__half>(__half x) { return __half2float(x); }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float x);
+template <> __device__ __forceinline__ float from_f32<float>(float x) { return x; }
+template <> __device__ __forceinline__ __half from_f32<__half>(float x) { return __float2half_rn(x); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+__device__ __forceinline__ float load_as_f32(const void* base, int64_t idx, int dtype) {
+  if (dtype == B200_SDPA_F32) return reinterpret_cast<const float*>(base)[idx];
+  if (dtype == B200_SDPA_F16) return __half2float(reinterpret_cast<const __half*>(base)[idx]);
+  return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(base)[idx]);
+}
+
+// Number of keys batch b may look at (right padding / ragged cache).
+__device__ __forceinline__ int valid_keys(const Problem& p, int b) {
+  int n = p.S;
+  if (p.kv_lens != nullptr) {
+    int len = p.kv_lens[b];
+    len = len < 0 ? 0 : len;
+    n = len < n ? len : n;
+  }
+  return n;
+}
+
+}  // namespace b200

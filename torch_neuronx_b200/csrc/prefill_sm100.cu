@@ -1,0 +1,645 @@
+// FlashAttention-style prefill kernel for sm_100a: TMA -> shared memory ->
+// tcgen05 tensor cores with accumulators in tensor memory (TMEM).
+//
+// One CTA owns 256 query rows of one (batch, query head): two 128-row tiles
+// that take turns on the tensor cores while the other one is in its softmax.
+// Roles (320 threads):
+//   warps 0-3   softmax of tile 0: one thread per query row (= one TMEM lane)
+//   warps 4-7   softmax of tile 1
+//   warp  8     TMA producer: Q once, then K(j), V(j) tiles through a ring
+//   warp  9     MMA issuer: S_t = Q_t K(j)^T and O_t += P_t V(j), one thread
+// TMEM columns: [0,128) S0, [128,256) S1, [256,256+D) O0, [256+D,256+2D) O1;
+// the probabilities P_t (16-bit, two per column) overwrite the first 64 columns
+// of S_t and are fed to the second product straight from TMEM.
+//
+// Online softmax in the exp2 domain on raw scores: p = 2^(s*c - m*c) with
+// c = scale*log2(e); the running maximum m is only raised when it grows by more
+// than 2^8, so O is rarely rescaled.  All statistics and O stay fp32; P is
+// rounded to the input dtype exactly once, as upstream rounds its
+// probabilities (torch_neuronx/_sdpa_math.py:94).  Rows without a visible key
+// give out = 0, lse = -inf (:85-91).  The causal rule is j <= i + shift with
+// shift = q_offset - k_offset (0 reproduces the top-left aligned triangle of
+// :20-28); kv_lens masks right padding; key tiles that no row of the CTA can
+// see are never loaded.
+//
+// Every wait is bounded: on expiry the role raises a CTA-wide abort flag, every
+// other role drains, tensor memory is freed and the status word reports
+// B200_SDPA_ERR_TIMEOUT.
+#include "common.cuh"
+#include "ptx_sm100.cuh"
+
+#include <mutex>
+
+namespace b200 {
+
+namespace {
+
+using namespace ptx;
+
+constexpr int kBlockM = 128;   // rows per query tile (= TMEM lanes)
+constexpr int kBlockN = 128;   // keys per tile
+constexpr int kTilesPerCta = 2;
+constexpr int kRowsPerCta = kBlockM * kTilesPerCta;
+constexpr int kThreads = 320;
+constexpr int kProducerWarp = 8;
+constexpr int kMmaWarp = 9;
+constexpr int kBoxBytes = kBlockN * 128;          // one TMA box: 128 rows x 64 16-bit elements
+constexpr uint32_t kTmemCols = 512;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr float kRescaleThreshold = 8.0f;         // in units of log2
+
+template <int D> struct Cfg {
+  static constexpr int kBoxes = D / 64;                      // TMA boxes per tile
+  static constexpr int kTileBytes = kBlockN * D * 2;
+  static constexpr int kStages = (D == 128) ? 4 : 8;         // K/V ring slots
+  static constexpr int kSmemTiles = (kTilesPerCta + kStages) * kTileBytes;
+  static constexpr int kSmemBytes = kSmemTiles + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+struct Sync {
+  uint64_t q_full;
+  uint64_t kv_full[8];
+  uint64_t kv_empty[8];
+  uint64_t s_full[2];
+  uint64_t p_ready[2];
+  uint64_t o_done[2];
+  uint64_t o_staged[2];
+  uint64_t drain;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float lg2(float x) {
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+template <bool BF16> __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  uint32_t r;
+  if (BF16) {
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  } else {
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  }
+  return r;
+}
+
+__device__ __forceinline__ bool wait_clocked(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                             long long limit_cycles) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 15u) == 0u) {
+      if (*abort_flag != 0) return false;
+      if (clock64() - t0 > limit_cycles) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void report(int* status, int role, int step, int extra) {
+  if (status == nullptr) return;
+  if (atomicCAS(status, 0, B200_SDPA_ERR_TIMEOUT) == 0) {
+    status[1] = role;
+    status[2] = step;
+    status[3] = extra;
+  }
+}
+
+// Visible-key geometry of one 128-row tile.
+struct TileGeom {
+  int row0;       // first query row
+  int n_tiles;    // key tiles to process (0: nothing visible, or tile beyond L)
+  int min_lim;    // visible-key count of the tile's first row (may be <= 0)
+  bool in_range;  // row0 < L
+};
+
+__device__ __forceinline__ TileGeom tile_geometry(const Problem& p, int row0, int kv_limit) {
+  TileGeom g;
+  g.row0 = row0;
+  g.in_range = row0 < p.L;
+  long long end = kv_limit, first = kv_limit;
+  if (p.causal) {
+    const int last_row = (row0 + kBlockM < p.L ? row0 + kBlockM : p.L) - 1;
+    const long long e = static_cast<long long>(last_row) + p.causal_shift + 1;
+    const long long f = static_cast<long long>(row0) + p.causal_shift + 1;
+    end = e < end ? e : end;
+    first = f < first ? f : first;
+  }
+  if (end < 0) end = 0;
+  if (first < -1) first = -1;
+  g.n_tiles = g.in_range ? static_cast<int>((end + kBlockN - 1) / kBlockN) : 0;
+  g.min_lim = static_cast<int>(first);
+  return g;
+}
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(kThreads, 1)
+prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+               const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o, const Problem p,
+               const int n_qblk, const long long wait_limit) {
+  using C = Cfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t tiles = (raw_addr + 1023u) & ~1023u;            // 1024-byte aligned tile area
+  Sync* sync = reinterpret_cast<Sync*>(smem_raw + (tiles - raw_addr) + C::kSmemTiles);
+  volatile int* abort_flag = &sync->abort_flag;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+
+  // work item: longest (latest) query blocks first, heads of one kv group adjacent
+  const int per_blk = p.Hq * p.B;
+  const int qblk = n_qblk - 1 - static_cast<int>(blockIdx.x / per_blk);
+  const int rem = static_cast<int>(blockIdx.x % per_blk);
+  const int h = rem % p.Hq;
+  const int b = rem / p.Hq;
+  const int hk = h / p.group;
+  const int kv_limit = valid_keys(p, b);
+  const TileGeom tg0 = tile_geometry(p, qblk * kRowsPerCta, kv_limit);
+  const TileGeom tg1 = tile_geometry(p, qblk * kRowsPerCta + kBlockM, kv_limit);
+  const int n_iter = tg0.n_tiles > tg1.n_tiles ? tg0.n_tiles : tg1.n_tiles;
+
+  const uint32_t q_smem[2] = {tiles, tiles + C::kTileBytes};
+  const uint32_t kv_smem = tiles + kTilesPerCta * C::kTileBytes;
+
+  if (tid == 0) {
+    mbar_init(smem_u32(&sync->q_full), 1);
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(smem_u32(&sync->kv_full[s]), 1);
+      mbar_init(smem_u32(&sync->kv_empty[s]), 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(smem_u32(&sync->s_full[t]), 1);
+      mbar_init(smem_u32(&sync->p_ready[t]), kBlockM);
+      mbar_init(smem_u32(&sync->o_done[t]), 1);
+      mbar_init(smem_u32(&sync->o_staged[t]), kBlockM);
+    }
+    mbar_init(smem_u32(&sync->drain), 1);
+    sync->abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == kMmaWarp) {
+    tmem_alloc(smem_u32(&sync->tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  if (warp == kProducerWarp && lane == 0) {
+    prefetch_tmap(&tm_q);
+    prefetch_tmap(&tm_k);
+    prefetch_tmap(&tm_v);
+    prefetch_tmap(&tm_o);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = sync->tmem_base;
+
+  if (warp == kProducerWarp) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t q_bytes = 0;
+      if (tg0.in_range) q_bytes += C::kTileBytes;
+      if (tg1.in_range) q_bytes += C::kTileBytes;
+      const uint32_t qbar = smem_u32(&sync->q_full);
+      mbar_arrive_expect_tx(qbar, q_bytes);
+      for (int t = 0; t < 2; ++t) {
+        const TileGeom& tg = t == 0 ? tg0 : tg1;
+        if (!tg.in_range) continue;
+        for (int bx = 0; bx < C::kBoxes; ++bx)
+          tma_load_4d(q_smem[t] + bx * kBoxBytes, &tm_q, qbar, bx * 64, tg.row0, h, b);
+      }
+      bool alive = true;
+      for (int item = 0; item < 2 * n_iter && alive; ++item) {
+        const int j = item >> 1;
+        const int stage = item % C::kStages;
+        const uint32_t round = static_cast<uint32_t>(item / C::kStages);
+        if (round > 0) {
+          alive = wait_clocked(smem_u32(&sync->kv_empty[stage]), (round - 1) & 1u, abort_flag, wait_limit);
+          if (!alive) {
+            report(p.status, 1, item, stage);
+            break;
+          }
+        }
+        const uint32_t bar = smem_u32(&sync->kv_full[stage]);
+        const uint32_t dst = kv_smem + stage * C::kTileBytes;
+        mbar_arrive_expect_tx(bar, C::kTileBytes);
+        const CUtensorMap* map = (item & 1) ? &tm_v : &tm_k;
+        for (int bx = 0; bx < C::kBoxes; ++bx) tma_load_4d(dst + bx * kBoxBytes, map, bar, bx * 64, j * kBlockN, hk, b);
+      }
+      if (*abort_flag != 0) {
+        // give copies already in flight time to land before shared memory goes away
+        for (int i = 0; i < 200; ++i) __nanosleep(1000);
+      }
+    }
+    __syncwarp();
+  } else if (warp == kMmaWarp) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = make_idesc(BF16, false, kBlockM, kBlockN);
+      constexpr uint32_t idesc_pv = make_idesc(BF16, true, kBlockM, D);
+      const uint32_t s_tmem[2] = {tmem_base, tmem_base + 128u};
+      const uint32_t o_tmem[2] = {tmem_base + 256u, tmem_base + 256u + D};
+      bool alive = n_iter > 0;
+
+      auto issue_qk = [&](int t, uint32_t kv_addr) {
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * kBoxBytes + (kk & 3) * 32;
+          mma_ss(s_tmem[t], smem_desc_sw128(q_smem[t] + off, 16, 1024), smem_desc_sw128(kv_addr + off, 16, 1024),
+                 idesc_qk, kk > 0 ? 1u : 0u);
+        }
+      };
+      auto issue_pv = [&](int t, uint32_t kv_addr, bool accumulate) {
+#pragma unroll
+        for (int kk = 0; kk < kBlockN / 16; ++kk) {
+          mma_ts(o_tmem[t], s_tmem[t] + kk * 8, smem_desc_sw128(kv_addr + kk * 2048, kBoxBytes, 1024), idesc_pv,
+                 (accumulate || kk > 0) ? 1u : 0u);
+        }
+      };
+      auto wait_full = [&](int item) -> bool {
+        const int stage = item % C::kStages;
+        const uint32_t round = static_cast<uint32_t>(item / C::kStages);
+        const bool ok = wait_clocked(smem_u32(&sync->kv_full[stage]), round & 1u, abort_flag, wait_limit);
+        if (!ok) report(p.status, 2, item, stage);
+        return ok;
+      };
+      auto stage_addr = [&](int item) { return kv_smem + (item % C::kStages) * C::kTileBytes; };
+      auto empty_bar = [&](int item) { return smem_u32(&sync->kv_empty[item % C::kStages]); };
+
+      if (alive) {
+        alive = wait_clocked(smem_u32(&sync->q_full), 0, abort_flag, wait_limit);
+        if (!alive) report(p.status, 2, -1, 0);
+      }
+      if (alive) alive = wait_full(0);
+      if (alive) {
+        tc_fence_after_sync();
+        if (tg0.n_tiles > 0) {
+          issue_qk(0, stage_addr(0));
+          mma_commit(smem_u32(&sync->s_full[0]));
+        }
+        if (tg1.n_tiles > 0) {
+          issue_qk(1, stage_addr(0));
+          mma_commit(smem_u32(&sync->s_full[1]));
+        }
+        mma_commit(empty_bar(0));
+      }
+      for (int j = 0; j < n_iter && alive; ++j) {
+        const int item_v = 2 * j + 1, item_kn = 2 * j + 2;
+        const bool has_next = j + 1 < n_iter;
+        const bool act0 = j < tg0.n_tiles, act1 = j < tg1.n_tiles;
+        const bool nxt0 = j + 1 < tg0.n_tiles, nxt1 = j + 1 < tg1.n_tiles;
+        alive = wait_full(item_v);
+        if (!alive) break;
+        if (act0) {
+          alive = wait_clocked(smem_u32(&sync->p_ready[0]), j & 1, abort_flag, wait_limit);
+          if (!alive) {
+            report(p.status, 3, j, 0);
+            break;
+          }
+          tc_fence_after_sync();
+          issue_pv(0, stage_addr(item_v), j > 0);
+        }
+        if (has_next) {
+          alive = wait_full(item_kn);
+          if (!alive) break;
+          tc_fence_after_sync();
+        }
+        if (nxt0) {
+          issue_qk(0, stage_addr(item_kn));
+          mma_commit(smem_u32(&sync->s_full[0]));
+        } else if (act0) {
+          mma_commit(smem_u32(&sync->o_done[0]));
+        }
+        if (act1) {
+          alive = wait_clocked(smem_u32(&sync->p_ready[1]), j & 1, abort_flag, wait_limit);
+          if (!alive) {
+            report(p.status, 3, j, 1);
+            break;
+          }
+          tc_fence_after_sync();
+          issue_pv(1, stage_addr(item_v), j > 0);
+        }
+        mma_commit(empty_bar(item_v));
+        if (nxt1) {
+          issue_qk(1, stage_addr(item_kn));
+          mma_commit(smem_u32(&sync->s_full[1]));
+        } else if (act1) {
+          mma_commit(smem_u32(&sync->o_done[1]));
+        }
+        if (has_next) mma_commit(empty_bar(item_kn));
+      }
+      if (*abort_flag != 0) {
+        // let whatever was issued retire before tensor memory is released
+        mma_commit(smem_u32(&sync->drain));
+        long long t0 = clock64();
+        while (!mbar_try_wait(smem_u32(&sync->drain), 0) && clock64() - t0 < wait_limit) {
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ softmax roles
+    const int t = warp >> 2;                 // which 128-row tile
+    const int quad = warp & 3;               // TMEM lane quadrant this warp may touch
+    const int r = tid & 127;                 // row inside the tile
+    const TileGeom& tg = t == 0 ? tg0 : tg1;
+    const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t s_addr = tmem_base + lane_off + static_cast<uint32_t>(t) * 128u;
+    const uint32_t o_addr = tmem_base + lane_off + 256u + static_cast<uint32_t>(t) * D;
+    const int row_g = tg.row0 + r;
+    int lim = kv_limit;                      // keys [0, lim) are visible to this row
+    if (p.causal) {
+      const long long c = static_cast<long long>(row_g) + p.causal_shift + 1;
+      lim = c < lim ? static_cast<int>(c < 0 ? 0 : c) : lim;
+    }
+    const float sl2 = p.scale * kLog2e;
+    float m_run = -CUDART_INF_F, l_run = 0.f;
+    bool alive = true;
+
+    if (tg.in_range) {
+      for (int j = 0; j < tg.n_tiles; ++j) {
+        bool ok = wait_clocked(smem_u32(&sync->s_full[t]), j & 1, abort_flag, wait_limit);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          if (lane == 0) report(p.status, 4 + t, j, quad);
+          alive = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const int col0 = j * kBlockN;
+        const bool need_mask = col0 + kBlockN > tg.min_lim;
+
+        // pass 1: row maximum of the raw scores
+        float mx = -CUDART_INF_F;
+#pragma unroll
+        for (int c = 0; c < kBlockN / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(s_addr + c * 32, v);
+          tmem_ld_wait();
+          if (need_mask) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              mx = fmaxf(mx, (col0 + c * 32 + i < lim) ? __uint_as_float(v[i]) : -CUDART_INF_F);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+          }
+        }
+        const float m_new = fmaxf(m_run, mx);
+        const bool grow = (m_new - m_run) * sl2 > kRescaleThreshold;  // false for NaN (-inf - -inf)
+        float alpha = 1.f;
+        if (grow) {
+          alpha = ex2((m_run - m_new) * sl2);   // m_run = -inf -> 0
+          l_run *= alpha;
+          m_run = m_new;
+        }
+        if (j > 0 && __any_sync(0xffffffffu, grow)) {
+          // raise the reference maximum: O_t *= alpha (PV(j-1) has retired: its
+          // completion is ordered before s_full(j))
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t v[32];
+            tmem_ld_32x32(o_addr + c * 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+            tmem_st_32x32(o_addr + c * 32, v);
+          }
+          tmem_st_wait();
+        }
+        const float nms = (m_run == -CUDART_INF_F) ? 0.f : -m_run * sl2;
+
+        // pass 2: probabilities, row sum, P -> TMEM (over the first 64 columns of S)
+        float sum = 0.f;
+#pragma unroll
+        for (int c = 0; c < kBlockN / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(s_addr + c * 32, v);
+          tmem_ld_wait();
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float s0 = __uint_as_float(v[i]), s1 = __uint_as_float(v[i + 1]);
+            if (need_mask) {
+              s0 = (col0 + c * 32 + i < lim) ? s0 : -CUDART_INF_F;
+              s1 = (col0 + c * 32 + i + 1 < lim) ? s1 : -CUDART_INF_F;
+            }
+            const float p0 = ex2(fmaf(s0, sl2, nms));
+            const float p1 = ex2(fmaf(s1, sl2, nms));
+            sum += p0 + p1;
+            pk[i >> 1] = pack2<BF16>(p0, p1);
+          }
+          tmem_st_32x16(s_addr + c * 16, pk);
+        }
+        l_run += sum;
+        tmem_st_wait();
+        tc_fence_before_sync();
+        mbar_arrive(smem_u32(&sync->p_ready[t]));
+      }
+
+      // ------------------------------------------------------------- epilogue
+      if (alive && tg.n_tiles > 0) {
+        bool ok = wait_clocked(smem_u32(&sync->o_done[t]), 0, abort_flag, wait_limit);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          if (lane == 0) report(p.status, 6 + t, 0, quad);
+          alive = false;
+        }
+        tc_fence_after_sync();
+      }
+      if (alive) {
+        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+        uint8_t* o_stage = smem_raw + (q_smem[t] - raw_addr);   // the Q tile is no longer needed
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t v[32];
+          if (tg.n_tiles > 0) {
+            tmem_ld_32x32(o_addr + c * 32, v);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = 0u;
+          }
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2)
+            pk[i >> 1] = pack2<BF16>(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
+          // 32 columns = 64 bytes = four 16-byte units of the 128-byte swizzled row
+          uint8_t* box = o_stage + (c >> 1) * kBoxBytes + r * 128;
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int unit = ((c & 1) * 4 + u) ^ (r & 7);
+            *reinterpret_cast<uint4*>(box + unit * 16) = make_uint4(pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
+          }
+        }
+        // Every writer publishes its rows to the async proxy and arrives; only the
+        // storing thread waits (bounded), so a role that gave up cannot strand the
+        // others at a barrier.
+        fence_proxy_async_smem();
+        mbar_arrive(smem_u32(&sync->o_staged[t]));
+        if (r == 0 && wait_clocked(smem_u32(&sync->o_staged[t]), 0, abort_flag, wait_limit)) {
+          for (int bx = 0; bx < C::kBoxes; ++bx) tma_store_4d(&tm_o, q_smem[t] + bx * kBoxBytes, bx * 64, tg.row0, h, b);
+          tma_store_commit();
+          tma_store_wait_all();
+        }
+        if (p.lse != nullptr && row_g < p.L) {
+          const float lse = l_run > 0.f ? (m_run * sl2 + lg2(l_run)) * kLn2 : -CUDART_INF_F;
+          p.lse[b * p.ls[0] + h * p.ls[1] + row_g * p.ls[2]] = lse;
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == kMmaWarp) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------ host side --
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    } else {
+      cudaGetLastError();
+    }
+  });
+  return fn;
+}
+
+// (D, rows, heads, batch) view of a (B, H, S, D) tensor with unit inner stride.
+bool make_map(CUtensorMap* map, const void* base, bool bf16, int d, int rows, int heads, int batch,
+              const int64_t* stride /* elements, (B,H,S,D) order */) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return false;
+  const cuuint64_t dims[4] = {static_cast<cuuint64_t>(d), static_cast<cuuint64_t>(rows),
+                              static_cast<cuuint64_t>(heads), static_cast<cuuint64_t>(batch)};
+  auto fix = [&](int64_t s, int n) -> cuuint64_t {
+    // a dimension of extent 1 is never stepped; give it any legal stride
+    return static_cast<cuuint64_t>((n == 1 ? static_cast<int64_t>(d) : s) * 2);
+  };
+  const cuuint64_t strides[3] = {fix(stride[2], rows), fix(stride[1], heads), fix(stride[0], batch)};
+  const cuuint32_t box[4] = {64, static_cast<cuuint32_t>(kBlockN), 1, 1};
+  const cuuint32_t elem[4] = {1, 1, 1, 1};
+  const CUresult rc = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                         const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return rc == CUDA_SUCCESS;
+}
+
+bool strides_ok(const void* base, const int64_t* s, int rows, int heads, int batch) {
+  if (reinterpret_cast<uintptr_t>(base) % 16) return false;
+  if (s[3] != 1) return false;
+  const int n[3] = {batch, heads, rows};
+  for (int i = 0; i < 3; ++i) {
+    if (n[i] == 1) continue;
+    if (s[i] <= 0 || (s[i] * 2) % 16 != 0 || s[i] * 2 >= (1LL << 40)) return false;
+  }
+  return true;
+}
+
+long long wait_limit_cycles() {
+  // about two seconds at 2 GHz; B200_SDPA_WAIT_LIMIT overrides (cycles)
+  static long long v = [] {
+    const char* e = getenv("B200_SDPA_WAIT_LIMIT");
+    long long x = e ? atoll(e) : 0;
+    return x > 0 ? x : (1LL << 32);
+  }();
+  return v;
+}
+
+template <int D, bool BF16>
+int launch_variant(const Problem& p, cudaStream_t stream) {
+  using C = Cfg<D>;
+  CUtensorMap tq, tk, tv, to;
+  if (!make_map(&tq, p.q, BF16, D, p.L, p.Hq, p.B, p.qs) || !make_map(&tk, p.k, BF16, D, p.S, p.Hkv, p.B, p.ks) ||
+      !make_map(&tv, p.v, BF16, D, p.S, p.Hkv, p.B, p.vs) || !make_map(&to, p.out, BF16, D, p.L, p.Hq, p.B, p.os))
+    return B200_SDPA_ERR_CUDA;
+  auto kern = prefill_kernel<D, BF16>;
+  static std::once_flag once;
+  static cudaError_t attr_rc = cudaSuccess;
+  std::call_once(once, [&] {
+    attr_rc = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+  });
+  if (attr_rc != cudaSuccess) {
+    // the attribute is per device: retry once for processes that switch devices
+    attr_rc = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    if (attr_rc != cudaSuccess) {
+      cudaGetLastError();
+      return B200_SDPA_ERR_CUDA;
+    }
+  }
+  const int n_qblk = (p.L + kRowsPerCta - 1) / kRowsPerCta;
+  const long long grid = static_cast<long long>(n_qblk) * p.Hq * p.B;
+  if (grid <= 0 || grid > 0x7fffffffLL) return B200_SDPA_ERR_UNSUPPORTED;
+  kern<<<static_cast<unsigned>(grid), kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, to, p, n_qblk, wait_limit_cycles());
+  if (cudaGetLastError() != cudaSuccess) return B200_SDPA_ERR_CUDA;
+  count_launch(KID_PREFILL);
+  return B200_SDPA_OK;
+}
+
+}  // namespace
+
+bool prefill_eligible(const Problem& p, int dtype, bool* alignment_only_failure) {
+  if (alignment_only_failure) *alignment_only_failure = false;
+  if (dtype != B200_SDPA_F16 && dtype != B200_SDPA_BF16) return false;
+  if (p.E != p.Dv || (p.E != 64 && p.E != 128)) return false;
+  if (p.bias != nullptr) return false;
+  if (!(p.scale > 0.f) || !(p.scale < 1e30f)) return false;
+  if (p.L < 1 || p.S < 1) return false;
+  const bool ok = strides_ok(p.q, p.qs, p.L, p.Hq, p.B) && strides_ok(p.k, p.ks, p.S, p.Hkv, p.B) &&
+                  strides_ok(p.v, p.vs, p.S, p.Hkv, p.B) && strides_ok(p.out, p.os, p.L, p.Hq, p.B);
+  if (!ok && alignment_only_failure) *alignment_only_failure = true;
+  return ok;
+}
+
+int plan_prefill(const Problem& p, int dtype, B200SdpaPlan* plan) {
+  if (!prefill_eligible(p, dtype, nullptr)) return B200_SDPA_ERR_UNSUPPORTED;
+  const int n_qblk = (p.L + kRowsPerCta - 1) / kRowsPerCta;
+  const long long grid = static_cast<long long>(n_qblk) * p.Hq * p.B;
+  if (grid > 0x7fffffffLL) return B200_SDPA_ERR_UNSUPPORTED;
+  plan->path = B200_SDPA_PATH_PREFILL;
+  plan->block_m = kRowsPerCta;
+  plan->block_n = kBlockN;
+  plan->grid_x = static_cast<int32_t>(grid);
+  plan->grid_y = plan->grid_z = 1;
+  plan->threads = kThreads;
+  plan->smem_bytes = p.E == 128 ? Cfg<128>::kSmemBytes : Cfg<64>::kSmemBytes;
+  plan->kv_splits = 1;
+  plan->launches = 1;
+  plan->workspace_bytes = 0;
+  return B200_SDPA_OK;
+}
+
+int launch_prefill(const Problem& p, int dtype, cudaStream_t stream) {
+  if (!prefill_eligible(p, dtype, nullptr)) return B200_SDPA_ERR_UNSUPPORTED;
+  const bool bf16 = dtype == B200_SDPA_BF16;
+  if (p.E == 128) return bf16 ? launch_variant<128, true>(p, stream) : launch_variant<128, false>(p, stream);
+  return bf16 ? launch_variant<64, true>(p, stream) : launch_variant<64, false>(p, stream);
+}
+
+}  // namespace b200

@@ -1,0 +1,461 @@
+"""Operator layer: the fused SDPA forward on B200 behind upstream's op API.
+
+Three entry levels, mirroring upstream:
+
+``scaled_dot_product_attention(...)``
+    same keyword arguments as ``torch.nn.functional.scaled_dot_product_attention``;
+    what a model calls.
+
+``aten::_scaled_dot_product_fused_attention_overrideable`` (CUDA key)
+    the ATen op upstream registers for its device
+    (``torch_neuronx/python_ops/__init__.py:86-95``,
+    ``torch_neuronx/python_ops/scaled_dot_product_fused_attention.py:458-508``);
+    returns the same 9-tuple (``:366-376``).  Argument checks and messages follow
+    ``torch_neuronx/csrc/core/dispatch/NeuronDispatcher.cpp:2380-2458`` and
+    ``torch_neuronx/python_ops/base.py:1036-1111``.
+
+``b200_sdpa::fwd``
+    the kernel-level custom op with the positional signature of
+    ``nki_kernels::scaled_dot_product_attention_kernel``
+    (``torch_neuronx/python_ops/nki_kernels/scaled_dot_product_attention.py:9-41``)
+    plus one optional extension, ``kv_lens`` (valid keys per batch).
+
+All of them end in one foreign call into ``libb200_sdpa.so``.  There is no
+fallback: non-CUDA tensors are rejected and a missing library raises.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+_DTYPE_CODE = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
+
+# ----------------------------------------------------------------------------
+# per-device scratch and status words
+# ----------------------------------------------------------------------------
+
+_status_words: dict[int, torch.Tensor] = {}
+_zero_scalars: dict[int, torch.Tensor] = {}
+_workspaces: dict[tuple[int, int], torch.Tensor] = {}
+last_plan: dict = {}
+
+
+def _device_index(t: torch.Tensor) -> int:
+    return t.device.index if t.device.index is not None else torch.cuda.current_device()
+
+
+def _status_word(dev: int) -> torch.Tensor:
+    w = _status_words.get(dev)
+    if w is None:
+        w = torch.zeros(4, dtype=torch.int32, device=torch.device("cuda", dev))
+        _status_words[dev] = w
+    return w
+
+
+def _zero_scalar(dev: int) -> torch.Tensor:
+    z = _zero_scalars.get(dev)
+    if z is None:
+        z = torch.zeros((), dtype=torch.int64, device=torch.device("cuda", dev))
+        _zero_scalars[dev] = z
+    return z
+
+
+def _workspace(dev: int, nbytes: int) -> torch.Tensor:
+    """Scratch for the decode partials.  One buffer per (device, stream); it only
+    grows.  Work on one stream is ordered, so reuse across calls is safe."""
+    key = (dev, torch.cuda.current_stream(dev).cuda_stream)
+    w = _workspaces.get(key)
+    if w is None or w.numel() < nbytes:
+        w = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=torch.device("cuda", dev))
+        _workspaces[key] = w
+    return w
+
+
+def check_device_status(device=None) -> None:
+    """Synchronise and raise if any kernel reported a device-side error (a bounded
+    wait that gave up).  Cheap enough for tests; not called on the hot path."""
+    devs = list(_status_words) if device is None else [torch.device(device).index or 0]
+    for dev in devs:
+        w = _status_words.get(dev)
+        if w is None:
+            continue
+        vals = w.cpu().tolist()
+        if vals[0] != 0:
+            w.zero_()
+            raise RuntimeError(
+                f"b200_sdpa device status {vals[0]} ({_lib.strerror(vals[0])}); role={vals[1]} step={vals[2]} "
+                f"extra={vals[3]}"
+            )
+
+
+# ----------------------------------------------------------------------------
+# validation (same rules and messages as upstream's dispatcher)
+# ----------------------------------------------------------------------------
+
+
+def _validate(query, key, value, attn_bias, dropout_p, is_causal, return_debug_mask):
+    if return_debug_mask:
+        raise NotImplementedError("return_debug_mask=True is not supported: the fused kernel keeps no attention matrix")
+    if attn_bias is not None and is_causal:
+        raise RuntimeError(
+            "_scaled_dot_product_fused_attention_overrideable: Explicit attn_mask should not be set when is_causal=True"
+        )
+    for name, t in (("query", query), ("key", key), ("value", value)):
+        if not isinstance(t, torch.Tensor):
+            raise TypeError(f"{name} must be a Tensor")
+    if not (query.device.type == key.device.type == value.device.type):
+        raise RuntimeError("Expected query, key, and value to have the same device type")
+    if query.dtype not in (torch.float32, torch.float16, torch.bfloat16, torch.float64):
+        raise RuntimeError(f"SDPA: query dtype must be float32, float16, or bfloat16, got {query.dtype}")
+    if not (query.dtype == key.dtype == value.dtype):
+        raise RuntimeError("Expected query, key, and value to have the same dtype")
+    if query.dim() != 4 or key.dim() != 4 or value.dim() != 4:
+        raise RuntimeError("SDPA: query, key and value must be 4D tensors (B, H, S, D)")
+    if not (query.shape[0] == key.shape[0] == value.shape[0]):
+        raise RuntimeError("SDPA: batch sizes must match")
+    if key.shape[1] != value.shape[1]:
+        raise RuntimeError("SDPA: key and value must have the same number of heads")
+    if key.shape[2] != value.shape[2]:
+        raise RuntimeError("SDPA: key and value must have the same sequence length")
+    if query.shape[3] != key.shape[3]:
+        raise RuntimeError("SDPA: query and key must have the same embedding dimension")
+    if key.shape[1] == 0 or query.shape[1] % key.shape[1] != 0:
+        raise RuntimeError("SDPA: Number of heads in key and value must divide the number of heads in query")
+    if dropout_p < 0.0 or dropout_p > 1.0:
+        raise ValueError(f"dropout_p={dropout_p} is outside [0, 1]. Pass a value in [0, 1].")
+    if dropout_p != 0.0:
+        raise NotImplementedError("dropout_p != 0 is not supported by the B200 fused attention path")
+    if query.device.type != "cuda":
+        raise ValueError(f"Expected CUDA device, got {query.device}")
+    if not (query.device == key.device == value.device):
+        raise RuntimeError("Expected query, key, and value to be on the same device")
+
+
+def alloc_like_query(query: torch.Tensor, shape) -> torch.Tensor:
+    """Output buffer laid out like the query: identical strides when the shapes agree,
+    otherwise dense strides in the query's dimension order (the rule of torch's own
+    meta kernel for this op, which upstream also follows:
+    ``scaled_dot_product_fused_attention.py:357-358``).  The kernels store with these
+    strides directly, so no re-layout copy follows."""
+    shape = tuple(int(s) for s in shape)
+    if tuple(query.shape) == shape:
+        return torch.empty_like(query)
+    order = sorted(range(4), key=lambda i: query.stride(i), reverse=True)
+    permuted = [shape[i] for i in order]
+    back = [order.index(i) for i in range(4)]
+    return torch.empty(permuted, dtype=query.dtype, device=query.device).permute(back)
+
+
+def _bias_strides(bias: torch.Tensor, target):
+    """Strides of ``bias`` viewed as broadcast to ``target`` (0 where broadcast)."""
+    if bias.dim() > 4:
+        raise RuntimeError("attn_mask must have at most 4 dimensions")
+    shape = (1,) * (4 - bias.dim()) + tuple(bias.shape)
+    stride = (0,) * (4 - bias.dim()) + tuple(bias.stride())
+    out = []
+    for s, st, t in zip(shape, stride, target):
+        if s == t:
+            out.append(st if s != 1 else 0)
+        elif s == 1:
+            out.append(0)
+        else:
+            raise RuntimeError(f"attn_mask of shape {tuple(bias.shape)} is not broadcastable to {tuple(target)}")
+    return out
+
+
+# ----------------------------------------------------------------------------
+# the one foreign call
+# ----------------------------------------------------------------------------
+
+
+def sdpa_forward(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    *,
+    attn_bias: Optional[torch.Tensor] = None,
+    is_causal: bool = False,
+    scale: Optional[float] = None,
+    kv_lens: Optional[torch.Tensor] = None,
+    q_offset: int = 0,
+    k_offset: int = 0,
+    need_lse: bool = True,
+    out: Optional[torch.Tensor] = None,
+    lse: Optional[torch.Tensor] = None,
+    force_path: int = _lib.PATH_AUTO,
+    kv_chunk: int = 0,
+):
+    """Launch the forward on the current CUDA stream; returns ``(out, lse)``
+    (``lse`` is ``None`` when ``need_lse`` is false and no buffer was passed).
+
+    Inputs must already satisfy :func:`_validate`; dtype is fp32/fp16/bf16.
+    ``attn_bias`` is additive (bool masks are converted by the callers)."""
+    lib = _lib.load()
+    dev = _device_index(query)
+    B, Hq, L, E = query.shape
+    Hkv, S, Dv = key.shape[1], key.shape[2], value.shape[3]
+    if scale is None:
+        scale = 1.0 / math.sqrt(E)
+    if out is None:
+        out = alloc_like_query(query, (B, Hq, L, Dv))
+    if lse is None and need_lse:
+        lse = torch.empty((B, Hq, L), dtype=torch.float32, device=query.device)
+
+    p = _lib.Params()
+    p.struct_size = C.sizeof(_lib.Params)
+    p.dtype = _DTYPE_CODE[query.dtype]
+    p.device = dev
+    p.force_path = force_path
+    p.q, p.k, p.v, p.out = query.data_ptr(), key.data_ptr(), value.data_ptr(), out.data_ptr()
+    p.lse = lse.data_ptr() if lse is not None else None
+    p.q_stride[:] = query.stride()
+    p.k_stride[:] = key.stride()
+    p.v_stride[:] = value.stride()
+    p.out_stride[:] = out.stride()
+    if lse is not None:
+        p.lse_stride[:] = lse.stride()
+    p.B, p.Hq, p.Hkv, p.L, p.S, p.E, p.Dv = B, Hq, Hkv, L, S, E, Dv
+    p.scale = float(scale)
+    p.is_causal = 1 if is_causal else 0
+    p.q_offset, p.k_offset = int(q_offset), int(k_offset)
+    if kv_lens is not None:
+        if kv_lens.dtype != torch.int32 or kv_lens.device != query.device or kv_lens.shape != (B,):
+            raise RuntimeError("kv_lens must be an int32 CUDA tensor of shape (B,) on the query's device")
+        if not kv_lens.is_contiguous():
+            kv_lens = kv_lens.contiguous()
+        p.kv_lens = kv_lens.data_ptr()
+    if attn_bias is not None:
+        if attn_bias.dtype not in _DTYPE_CODE:
+            attn_bias = attn_bias.to(torch.float32)
+        p.bias = attn_bias.data_ptr()
+        p.bias_dtype = _DTYPE_CODE[attn_bias.dtype]
+        p.bias_stride[:] = _bias_strides(attn_bias, (B, Hq, L, S))
+    p.kv_chunk = int(kv_chunk)
+    p.status = _status_word(dev).data_ptr()
+
+    plan = _lib.Plan()
+    plan.struct_size = C.sizeof(_lib.Plan)
+    rc = lib.b200_sdpa_query_plan(C.byref(p), C.byref(plan))
+    if rc != _lib.OK:
+        raise RuntimeError(f"b200_sdpa_query_plan: {_lib.strerror(rc)}")
+    ws = None
+    if plan.workspace_bytes:
+        ws = _workspace(dev, int(plan.workspace_bytes))
+        p.workspace = ws.data_ptr()
+        p.workspace_bytes = ws.numel()
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    rc = lib.b200_sdpa_fwd(C.byref(p), C.c_void_p(stream))
+    if rc != _lib.OK:
+        raise RuntimeError(f"b200_sdpa_fwd: {_lib.strerror(rc)}")
+    last_plan.clear()
+    last_plan.update(
+        path=_lib.PATH_NAMES.get(plan.path, str(plan.path)), block_m=plan.block_m, block_n=plan.block_n,
+        grid=(plan.grid_x, plan.grid_y, plan.grid_z), threads=plan.threads, smem_bytes=plan.smem_bytes,
+        kv_splits=plan.kv_splits, launches=plan.launches, workspace_bytes=int(plan.workspace_bytes),
+    )
+    return out, lse
+
+
+def merge_partials(acc, acc_lse, part, part_lse, *, first=False, final_out=None):
+    """One ring-step merge on the current stream: fold ``(part, part_lse)`` into the
+    fp32 running ``(acc, acc_lse)`` in place; optionally also write the merged rows
+    to ``final_out`` in the partial's dtype."""
+    lib = _lib.load()
+    B, Hq, L, Dv = part.shape
+    if acc.dtype != torch.float32 or not acc.is_contiguous() or tuple(acc.shape) != (B, Hq, L, Dv):
+        raise RuntimeError("acc must be a contiguous fp32 tensor shaped like the partial")
+    if acc_lse.dtype != torch.float32 or not acc_lse.is_contiguous() or tuple(acc_lse.shape) != (B, Hq, L):
+        raise RuntimeError("acc_lse must be a contiguous fp32 tensor of shape (B, Hq, L)")
+    m = _lib.MergeParams()
+    m.struct_size = C.sizeof(_lib.MergeParams)
+    m.dtype = _DTYPE_CODE[part.dtype]
+    m.device = _device_index(part)
+    m.first = 1 if first else 0
+    m.acc, m.acc_lse = acc.data_ptr(), acc_lse.data_ptr()
+    m.part, m.part_lse = part.data_ptr(), part_lse.data_ptr()
+    m.part_stride[:] = part.stride()
+    m.part_lse_stride[:] = part_lse.stride()
+    if final_out is not None:
+        m.final_out = final_out.data_ptr()
+        m.final_stride[:] = final_out.stride()
+    m.B, m.Hq, m.L, m.Dv = B, Hq, L, Dv
+    rc = lib.b200_sdpa_merge(C.byref(m), C.c_void_p(torch.cuda.current_stream(m.device).cuda_stream))
+    if rc != _lib.OK:
+        raise RuntimeError(f"b200_sdpa_merge: {_lib.strerror(rc)}")
+
+
+# ----------------------------------------------------------------------------
+# ATen-level op
+# ----------------------------------------------------------------------------
+
+
+def _additive_bias(attn_mask: Optional[torch.Tensor], query: torch.Tensor):
+    """Bool mask (True = keep) -> 0 / -inf in the query dtype; float masks are used as
+    they are (``decompositions.py:2099-2104``)."""
+    if attn_mask is None:
+        return None
+    if attn_mask.dtype == torch.bool:
+        return torch.where(attn_mask, 0.0, float("-inf")).to(query.dtype)
+    return attn_mask
+
+
+def fused_attention_overrideable(
+    query, key, value, attn_bias=None, dropout_p=0.0, is_causal=False, return_debug_mask=False, *, scale=None
+):
+    """CUDA implementation of ``aten::_scaled_dot_product_fused_attention_overrideable``.
+
+    Returns ``(output, logsumexp, cum_seq_q, cum_seq_k, max_q, max_k, philox_seed,
+    philox_offset, debug_attn_mask)``: output in the query dtype with the query's
+    layout, logsumexp fp32 ``(B, Hq, L)`` always (the ATen contract upstream keeps,
+    ``scaled_dot_product_fused_attention.py:291-295``), the unused slots ``None`` and
+    the philox slots zero scalars since dropout is not offered."""
+    _validate(query, key, value, attn_bias, dropout_p, is_causal, return_debug_mask)
+    B, Hq, L, _ = query.shape
+    S, Dv = key.shape[2], value.shape[3]
+    if query.numel() == 0 or key.shape[3] == 0 or Dv == 0:
+        raise RuntimeError("SDPA: zero-size inputs are not routed to the fused kernel")
+    in_dtype = query.dtype
+    if in_dtype == torch.float64:  # computed in fp32 and cast back (NeuronDispatcher.cpp:2418-2434)
+        query, key, value = query.float(), key.float(), value.float()
+        if attn_bias is not None and attn_bias.dtype == torch.float64:
+            attn_bias = attn_bias.float()
+    bias = _additive_bias(attn_bias, query)
+    out, lse = sdpa_forward(query, key, value, attn_bias=bias, is_causal=is_causal, scale=scale, need_lse=True)
+    if in_dtype == torch.float64:
+        out = out.double()
+    zero = _zero_scalar(_device_index(query))
+    return out, lse, None, None, L, S, zero, zero, None
+
+
+# ----------------------------------------------------------------------------
+# kernel-level custom op (signature of upstream's nki_kernels op)
+# ----------------------------------------------------------------------------
+
+_LIB_DEF = torch.library.Library("b200_sdpa", "DEF")
+_LIB_DEF.define(
+    "fwd(Tensor q, Tensor k, Tensor v, bool is_causal, float dropout_p, float? scale, bool training, "
+    "int? seed, Tensor(a!)? lse, *, Tensor? kv_lens=None) -> Tensor"
+)
+
+
+def _fwd_cuda(q, k, v, is_causal, dropout_p, scale, training, seed, lse, *, kv_lens=None):
+    _validate(q, k, v, None, dropout_p, False, False)
+    B, Hq, L, _ = q.shape
+    buf = None
+    if training:
+        if lse is not None and lse.dtype == torch.float32 and tuple(lse.shape) == (B, Hq, L) and lse.is_cuda:
+            buf = lse  # written in place: no copy as upstream's lse.copy_() needs
+    out, got = sdpa_forward(q, k, v, is_causal=is_causal, scale=scale, kv_lens=kv_lens, need_lse=training, lse=buf)
+    if training and lse is not None and buf is None:
+        lse.copy_(got.reshape(lse.shape))
+    return out
+
+
+def _fwd_meta(q, k, v, is_causal, dropout_p, scale, training, seed, lse, *, kv_lens=None):
+    return alloc_like_query(q, (q.shape[0], q.shape[1], q.shape[2], v.shape[3]))
+
+
+_LIB_IMPL = torch.library.Library("b200_sdpa", "IMPL")
+_LIB_IMPL.impl("fwd", _fwd_cuda, "CUDA")
+_LIB_IMPL.impl("fwd", _fwd_meta, "Meta")
+
+
+def scaled_dot_product_attention_kernel(
+    q, k, v, is_causal=False, dropout_p=0.0, scale=None, training=False, seed=None, lse=None, kv_lens=None
+):
+    """Same call shape as upstream's ``scaled_dot_product_attention_kernel``
+    (``nki_kernels/scaled_dot_product_attention.py:44-86``): returns the attention
+    output; with ``training=True`` the fp32 log-sum-exp is written into ``lse``."""
+    return torch.ops.b200_sdpa.fwd(q, k, v, is_causal, dropout_p, scale, training, seed, lse, kv_lens=kv_lens)
+
+
+# ----------------------------------------------------------------------------
+# registration with ATen
+# ----------------------------------------------------------------------------
+
+_ATEN_IMPL = None
+_ROUTING = None
+_SDP_OVERRIDEABLE = 4  # at::SDPBackend::overrideable
+
+
+def register_aten_override() -> None:
+    """Register the CUDA kernel of the overrideable fused-attention op (upstream does the
+    same for its device key at import, ``python_ops/__init__.py:86-95``)."""
+    global _ATEN_IMPL
+    if _ATEN_IMPL is not None:
+        return
+    lib = torch.library.Library("aten", "IMPL")
+    lib.impl("_scaled_dot_product_fused_attention_overrideable", fused_attention_overrideable, "CUDA")
+    _ATEN_IMPL = lib
+
+
+def _supported_by_fused_path(query, key, value, attn_mask, dropout_p, is_causal) -> bool:
+    """Same decision shape as upstream's backend choice
+    (``torch_neuronx/csrc/aten/SdpBackendSelection.cpp:14-68``): 4-D, non-empty, and
+    additionally what this build serves (dtype, no dropout)."""
+    if query.dim() != 4 or key.dim() != 4 or value.dim() != 4:
+        return False
+    if query.numel() == 0 or key.numel() == 0 or value.numel() == 0:
+        return False
+    if query.dtype not in _DTYPE_CODE or dropout_p != 0.0:
+        return False
+    if attn_mask is not None and is_causal:
+        return False
+    return True
+
+
+def enable_sdpa_routing() -> None:
+    """Make plain ``F.scaled_dot_product_attention`` on CUDA tensors reach the fused
+    op by answering ``overrideable`` from ``aten::_fused_sdp_choice`` for inputs this
+    build serves (upstream: ``SdpBackendSelection.cpp:74``).  Opt-in because it
+    replaces torch's own CUDA backend choice process-wide."""
+    global _ROUTING
+    register_aten_override()
+    if _ROUTING is not None:
+        return
+    stock = torch.ops.aten._fused_sdp_choice.default
+
+    def choice(query, key, value, attn_mask=None, dropout_p=0.0, is_causal=False, *, scale=None, enable_gqa=False):
+        if _supported_by_fused_path(query, key, value, attn_mask, dropout_p, is_causal):
+            return _SDP_OVERRIDEABLE
+        return 0  # math
+
+    lib = torch.library.Library("aten", "IMPL")
+    lib.impl("_fused_sdp_choice", choice, "CUDA")
+    _ROUTING = (lib, stock)
+
+
+# ----------------------------------------------------------------------------
+# user-facing function
+# ----------------------------------------------------------------------------
+
+
+def scaled_dot_product_attention(
+    query, key, value, attn_mask=None, dropout_p=0.0, is_causal=False, scale=None, enable_gqa=False, *, kv_lens=None
+):
+    """Drop-in for ``torch.nn.functional.scaled_dot_product_attention`` on CUDA tensors.
+
+    ``enable_gqa`` is accepted for signature parity; grouped heads are detected from
+    the shapes (``Hq % Hkv == 0``) and never expanded in memory.  ``kv_lens``
+    (int32 ``(B,)``) is the one extension: valid keys per batch for right padding or
+    a ragged cache, instead of a dense mask."""
+    _validate(query, key, value, attn_mask, dropout_p, is_causal, False)
+    if not enable_gqa and query.shape[1] != key.shape[1]:
+        raise RuntimeError("SDPA: number of heads differ between query and key; pass enable_gqa=True")
+    if kv_lens is None:
+        return torch.ops.aten._scaled_dot_product_fused_attention_overrideable(
+            query, key, value, attn_mask, dropout_p, is_causal, False, scale=scale
+        )[0]
+    in_dtype = query.dtype
+    if in_dtype == torch.float64:
+        query, key, value = query.float(), key.float(), value.float()
+    bias = _additive_bias(attn_mask, query)
+    out, _ = sdpa_forward(query, key, value, attn_bias=bias, is_causal=is_causal, scale=scale, kv_lens=kv_lens,
+                          need_lse=False)
+    return out.double() if in_dtype == torch.float64 else out
