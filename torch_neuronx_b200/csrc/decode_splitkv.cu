@@ -238,7 +238,7 @@ __global__ void __launch_bounds__(D) decode_combine_kernel(const Problem p, cons
   T* out = reinterpret_cast<T*>(p.out);
   out[b * p.os[0] + h * p.os[1] + d * p.os[3]] = from_f32<T>(o * inv);
   if (p.lse != nullptr && d == 0)
-    p.lse[b * p.ls[0] + h * p.ls[1]] = (mx == -CUDART_INF_F) ? -CUDART_INF_F : (mx + log2f(lsum)) * kLn2;
+    p.lse[b * p.ls[0] + h * p.ls[1]] = (mx == -CUDART_INF_F) ? -CUDART_INF_F : fmaf(mx, kLn2, logf(lsum));
 }
 
 int pick_group(int group) { return group >= 8 ? 8 : group > 2 ? 4 : group; }

@@ -493,7 +493,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           tma_store_wait_all();
         }
         if (p.lse != nullptr && row_g < p.L) {
-          const float lse = l_run > 0.f ? (m_run * sl2 + lg2(l_run)) * kLn2 : -CUDART_INF_F;
+          // one rounding at the magnitude of the maximum: m*scale + ln(l)
+          const float lse = l_run > 0.f ? fmaf(m_run, p.scale, lg2(l_run) * kLn2) : -CUDART_INF_F;
           p.lse[b * p.ls[0] + h * p.ls[1] + row_g * p.ls[2]] = lse;
         }
       }

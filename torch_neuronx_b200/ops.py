@@ -31,6 +31,7 @@ import math
 from typing import Optional
 
 import torch
+import torch.overrides
 
 from . import _lib
 
@@ -410,25 +411,46 @@ def _supported_by_fused_path(query, key, value, attn_mask, dropout_p, is_causal)
     return True
 
 
+class _SdpaRouting(torch.overrides.TorchFunctionMode):
+    """Sends ``F.scaled_dot_product_attention`` calls this build serves to the fused op
+    and leaves every other call to torch."""
+
+    def __torch_function__(self, func, types, args=(), kwargs=None):
+        kwargs = kwargs or {}
+        if func is torch.nn.functional.scaled_dot_product_attention:
+            names = ("query", "key", "value", "attn_mask", "dropout_p", "is_causal", "scale", "enable_gqa")
+            bound = dict(zip(names, args))
+            bound.update(kwargs)
+            q, k, v = bound.get("query"), bound.get("key"), bound.get("value")
+            mask, drop = bound.get("attn_mask"), bound.get("dropout_p", 0.0)
+            causal = bound.get("is_causal", False)
+            if (
+                isinstance(q, torch.Tensor) and isinstance(k, torch.Tensor) and isinstance(v, torch.Tensor)
+                and q.is_cuda and k.is_cuda and v.is_cuda
+                and not (q.requires_grad or k.requires_grad or v.requires_grad)
+                and _supported_by_fused_path(q, k, v, mask, drop, causal)
+                and q.dtype == k.dtype == v.dtype
+                and (q.shape[1] == k.shape[1] or bound.get("enable_gqa", False))
+            ):
+                return torch.ops.aten._scaled_dot_product_fused_attention_overrideable(
+                    q, k, v, mask, drop, causal, False, scale=bound.get("scale"))[0]
+        return func(*args, **kwargs)
+
+
 def enable_sdpa_routing() -> None:
-    """Make plain ``F.scaled_dot_product_attention`` on CUDA tensors reach the fused
-    op by answering ``overrideable`` from ``aten::_fused_sdp_choice`` for inputs this
-    build serves (upstream: ``SdpBackendSelection.cpp:74``).  Opt-in because it
-    replaces torch's own CUDA backend choice process-wide."""
+    """Make plain ``F.scaled_dot_product_attention`` on CUDA tensors reach the fused op
+    for inputs this build serves -- the role upstream's ``_fused_sdp_choice`` stub plays
+    for its device (``SdpBackendSelection.cpp:14-75``).  For CUDA tensors torch asks its
+    built-in choice function directly and never the dispatcher, so the decision is made
+    one level up, in a torch-function mode installed for the rest of the process.
+    Opt-in; tensors that need autograd stay with torch (this build has no backward)."""
     global _ROUTING
     register_aten_override()
     if _ROUTING is not None:
         return
-    stock = torch.ops.aten._fused_sdp_choice.default
-
-    def choice(query, key, value, attn_mask=None, dropout_p=0.0, is_causal=False, *, scale=None, enable_gqa=False):
-        if _supported_by_fused_path(query, key, value, attn_mask, dropout_p, is_causal):
-            return _SDP_OVERRIDEABLE
-        return 0  # math
-
-    lib = torch.library.Library("aten", "IMPL")
-    lib.impl("_fused_sdp_choice", choice, "CUDA")
-    _ROUTING = (lib, stock)
+    mode = _SdpaRouting()
+    mode.__enter__()
+    _ROUTING = mode
 
 
 # ----------------------------------------------------------------------------
