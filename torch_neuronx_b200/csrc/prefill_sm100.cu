@@ -207,14 +207,17 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   if (warp == kProducerWarp) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
+      // A tile without visible keys never reads its Q: its shared-memory slot is
+      // used straight away to stage the all-zero output, so nothing may be in
+      // flight into it.
       uint32_t q_bytes = 0;
-      if (tg0.in_range) q_bytes += C::kTileBytes;
-      if (tg1.in_range) q_bytes += C::kTileBytes;
+      if (tg0.n_tiles > 0) q_bytes += C::kTileBytes;
+      if (tg1.n_tiles > 0) q_bytes += C::kTileBytes;
       const uint32_t qbar = smem_u32(&sync->q_full);
-      mbar_arrive_expect_tx(qbar, q_bytes);
+      if (q_bytes > 0) mbar_arrive_expect_tx(qbar, q_bytes);
       for (int t = 0; t < 2; ++t) {
         const TileGeom& tg = t == 0 ? tg0 : tg1;
-        if (!tg.in_range) continue;
+        if (tg.n_tiles == 0) continue;
         for (int bx = 0; bx < C::kBoxes; ++bx)
           tma_load_4d(q_smem[t] + bx * kBoxBytes, &tm_q, qbar, bx * 64, tg.row0, h, b);
       }
