@@ -201,6 +201,26 @@ int b200_sdpa_fwd(const B200SdpaParams* params, void* stream);
  */
 int b200_sdpa_decode(const B200SdpaParams* params, void* stream);
 
+/*
+ * Split-KV flash decoding for callers that cannot supply a workspace.  Same
+ * contract and results as b200_sdpa_decode(), except that `workspace` and
+ * `workspace_bytes` are ignored: the partial results go to a fixed scratch array
+ * that lives inside the library (B200_SDPA_STATIC_SCRATCH_BYTES on every GPU that
+ * loads it, until the process ends).  Meant for hosts that gave all device
+ * memory to their own pool at start-up, or that run where allocator calls are not
+ * allowed; the call itself performs no allocation of any kind.
+ *   - a request whose partials need more than the capacity (see `workspace_bytes`
+ *     of b200_sdpa_query_plan) returns B200_SDPA_ERR_TOO_LARGE and launches nothing;
+ *   - the first call on each device resolves the array's device address; make that
+ *     first call outside any stream capture;
+ *   - all calls share the one array, which keeps the previous call's contents; the
+ *     kernels overwrite every slot they read, but calls that overlap on the GPU
+ *     (different streams) race on it -- serialise them.
+ * This entry point has no counterpart in the upstream project.
+ */
+#define B200_SDPA_STATIC_SCRATCH_BYTES (16u << 20)
+int b200_sdpa_decode_static(const B200SdpaParams* params, void* stream);
+
 /* Enqueue one ring-step merge (see B200SdpaMergeParams). */
 int b200_sdpa_merge(const B200SdpaMergeParams* params, void* stream);
 

@@ -20,6 +20,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libb200_sdpa.so")
 
 ABI_VERSION = 1
+STATIC_SCRATCH_BYTES = 16 << 20  # B200_SDPA_STATIC_SCRATCH_BYTES
 
 # b200_sdpa_status
 OK = 0
@@ -127,6 +128,7 @@ EXPORTS = {
     "b200_sdpa_query_plan": (C.c_int, [C.POINTER(Params), C.POINTER(Plan)]),
     "b200_sdpa_fwd": (C.c_int, [C.POINTER(Params), C.c_void_p]),
     "b200_sdpa_decode": (C.c_int, [C.POINTER(Params), C.c_void_p]),
+    "b200_sdpa_decode_static": (C.c_int, [C.POINTER(Params), C.c_void_p]),
     "b200_sdpa_merge": (C.c_int, [C.POINTER(MergeParams), C.c_void_p]),
     "b200_sdpa_launch_count": (C.c_uint64, [C.c_int]),
     "b200_sdpa_reset_launch_counts": (None, []),

@@ -176,6 +176,16 @@ int b200_sdpa_decode(const B200SdpaParams* params, void* stream) {
                        reinterpret_cast<cudaStream_t>(stream));
 }
 
+int b200_sdpa_decode_static(const B200SdpaParams* params, void* stream) {
+  Problem p;
+  int rc = validate(params, &p);
+  if (rc != B200_SDPA_OK) return rc;
+  if (!decode_eligible(p, params->dtype)) return B200_SDPA_ERR_UNSUPPORTED;
+  rc = select_device(params->device);
+  if (rc != B200_SDPA_OK) return rc;
+  return launch_decode_static(p, params->dtype, params->kv_chunk, reinterpret_cast<cudaStream_t>(stream));
+}
+
 int b200_sdpa_merge(const B200SdpaMergeParams* m, void* stream) {
   if (m == nullptr) return B200_SDPA_ERR_NULL;
   if (m->struct_size != sizeof(B200SdpaMergeParams)) return B200_SDPA_ERR_STRUCT;

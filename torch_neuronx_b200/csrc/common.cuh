@@ -44,6 +44,7 @@ int launch_decode(const Problem& p, int dtype, int kv_chunk, void* workspace, ui
                   cudaStream_t stream);
 int plan_decode(const Problem& p, int dtype, int kv_chunk, B200SdpaPlan* plan);
 bool decode_eligible(const Problem& p, int dtype);
+int launch_decode_static(const Problem& p, int dtype, int kv_chunk, cudaStream_t stream);
 
 int launch_prefill(const Problem& p, int dtype, cudaStream_t stream);
 int plan_prefill(const Problem& p, int dtype, B200SdpaPlan* plan);

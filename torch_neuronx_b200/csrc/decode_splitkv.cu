@@ -17,6 +17,8 @@
 // with a key-length mask; dead rows (no visible key) give out = 0, lse = -inf.
 #include "common.cuh"
 
+#include <mutex>
+
 namespace b200 {
 
 namespace {
@@ -348,5 +350,60 @@ int launch_decode(const Problem& p, int dtype, int kv_chunk, void* workspace, ui
     default: return B200_SDPA_ERR_DTYPE;
   }
 }
+
+// ---------------------------------------------------------------------------
+// Decode with built-in scratch.
+//
+// Some hosts cannot give this library a workspace at call time: a serving
+// process that handed all device memory to its own pool when it started (so a
+// later cudaMalloc fails or is forbidden), or code on a path where allocator
+// calls are not permitted at all.  For them the partials of the split-KV
+// kernel live in the fixed array below instead of caller-provided memory.
+// Every GPU that loads the library carries the array until the process exits,
+// which is why it is kept modest; requests whose partials do not fit are
+// rejected, never truncated.
+//
+// The array's name is only a host-side handle.  Its device address is looked
+// up once per device with cudaGetSymbolAddress(), with that device current, the
+// first time the entry point is used on the device -- so the first call per
+// device should be made outside any stream capture.  All calls share the array
+// and it keeps whatever the previous call left: the kernels write every slot
+// they later read, so nothing has to be cleared, but two calls that overlap on
+// the GPU (different streams) would race on it.
+// ---------------------------------------------------------------------------
+constexpr unsigned long long kStaticScratchBytes = B200_SDPA_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_decode_scratch[kStaticScratchBytes];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_scratch_mutex;
+void* g_scratch_ptr[kMaxDevices] = {};
+}  // namespace
+
+int launch_decode_static(const Problem& p, int dtype, int kv_chunk, cudaStream_t stream) {
+  if (!decode_eligible(p, dtype)) return B200_SDPA_ERR_UNSUPPORTED;
+  const DecodeGeom gm = geometry(p, kv_chunk);
+  if (gm.ws_bytes > kStaticScratchBytes) return B200_SDPA_ERR_TOO_LARGE;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    cudaGetLastError();
+    return B200_SDPA_ERR_CUDA;
+  }
+  void* ptr = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    if (g_scratch_ptr[dev] == nullptr) {
+      void* found = nullptr;
+      if (cudaGetSymbolAddress(&found, g_decode_scratch) != cudaSuccess || found == nullptr) {
+        cudaGetLastError();
+        return B200_SDPA_ERR_CUDA;
+      }
+      g_scratch_ptr[dev] = found;
+    }
+    ptr = g_scratch_ptr[dev];
+  }
+  return launch_decode(p, dtype, kv_chunk, ptr, kStaticScratchBytes, stream);
+}
+
 
 }  // namespace b200
