@@ -406,6 +406,10 @@ def run_ours(args, rank, local_rank, world):
         extra["fp32_config1"] = {"workload": "fp32 [2,8,512,64] causal (configuration 1)", "ms": fms,
                                  "path": T.ops.last_plan.get("path")}
 
+    ring = None
+    if world > 1 and not args.no_extra:
+        ring = run_ring(T, dist, dev, rank, world, peaks)
+
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu:
         threads = os.cpu_count() or 1
@@ -429,10 +433,50 @@ def run_ours(args, rank, local_rank, world):
             "roofline": roofline, "e2e": e2e, "cpu_baseline": cpu_baseline, "clocks": clk.summary(),
             "gpu_launches": launches, "extra": extra,
         }
+        if ring is not None:
+            line["extra"]["ring_long_context"] = ring
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def run_ring(T, dist, dev, rank, world, peaks):
+    """Configuration 5: one causal 131072-token sequence, bf16 q [1,64,S,128], k/v [1,8,S,128],
+    sequence-sharded over the ranks (zigzag placement), K/V blocks rotated with NCCL
+    send/recv while the previous block is being computed."""
+    S, Hq, Hkv, D = 131072, 64, 8, 128
+    n_local = S // world
+    g = torch.Generator(device=dev).manual_seed(4000 + rank)
+    q = torch.randn(1, Hq, n_local, D, generator=g, device=dev, dtype=torch.bfloat16)
+    k = torch.randn(1, Hkv, n_local, D, generator=g, device=dev, dtype=torch.bfloat16)
+    v = torch.randn(1, Hkv, n_local, D, generator=g, device=dev, dtype=torch.bfloat16)
+    scale = 1.0 / math.sqrt(D)
+
+    def step():
+        return T.ring_attention(q, k, v, is_causal=True, scale=scale, layout="zigzag")
+
+    step()
+    torch.cuda.synchronize()
+    T.check_device_status()
+    dist.barrier()
+    iters = 2
+    ms = time_steps(step, iters)
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    flops = 4.0 * D * Hq * (S * (S + 1) // 2)
+    tf = flops / (t.item() * 1e-3) / 1e12
+    block_bytes = 2 * n_local * Hkv * D * 2
+    return {
+        "workload": f"long-context causal GQA prefill bf16 q[1,64,131072,128] kv[1,8,131072,128] over {world} GPUs "
+                    "(configuration 5), zigzag ring, K/V rotated un-expanded over NCCL send/recv",
+        "value": tf, "unit": "TFLOP/s", "per_gpu_tflops": tf / world, "ms": t.item(), "iters": iters,
+        "ring_bytes_per_step_per_gpu": block_bytes, "ring_steps": world - 1,
+        "roofline": {"bound": "tensor", "achieved": tf / world, "peak": peaks["bf16_tflops_sustained"],
+                     "unit": "TFLOP/s", "frac": tf / world / peaks["bf16_tflops_sustained"],
+                     "peak_kind": f"bf16_tflops_sustained of {peaks['source']}",
+                     "link_time_ms_per_step": block_bytes / 770e9 * 1e3},
+    }
 
 
 def main():
