@@ -70,6 +70,22 @@ struct Sync {
   int abort_flag;
 };
 
+// Optional phase timing (development builds only: -DB200_PHASE_TIMING).  One thread
+// per role adds the cycles it spent in each phase to a global table.
+#ifdef B200_PHASE_TIMING
+__device__ unsigned long long g_phase[32];
+#define PHASE_DECL long long ph_t0 = clock64(), ph_t1
+#define PHASE_ADD(slot, cond)                                                         \
+  do {                                                                                \
+    ph_t1 = clock64();                                                                \
+    if (cond) atomicAdd(&g_phase[slot], static_cast<unsigned long long>(ph_t1 - ph_t0)); \
+    ph_t0 = ph_t1;                                                                    \
+  } while (0)
+#else
+#define PHASE_DECL
+#define PHASE_ADD(slot, cond)
+#endif
+
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -80,6 +96,53 @@ __device__ __forceinline__ float lg2(float x) {
   asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// 2^x on the FMA pipe: round x to the nearest integer n with the 1.5*2^23 trick,
+// evaluate a degree-3 minimax polynomial of 2^f on f = x - n in [-0.5, 0.5]
+// (max relative error 7.5e-5, far below the 16-bit rounding of P) and add n to the
+// exponent field.  x is clamped at -126 so the exponent never wraps; the result for
+// such x is ~1e-38 instead of 0, so this form is only used on tiles without masked
+// columns (a masked column must contribute exactly 0).
+__device__ __forceinline__ float exp2_poly(float x) {
+  x = fmaxf(x, -126.f);
+  const float magic = 12582912.f;
+  const float t = x + magic;
+  const float f = x - (t - magic);
+  float p = fmaf(5.517166285e-02f, f, 2.426111217e-01f);
+  p = fmaf(p, f, 6.932609866e-01f);
+  p = fmaf(p, f, 9.999280736e-01f);
+  return __uint_as_float(__float_as_uint(p) + (__float_as_uint(t) << 23));
+}
+
+#ifndef B200_POLY_OF_8
+#define B200_POLY_OF_8 0   // of every 8 consecutive probabilities, how many use exp2_poly
+                           // (measured: the softmax is issue-bound, not MUFU-bound, so 0 is fastest)
+#endif
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+// packed fp32 pairs (one instruction for two lanes of arithmetic)
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+
 template <bool BF16> __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   uint32_t r;
   if (BF16) {
@@ -254,18 +317,23 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       const uint32_t o_tmem[2] = {tmem_base + 256u, tmem_base + 256u + D};
       bool alive = n_iter > 0;
 
-      auto issue_qk = [&](int t, uint32_t kv_addr) {
+      // descriptors: fixed fields once, then only the 16-byte-unit start address moves
+      const uint64_t q_desc[2] = {smem_desc_sw128(q_smem[0], 16, 1024), smem_desc_sw128(q_smem[1], 16, 1024)};
+      const uint64_t kv_desc_k = smem_desc_sw128(kv_smem, 16, 1024);          // K tile as K-major B operand
+      const uint64_t kv_desc_v = smem_desc_sw128(kv_smem, kBoxBytes, 1024);   // V tile as MN-major B operand
+      auto issue_qk = [&](int t, uint32_t stage) {
+        const uint64_t kd = kv_desc_k + static_cast<uint64_t>(stage * (C::kTileBytes >> 4));
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * kBoxBytes + (kk & 3) * 32;
-          mma_ss(s_tmem[t], smem_desc_sw128(q_smem[t] + off, 16, 1024), smem_desc_sw128(kv_addr + off, 16, 1024),
-                 idesc_qk, kk > 0 ? 1u : 0u);
+          const uint64_t off = static_cast<uint64_t>(((kk >> 2) * kBoxBytes + (kk & 3) * 32) >> 4);
+          mma_ss(s_tmem[t], q_desc[t] + off, kd + off, idesc_qk, kk > 0 ? 1u : 0u);
         }
       };
-      auto issue_pv = [&](int t, uint32_t kv_addr, bool accumulate) {
+      auto issue_pv = [&](int t, uint32_t stage, bool accumulate) {
+        const uint64_t vd = kv_desc_v + static_cast<uint64_t>(stage * (C::kTileBytes >> 4));
 #pragma unroll
         for (int kk = 0; kk < kBlockN / 16; ++kk) {
-          mma_ts(o_tmem[t], s_tmem[t] + kk * 8, smem_desc_sw128(kv_addr + kk * 2048, kBoxBytes, 1024), idesc_pv,
+          mma_ts(o_tmem[t], s_tmem[t] + kk * 8, vd + static_cast<uint64_t>(kk * (2048 >> 4)), idesc_pv,
                  (accumulate || kk > 0) ? 1u : 0u);
         }
       };
@@ -276,7 +344,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         if (!ok) report(p.status, 2, item, stage);
         return ok;
       };
-      auto stage_addr = [&](int item) { return kv_smem + (item % C::kStages) * C::kTileBytes; };
+      auto stage_addr = [&](int item) { return static_cast<uint32_t>(item % C::kStages); };
       auto empty_bar = [&](int item) { return smem_u32(&sync->kv_empty[item % C::kStages]); };
 
       if (alive) {
@@ -296,13 +364,16 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
         mma_commit(empty_bar(0));
       }
+      PHASE_DECL;
       for (int j = 0; j < n_iter && alive; ++j) {
         const int item_v = 2 * j + 1, item_kn = 2 * j + 2;
         const bool has_next = j + 1 < n_iter;
         const bool act0 = j < tg0.n_tiles, act1 = j < tg1.n_tiles;
         const bool nxt0 = j + 1 < tg0.n_tiles, nxt1 = j + 1 < tg1.n_tiles;
+        PHASE_ADD(22, true);                        // 22: loop overhead
         alive = wait_full(item_v);
         if (!alive) break;
+        PHASE_ADD(16, true);                        // 16: waiting for V(j)
         if (act0) {
           alive = wait_clocked(smem_u32(&sync->p_ready[0]), j & 1, abort_flag, wait_limit);
           if (!alive) {
@@ -310,6 +381,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             break;
           }
           tc_fence_after_sync();
+          PHASE_ADD(17, true);                      // 17: waiting for P0(j)
           issue_pv(0, stage_addr(item_v), j > 0);
         }
         if (has_next) {
@@ -323,6 +395,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         } else if (act0) {
           mma_commit(smem_u32(&sync->o_done[0]));
         }
+        PHASE_ADD(18, true);                        // 18: issue PV0 + (wait K) + QK0
         if (act1) {
           alive = wait_clocked(smem_u32(&sync->p_ready[1]), j & 1, abort_flag, wait_limit);
           if (!alive) {
@@ -330,6 +403,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             break;
           }
           tc_fence_after_sync();
+          PHASE_ADD(19, true);                      // 19: waiting for P1(j)
           issue_pv(1, stage_addr(item_v), j > 0);
         }
         mma_commit(empty_bar(item_v));
@@ -340,6 +414,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           mma_commit(smem_u32(&sync->o_done[1]));
         }
         if (has_next) mma_commit(empty_bar(item_kn));
+        PHASE_ADD(20, true);                        // 20: issue PV1 + QK1
+#ifdef B200_PHASE_TIMING
+        atomicAdd(&g_phase[31], 1ull);
+#endif
       }
       if (*abort_flag != 0) {
         // let whatever was issued retire before tensor memory is released
@@ -369,8 +447,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     float m_run = -CUDART_INF_F, l_run = 0.f;
     bool alive = true;
 
+    PHASE_DECL;
     if (tg.in_range) {
       for (int j = 0; j < tg.n_tiles; ++j) {
+        PHASE_ADD(8 + (j == 0 ? 0 : 1), r == 0);   // 8: prologue until the first wait, 9: arrive -> next wait
         bool ok = wait_clocked(smem_u32(&sync->s_full[t]), j & 1, abort_flag, wait_limit);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) {
@@ -379,25 +459,40 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           break;
         }
         tc_fence_after_sync();
+        PHASE_ADD(0, r == 0);                       // 0: waiting for S
         const int col0 = j * kBlockN;
         const bool need_mask = col0 + kBlockN > tg.min_lim;
 
-        // pass 1: row maximum of the raw scores
-        float mx = -CUDART_INF_F;
+        // S row -> registers in two halves; the second half is in flight while the
+        // maximum of the first is taken
+        uint32_t sv[kBlockN];
+        tmem_ld_32x32(s_addr, reinterpret_cast<uint32_t(&)[32]>(sv[0]));
+        tmem_ld_32x32(s_addr + 32, reinterpret_cast<uint32_t(&)[32]>(sv[32]));
+        tmem_ld_wait();
+        tmem_ld_32x32(s_addr + 64, reinterpret_cast<uint32_t(&)[32]>(sv[64]));
+        tmem_ld_32x32(s_addr + 96, reinterpret_cast<uint32_t(&)[32]>(sv[96]));
+        float mxa = -CUDART_INF_F, mxb = -CUDART_INF_F;
+        if (need_mask) {
 #pragma unroll
-        for (int c = 0; c < kBlockN / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32(s_addr + c * 32, v);
-          tmem_ld_wait();
-          if (need_mask) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              mx = fmaxf(mx, (col0 + c * 32 + i < lim) ? __uint_as_float(v[i]) : -CUDART_INF_F);
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
-          }
+          for (int i = 0; i < 64; ++i) sv[i] = (col0 + i < lim) ? sv[i] : 0xff800000u;  // -inf
         }
+#pragma unroll
+        for (int i = 0; i < 64; i += 4) {
+          mxa = max3(mxa, __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]));
+          mxb = max3(mxb, __uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3]));
+        }
+        tmem_ld_wait();
+        PHASE_ADD(1, r == 0);                       // 1: S TMEM -> registers (+ first half max)
+        if (need_mask) {
+#pragma unroll
+          for (int i = 64; i < kBlockN; ++i) sv[i] = (col0 + i < lim) ? sv[i] : 0xff800000u;
+        }
+#pragma unroll
+        for (int i = 64; i < kBlockN; i += 4) {
+          mxa = max3(mxa, __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]));
+          mxb = max3(mxb, __uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3]));
+        }
+        const float mx = fmaxf(mxa, mxb);
         const float m_new = fmaxf(m_run, mx);
         const bool grow = (m_new - m_run) * sl2 > kRescaleThreshold;  // false for NaN (-inf - -inf)
         float alpha = 1.f;
@@ -410,45 +505,59 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           // raise the reference maximum: O_t *= alpha (PV(j-1) has retired: its
           // completion is ordered before s_full(j))
 #pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t v[32];
-            tmem_ld_32x32(o_addr + c * 32, v);
+          for (int c = 0; c < D / 16; ++c) {
+            uint32_t v[16];
+            tmem_ld_32x16(o_addr + c * 16, v);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-            tmem_st_32x32(o_addr + c * 32, v);
+            for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+            tmem_st_32x16(o_addr + c * 16, v);
           }
           tmem_st_wait();
         }
         const float nms = (m_run == -CUDART_INF_F) ? 0.f : -m_run * sl2;
+        PHASE_ADD(2, r == 0);                       // 2: mask, max, vote, (rescale)
 
-        // pass 2: probabilities, row sum, P -> TMEM (over the first 64 columns of S)
-        float sum = 0.f;
+        // probabilities, row sum (four chains), P -> TMEM over the first 64 columns of S.
+        // On tiles without masked columns a fixed share of the exponentials is
+        // evaluated on the FMA pipe so that the 16 MUFU lanes of the SM stop being the
+        // only limiter.
+        uint64_t sum2[2] = {0ull, 0ull};           // two packed accumulators = four chains
+        const uint64_t sl2_2 = f2_pack(sl2, sl2), nms_2 = f2_pack(nms, nms);
 #pragma unroll
         for (int c = 0; c < kBlockN / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32(s_addr + c * 32, v);
-          tmem_ld_wait();
           uint32_t pk[16];
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            float s0 = __uint_as_float(v[i]), s1 = __uint_as_float(v[i + 1]);
-            if (need_mask) {
-              s0 = (col0 + c * 32 + i < lim) ? s0 : -CUDART_INF_F;
-              s1 = (col0 + c * 32 + i + 1 < lim) ? s1 : -CUDART_INF_F;
-            }
-            const float p0 = ex2(fmaf(s0, sl2, nms));
-            const float p1 = ex2(fmaf(s1, sl2, nms));
-            sum += p0 + p1;
+            float x0, x1;
+            f2_unpack(f2_fma(f2_pack(__uint_as_float(sv[c * 32 + i]), __uint_as_float(sv[c * 32 + i + 1])), sl2_2, nms_2),
+                      x0, x1);
+            const bool poly0 = B200_POLY_OF_8 > 0 && !need_mask && (i & 7) < B200_POLY_OF_8;
+            const bool poly1 = B200_POLY_OF_8 > 0 && !need_mask && ((i + 1) & 7) < B200_POLY_OF_8;
+            const float p0 = poly0 ? exp2_poly(x0) : ex2(x0);
+            const float p1 = poly1 ? exp2_poly(x1) : ex2(x1);
+            sum2[(i >> 1) & 1] = f2_add(sum2[(i >> 1) & 1], f2_pack(p0, p1));
             pk[i >> 1] = pack2<BF16>(p0, p1);
           }
           tmem_st_32x16(s_addr + c * 16, pk);
         }
+        float sum4[4];
+        f2_unpack(sum2[0], sum4[0], sum4[1]);
+        f2_unpack(sum2[1], sum4[2], sum4[3]);
+        const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
         l_run += sum;
+        PHASE_ADD(3, r == 0);                       // 3: exp, sum, pack, st issue
         tmem_st_wait();
         tc_fence_before_sync();
         mbar_arrive(smem_u32(&sync->p_ready[t]));
+        PHASE_ADD(4, r == 0);                       // 4: st wait + arrive
+        if (r == 0) {
+#ifdef B200_PHASE_TIMING
+          atomicAdd(&g_phase[15], 1ull);            // tile iterations counted
+#endif
+        }
       }
+      PHASE_ADD(9, false);
 
       // ------------------------------------------------------------- epilogue
       if (alive && tg.n_tiles > 0) {
@@ -495,6 +604,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           tma_store_commit();
           tma_store_wait_all();
         }
+        PHASE_ADD(10, r == 0);                      // 10: epilogue (wait O, scale, stage, store)
         if (p.lse != nullptr && row_g < p.L) {
           // one rounding at the magnitude of the maximum: m*scale + ln(l)
           const float lse = l_run > 0.f ? fmaf(m_run, p.scale, lg2(l_run) * kLn2) : -CUDART_INF_F;
@@ -607,6 +717,17 @@ int launch_variant(const Problem& p, cudaStream_t stream) {
 }
 
 }  // namespace
+
+#ifdef B200_PHASE_TIMING
+extern "C" int b200_debug_read_phases(unsigned long long* host32, int reset) {
+  if (cudaMemcpyFromSymbol(host32, g_phase, sizeof(unsigned long long) * 32) != cudaSuccess) return 1;
+  if (reset) {
+    unsigned long long z[32] = {};
+    if (cudaMemcpyToSymbol(g_phase, z, sizeof(z)) != cudaSuccess) return 1;
+  }
+  return 0;
+}
+#endif
 
 bool prefill_eligible(const Problem& p, int dtype, bool* alignment_only_failure) {
   if (alignment_only_failure) *alignment_only_failure = false;
