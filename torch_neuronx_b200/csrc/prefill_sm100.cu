@@ -29,6 +29,7 @@
 #include "ptx_sm100.cuh"
 
 #include <mutex>
+#include <type_traits>
 
 namespace b200 {
 
@@ -62,7 +63,7 @@ struct Sync {
   uint64_t kv_full[8];
   uint64_t kv_empty[8];
   uint64_t s_full[2];
-  uint64_t p_ready[2];
+  uint64_t p_ready[2][2];  // [tile][half of P]
   uint64_t o_done[2];
   uint64_t o_staged[2];
   uint64_t drain;
@@ -72,6 +73,17 @@ struct Sync {
 
 // Optional phase timing (development builds only: -DB200_PHASE_TIMING).  One thread
 // per role adds the cycles it spent in each phase to a global table.
+#ifdef B200_TRACE
+// Development only: time stamps of one CTA.  g_trace[role][step][event]
+__device__ long long g_trace[6][64][4];
+#define TRACE(role, step, ev)                                                        \
+  do {                                                                               \
+    if (blockIdx.x == 0 && (step) < 64) g_trace[role][step][ev] = clock64();         \
+  } while (0)
+#else
+#define TRACE(role, step, ev)
+#endif
+
 #ifdef B200_PHASE_TIMING
 __device__ unsigned long long g_phase[32];
 #define PHASE_DECL long long ph_t0 = clock64(), ph_t1
@@ -96,28 +108,6 @@ __device__ __forceinline__ float lg2(float x) {
   asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// 2^x on the FMA pipe: round x to the nearest integer n with the 1.5*2^23 trick,
-// evaluate a degree-3 minimax polynomial of 2^f on f = x - n in [-0.5, 0.5]
-// (max relative error 7.5e-5, far below the 16-bit rounding of P) and add n to the
-// exponent field.  x is clamped at -126 so the exponent never wraps; the result for
-// such x is ~1e-38 instead of 0, so this form is only used on tiles without masked
-// columns (a masked column must contribute exactly 0).
-__device__ __forceinline__ float exp2_poly(float x) {
-  x = fmaxf(x, -126.f);
-  const float magic = 12582912.f;
-  const float t = x + magic;
-  const float f = x - (t - magic);
-  float p = fmaf(5.517166285e-02f, f, 2.426111217e-01f);
-  p = fmaf(p, f, 6.932609866e-01f);
-  p = fmaf(p, f, 9.999280736e-01f);
-  return __uint_as_float(__float_as_uint(p) + (__float_as_uint(t) << 23));
-}
-
-#ifndef B200_POLY_OF_8
-#define B200_POLY_OF_8 0   // of every 8 consecutive probabilities, how many use exp2_poly
-                           // (measured: the softmax is issue-bound, not MUFU-bound, so 0 is fastest)
-#endif
-
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float r;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
@@ -244,7 +234,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(smem_u32(&sync->s_full[t]), 1);
-      mbar_init(smem_u32(&sync->p_ready[t]), kBlockM);
+      mbar_init(smem_u32(&sync->p_ready[t][0]), kBlockM);
+      mbar_init(smem_u32(&sync->p_ready[t][1]), kBlockM);
       mbar_init(smem_u32(&sync->o_done[t]), 1);
       mbar_init(smem_u32(&sync->o_staged[t]), kBlockM);
     }
@@ -310,118 +301,134 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     __syncwarp();
   } else if (warp == kMmaWarp) {
     // -------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    // The whole warp runs the control flow (waits included) so that addresses and
+    // descriptors stay in the uniform datapath; one elected lane issues.  The tile
+    // index is a compile-time constant everywhere for the same reason.
+    {
       constexpr uint32_t idesc_qk = make_idesc(BF16, false, kBlockM, kBlockN);
       constexpr uint32_t idesc_pv = make_idesc(BF16, true, kBlockM, D);
-      const uint32_t s_tmem[2] = {tmem_base, tmem_base + 128u};
-      const uint32_t o_tmem[2] = {tmem_base + 256u, tmem_base + 256u + D};
       bool alive = n_iter > 0;
 
       // descriptors: fixed fields once, then only the 16-byte-unit start address moves
-      const uint64_t q_desc[2] = {smem_desc_sw128(q_smem[0], 16, 1024), smem_desc_sw128(q_smem[1], 16, 1024)};
+      const uint64_t q_desc0 = smem_desc_sw128(q_smem[0], 16, 1024), q_desc1 = smem_desc_sw128(q_smem[1], 16, 1024);
       const uint64_t kv_desc_k = smem_desc_sw128(kv_smem, 16, 1024);          // K tile as K-major B operand
       const uint64_t kv_desc_v = smem_desc_sw128(kv_smem, kBoxBytes, 1024);   // V tile as MN-major B operand
-      auto issue_qk = [&](int t, uint32_t stage) {
+      auto issue_qk = [&](auto tile_const, uint32_t stage) {
+        constexpr int t = decltype(tile_const)::value;
+        const uint64_t qd = t == 0 ? q_desc0 : q_desc1;
         const uint64_t kd = kv_desc_k + static_cast<uint64_t>(stage * (C::kTileBytes >> 4));
+        const uint32_t d_addr = tmem_base + static_cast<uint32_t>(t * 128);
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint64_t off = static_cast<uint64_t>(((kk >> 2) * kBoxBytes + (kk & 3) * 32) >> 4);
-          mma_ss(s_tmem[t], q_desc[t] + off, kd + off, idesc_qk, kk > 0 ? 1u : 0u);
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint64_t off = static_cast<uint64_t>(((kk >> 2) * kBoxBytes + (kk & 3) * 32) >> 4);
+            mma_ss(d_addr, qd + off, kd + off, idesc_qk, kk > 0 ? 1u : 0u);
+          }
         }
       };
-      auto issue_pv = [&](int t, uint32_t stage, bool accumulate) {
-        const uint64_t vd = kv_desc_v + static_cast<uint64_t>(stage * (C::kTileBytes >> 4));
+      // O_t (+)= P_t[:, half*64 .. half*64+63] . V[half*64 .. , :]   (four K-steps of 16 keys)
+      auto issue_pv_half = [&](auto tile_const, uint32_t stage, int half, bool accumulate) {
+        constexpr int t = decltype(tile_const)::value;
+        const uint64_t vd = kv_desc_v + static_cast<uint64_t>(stage * (C::kTileBytes >> 4) + half * 4 * (2048 >> 4));
+        const uint32_t d_addr = tmem_base + static_cast<uint32_t>(256 + t * D);
+        const uint32_t a_addr = tmem_base + static_cast<uint32_t>(t * 128 + half * 32);
+        const uint32_t acc0 = (accumulate || half > 0) ? 1u : 0u;
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < kBlockN / 16; ++kk) {
-          mma_ts(o_tmem[t], s_tmem[t] + kk * 8, vd + static_cast<uint64_t>(kk * (2048 >> 4)), idesc_pv,
-                 (accumulate || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < 4; ++kk) {
+            mma_ts(d_addr, a_addr + static_cast<uint32_t>(kk * 8), vd + static_cast<uint64_t>(kk * (2048 >> 4)), idesc_pv,
+                   kk > 0 ? 1u : acc0);
+          }
         }
+      };
+      auto commit = [&](uint32_t bar) {
+        if (elect_one()) mma_commit(bar);
       };
       auto wait_full = [&](int item) -> bool {
         const int stage = item % C::kStages;
         const uint32_t round = static_cast<uint32_t>(item / C::kStages);
         const bool ok = wait_clocked(smem_u32(&sync->kv_full[stage]), round & 1u, abort_flag, wait_limit);
-        if (!ok) report(p.status, 2, item, stage);
+        if (!ok && lane == 0) report(p.status, 2, item, stage);
         return ok;
       };
       auto stage_addr = [&](int item) { return static_cast<uint32_t>(item % C::kStages); };
       auto empty_bar = [&](int item) { return smem_u32(&sync->kv_empty[item % C::kStages]); };
+      const std::integral_constant<int, 0> T0{};
+      const std::integral_constant<int, 1> T1{};
 
       if (alive) {
         alive = wait_clocked(smem_u32(&sync->q_full), 0, abort_flag, wait_limit);
-        if (!alive) report(p.status, 2, -1, 0);
+        if (!alive && lane == 0) report(p.status, 2, -1, 0);
       }
       if (alive) alive = wait_full(0);
       if (alive) {
         tc_fence_after_sync();
         if (tg0.n_tiles > 0) {
-          issue_qk(0, stage_addr(0));
-          mma_commit(smem_u32(&sync->s_full[0]));
+          issue_qk(T0, stage_addr(0));
+          commit(smem_u32(&sync->s_full[0]));
         }
         if (tg1.n_tiles > 0) {
-          issue_qk(1, stage_addr(0));
-          mma_commit(smem_u32(&sync->s_full[1]));
+          issue_qk(T1, stage_addr(0));
+          commit(smem_u32(&sync->s_full[1]));
         }
-        mma_commit(empty_bar(0));
+        commit(empty_bar(0));
       }
       PHASE_DECL;
       for (int j = 0; j < n_iter && alive; ++j) {
         const int item_v = 2 * j + 1, item_kn = 2 * j + 2;
         const bool has_next = j + 1 < n_iter;
-        const bool act0 = j < tg0.n_tiles, act1 = j < tg1.n_tiles;
-        const bool nxt0 = j + 1 < tg0.n_tiles, nxt1 = j + 1 < tg1.n_tiles;
-        PHASE_ADD(22, true);                        // 22: loop overhead
+        PHASE_ADD(22, lane == 0);                   // 22: loop overhead
         alive = wait_full(item_v);
         if (!alive) break;
-        PHASE_ADD(16, true);                        // 16: waiting for V(j)
-        if (act0) {
-          alive = wait_clocked(smem_u32(&sync->p_ready[0]), j & 1, abort_flag, wait_limit);
-          if (!alive) {
-            report(p.status, 3, j, 0);
-            break;
+        PHASE_ADD(16, lane == 0);                   // 16: waiting for V(j)
+        // one tile: P_t(j) V(j) in two halves as the halves of P arrive, then Q_t K(j+1)^T
+        auto serve = [&](auto tile_const) {
+          constexpr int t = decltype(tile_const)::value;
+          const int nt = t == 0 ? tg0.n_tiles : tg1.n_tiles;
+          if (j < nt) {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              alive = wait_clocked(smem_u32(&sync->p_ready[t][half]), j & 1, abort_flag, wait_limit);
+              if (!alive) {
+                if (lane == 0) report(p.status, 3, j, t);
+                return;
+              }
+              tc_fence_after_sync();
+              if (half == 0) {
+                if (lane == 0) TRACE(2 + t, j, 1);
+                PHASE_ADD(17 + 2 * t, lane == 0);   // 17 / 19: waiting for the first half of P_t(j)
+              }
+              issue_pv_half(tile_const, stage_addr(item_v), half, j > 0);
+            }
+            if (lane == 0) TRACE(2 + t, j, 2);
           }
-          tc_fence_after_sync();
-          PHASE_ADD(17, true);                      // 17: waiting for P0(j)
-          issue_pv(0, stage_addr(item_v), j > 0);
-        }
-        if (has_next) {
-          alive = wait_full(item_kn);
-          if (!alive) break;
-          tc_fence_after_sync();
-        }
-        if (nxt0) {
-          issue_qk(0, stage_addr(item_kn));
-          mma_commit(smem_u32(&sync->s_full[0]));
-        } else if (act0) {
-          mma_commit(smem_u32(&sync->o_done[0]));
-        }
-        PHASE_ADD(18, true);                        // 18: issue PV0 + (wait K) + QK0
-        if (act1) {
-          alive = wait_clocked(smem_u32(&sync->p_ready[1]), j & 1, abort_flag, wait_limit);
-          if (!alive) {
-            report(p.status, 3, j, 1);
-            break;
+          if (t == 0 && has_next) {
+            alive = wait_full(item_kn);
+            if (!alive) return;
+            tc_fence_after_sync();
           }
-          tc_fence_after_sync();
-          PHASE_ADD(19, true);                      // 19: waiting for P1(j)
-          issue_pv(1, stage_addr(item_v), j > 0);
-        }
-        mma_commit(empty_bar(item_v));
-        if (nxt1) {
-          issue_qk(1, stage_addr(item_kn));
-          mma_commit(smem_u32(&sync->s_full[1]));
-        } else if (act1) {
-          mma_commit(smem_u32(&sync->o_done[1]));
-        }
-        if (has_next) mma_commit(empty_bar(item_kn));
-        PHASE_ADD(20, true);                        // 20: issue PV1 + QK1
+          if (j + 1 < nt) {
+            issue_qk(tile_const, stage_addr(item_kn));
+            commit(smem_u32(&sync->s_full[t]));
+          } else if (j < nt) {
+            commit(smem_u32(&sync->o_done[t]));
+          }
+          if (lane == 0) TRACE(2 + t, j, 3);
+          PHASE_ADD(18 + 2 * t, lane == 0);         // 18 / 20: issue P V + (wait K) + Q K^T
+        };
+        serve(T0);
+        if (!alive) break;
+        serve(T1);
+        if (!alive) break;
+        commit(empty_bar(item_v));
+        if (has_next) commit(empty_bar(item_kn));
 #ifdef B200_PHASE_TIMING
-        atomicAdd(&g_phase[31], 1ull);
+        if (lane == 0) atomicAdd(&g_phase[31], 1ull);
 #endif
       }
       if (*abort_flag != 0) {
         // let whatever was issued retire before tensor memory is released
-        mma_commit(smem_u32(&sync->drain));
+        commit(smem_u32(&sync->drain));
         long long t0 = clock64();
         while (!mbar_try_wait(smem_u32(&sync->drain), 0) && clock64() - t0 < wait_limit) {
         }
@@ -459,6 +466,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           break;
         }
         tc_fence_after_sync();
+        if (r == 0) TRACE(t, j, 0);
+        if (r == 96) TRACE(4 + t, j, 0);
         PHASE_ADD(0, r == 0);                       // 0: waiting for S
         const int col0 = j * kBlockN;
         const bool need_mask = col0 + kBlockN > tg.min_lim;
@@ -516,6 +525,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           tmem_st_wait();
         }
         const float nms = (m_run == -CUDART_INF_F) ? 0.f : -m_run * sl2;
+        if (r == 0) TRACE(t, j, 1);
         PHASE_ADD(2, r == 0);                       // 2: mask, max, vote, (rescale)
 
         // probabilities, row sum (four chains), P -> TMEM over the first 64 columns of S.
@@ -532,14 +542,20 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             float x0, x1;
             f2_unpack(f2_fma(f2_pack(__uint_as_float(sv[c * 32 + i]), __uint_as_float(sv[c * 32 + i + 1])), sl2_2, nms_2),
                       x0, x1);
-            const bool poly0 = B200_POLY_OF_8 > 0 && !need_mask && (i & 7) < B200_POLY_OF_8;
-            const bool poly1 = B200_POLY_OF_8 > 0 && !need_mask && ((i + 1) & 7) < B200_POLY_OF_8;
-            const float p0 = poly0 ? exp2_poly(x0) : ex2(x0);
-            const float p1 = poly1 ? exp2_poly(x1) : ex2(x1);
+            const float p0 = ex2(x0);
+            const float p1 = ex2(x1);
             sum2[(i >> 1) & 1] = f2_add(sum2[(i >> 1) & 1], f2_pack(p0, p1));
             pk[i >> 1] = pack2<BF16>(p0, p1);
           }
           tmem_st_32x16(s_addr + c * 16, pk);
+          if (c == 1) {
+            // first 64 keys of P are in TMEM: let P V start on them while the rest is computed
+            tmem_st_wait();
+            tc_fence_before_sync();
+            mbar_arrive(smem_u32(&sync->p_ready[t][0]));
+            if (r == 0) TRACE(t, j, 3);
+            if (r == 96) TRACE(4 + t, j, 3);
+          }
         }
         float sum4[4];
         f2_unpack(sum2[0], sum4[0], sum4[1]);
@@ -549,7 +565,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         PHASE_ADD(3, r == 0);                       // 3: exp, sum, pack, st issue
         tmem_st_wait();
         tc_fence_before_sync();
-        mbar_arrive(smem_u32(&sync->p_ready[t]));
+        mbar_arrive(smem_u32(&sync->p_ready[t][1]));
+        if (r == 0) TRACE(t, j, 2);
+        if (r == 96) TRACE(4 + t, j, 2);
         PHASE_ADD(4, r == 0);                       // 4: st wait + arrive
         if (r == 0) {
 #ifdef B200_PHASE_TIMING
@@ -717,6 +735,12 @@ int launch_variant(const Problem& p, cudaStream_t stream) {
 }
 
 }  // namespace
+
+#ifdef B200_TRACE
+extern "C" int b200_debug_read_trace(long long* host) {
+  return cudaMemcpyFromSymbol(host, g_trace, sizeof(long long) * 6 * 64 * 4) != cudaSuccess;
+}
+#endif
 
 #ifdef B200_PHASE_TIMING
 extern "C" int b200_debug_read_phases(unsigned long long* host32, int reset) {
