@@ -44,6 +44,9 @@ int launch_decode(const Problem& p, int dtype, int kv_chunk, void* workspace, ui
                   cudaStream_t stream);
 int plan_decode(const Problem& p, int dtype, int kv_chunk, B200SdpaPlan* plan);
 bool decode_eligible(const Problem& p, int dtype);
+bool decode_mma_eligible(const Problem& p, int dtype);
+int launch_decode_partial_mma(const Problem& p, int dtype, int chunk, int nsplit, float* part_o, float* part_ml,
+                              cudaStream_t stream);
 int launch_decode_static(const Problem& p, int dtype, int kv_chunk, cudaStream_t stream);
 
 int launch_prefill(const Problem& p, int dtype, cudaStream_t stream);

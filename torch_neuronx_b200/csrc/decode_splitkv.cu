@@ -17,6 +17,7 @@
 // with a key-length mask; dead rows (no visible key) give out = 0, lse = -inf.
 #include "common.cuh"
 
+#include <cstdlib>
 #include <mutex>
 
 namespace b200 {
@@ -254,7 +255,7 @@ int default_chunk(const Problem& p) {
   int64_t chunk = (p.S + want - 1) / want;
   chunk = (chunk + 127) / 128 * 128;
   if (chunk < 256) chunk = 256;
-  if (chunk > 1024) chunk = 1024;
+  if (chunk > 2048) chunk = 2048;
   return static_cast<int>(chunk);
 }
 
@@ -274,16 +275,31 @@ DecodeGeom geometry(const Problem& p, int kv_chunk) {
   return gm;
 }
 
+template <typename T, int D>
+int launch_combine(const Problem& p, const DecodeGeom& gm, float* po, float* pml, cudaStream_t stream) {
+  decode_combine_kernel<T, D><<<p.B * p.Hq, D, 0, stream>>>(p, gm.chunk, gm.nsplit, po, pml);
+  if (cudaGetLastError() != cudaSuccess) return B200_SDPA_ERR_CUDA;
+  count_launch(KID_COMBINE);
+  return B200_SDPA_OK;
+}
+
 template <typename T, int D, int G>
 int launch_pg(const Problem& p, const DecodeGeom& gm, float* po, float* pml, cudaStream_t stream) {
   dim3 grid(gm.nsplit, p.Hkv * gm.nsub, p.B);
   decode_partial_kernel<T, D, G><<<grid, kThreads, 0, stream>>>(p, gm.chunk, gm.nsplit, po, pml);
   if (cudaGetLastError() != cudaSuccess) return B200_SDPA_ERR_CUDA;
   count_launch(KID_DECODE);
-  decode_combine_kernel<T, D><<<p.B * p.Hq, D, 0, stream>>>(p, gm.chunk, gm.nsplit, po, pml);
-  if (cudaGetLastError() != cudaSuccess) return B200_SDPA_ERR_CUDA;
-  count_launch(KID_COMBINE);
-  return B200_SDPA_OK;
+  return launch_combine<T, D>(p, gm, po, pml, stream);
+}
+
+// 16-bit caches go to the tensor-core partial kernel (decode_mma.cu); the CUDA-core
+// kernel above keeps fp32 caches and can be forced with B200_SDPA_DECODE_SIMT=1.
+bool use_mma_partial(const Problem& p, int dtype) {
+  static const bool forced_simt = [] {
+    const char* e = getenv("B200_SDPA_DECODE_SIMT");
+    return e != nullptr && e[0] == '1';
+  }();
+  return !forced_simt && decode_mma_eligible(p, dtype);
 }
 
 template <typename T, int D>
@@ -339,6 +355,14 @@ int launch_decode(const Problem& p, int dtype, int kv_chunk, void* workspace, ui
   float* po = reinterpret_cast<float*>(workspace);
   float* pml = po + static_cast<uint64_t>(p.B) * p.Hq * gm.nsplit * p.Dv;
   const bool d128 = p.E == 128;
+  if (use_mma_partial(p, dtype)) {
+    const int rc = launch_decode_partial_mma(p, dtype, gm.chunk, gm.nsplit, po, pml, stream);
+    if (rc != B200_SDPA_OK) return rc;
+    if (dtype == B200_SDPA_BF16)
+      return d128 ? launch_combine<__nv_bfloat16, 128>(p, gm, po, pml, stream)
+                  : launch_combine<__nv_bfloat16, 64>(p, gm, po, pml, stream);
+    return d128 ? launch_combine<__half, 128>(p, gm, po, pml, stream) : launch_combine<__half, 64>(p, gm, po, pml, stream);
+  }
   switch (dtype) {
     case B200_SDPA_F32:
       return d128 ? launch_g<float, 128>(p, gm, po, pml, stream) : launch_g<float, 64>(p, gm, po, pml, stream);
