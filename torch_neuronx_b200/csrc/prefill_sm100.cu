@@ -200,7 +200,7 @@ template <int D, bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o, const Problem p,
-               const int n_qblk, const long long wait_limit) {
+               const int n_qblk, const int pair_heads, const long long wait_limit) {
   using C = Cfg<D>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -211,16 +211,24 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
 
-  // work item: longest (latest) query blocks first, heads of one kv group adjacent
-  const int per_blk = p.Hq * p.B;
+  // Work item: longest (latest) query blocks first, heads of one kv group adjacent.
+  // Two layouts of the CTA's two 128-row tiles:
+  //   pair_heads == 0: rows [256 q, +128) and [256 q + 128, +128) of one query head;
+  //   pair_heads == 1: the same 128 rows of two query heads that share a kv head
+  //     (even group size) -- both tiles then see exactly the same keys, so under a
+  //     causal mask neither waits for the other's extra diagonal tile.
+  const int heads_per_cta = pair_heads ? 2 : 1;
+  const int per_blk = (p.Hq / heads_per_cta) * p.B;
   const int qblk = n_qblk - 1 - static_cast<int>(blockIdx.x / per_blk);
   const int rem = static_cast<int>(blockIdx.x % per_blk);
-  const int h = rem % p.Hq;
-  const int b = rem / p.Hq;
-  const int hk = h / p.group;
+  const int hq0 = (rem % (p.Hq / heads_per_cta)) * heads_per_cta;
+  const int b = rem / (p.Hq / heads_per_cta);
+  const int hk = hq0 / p.group;
+  const int head_of_tile[2] = {hq0, pair_heads ? hq0 + 1 : hq0};
   const int kv_limit = valid_keys(p, b);
-  const TileGeom tg0 = tile_geometry(p, qblk * kRowsPerCta, kv_limit);
-  const TileGeom tg1 = tile_geometry(p, qblk * kRowsPerCta + kBlockM, kv_limit);
+  const int rows_per_cta = pair_heads ? kBlockM : kRowsPerCta;
+  const TileGeom tg0 = tile_geometry(p, qblk * rows_per_cta, kv_limit);
+  const TileGeom tg1 = tile_geometry(p, qblk * rows_per_cta + (pair_heads ? 0 : kBlockM), kv_limit);
   const int n_iter = tg0.n_tiles > tg1.n_tiles ? tg0.n_tiles : tg1.n_tiles;
 
   const uint32_t q_smem[2] = {tiles, tiles + C::kTileBytes};
@@ -273,7 +281,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const TileGeom& tg = t == 0 ? tg0 : tg1;
         if (tg.n_tiles == 0) continue;
         for (int bx = 0; bx < C::kBoxes; ++bx)
-          tma_load_4d(q_smem[t] + bx * kBoxBytes, &tm_q, qbar, bx * 64, tg.row0, h, b);
+          tma_load_4d(q_smem[t] + bx * kBoxBytes, &tm_q, qbar, bx * 64, tg.row0, head_of_tile[t], b);
       }
       bool alive = true;
       for (int item = 0; item < 2 * n_iter && alive; ++item) {
@@ -618,7 +626,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         fence_proxy_async_smem();
         mbar_arrive(smem_u32(&sync->o_staged[t]));
         if (r == 0 && wait_clocked(smem_u32(&sync->o_staged[t]), 0, abort_flag, wait_limit)) {
-          for (int bx = 0; bx < C::kBoxes; ++bx) tma_store_4d(&tm_o, q_smem[t] + bx * kBoxBytes, bx * 64, tg.row0, h, b);
+          for (int bx = 0; bx < C::kBoxes; ++bx) tma_store_4d(&tm_o, q_smem[t] + bx * kBoxBytes, bx * 64, tg.row0, head_of_tile[t], b);
           tma_store_commit();
           tma_store_wait_all();
         }
@@ -626,7 +634,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         if (p.lse != nullptr && row_g < p.L) {
           // one rounding at the magnitude of the maximum: m*scale + ln(l)
           const float lse = l_run > 0.f ? fmaf(m_run, p.scale, lg2(l_run) * kLn2) : -CUDART_INF_F;
-          p.lse[b * p.ls[0] + h * p.ls[1] + row_g * p.ls[2]] = lse;
+          p.lse[b * p.ls[0] + head_of_tile[t] * p.ls[1] + row_g * p.ls[2]] = lse;
         }
       }
     }
@@ -704,6 +712,10 @@ long long wait_limit_cycles() {
   return v;
 }
 
+// Pair two query heads of one kv head per CTA when the group size allows it and the
+// mask is causal (that is where the row-block layout leaves one tile idle at the end).
+int pair_heads_mode(const Problem& p) { return (p.causal && p.group % 2 == 0) ? 1 : 0; }
+
 template <int D, bool BF16>
 int launch_variant(const Problem& p, cudaStream_t stream) {
   using C = Cfg<D>;
@@ -725,10 +737,13 @@ int launch_variant(const Problem& p, cudaStream_t stream) {
       return B200_SDPA_ERR_CUDA;
     }
   }
-  const int n_qblk = (p.L + kRowsPerCta - 1) / kRowsPerCta;
-  const long long grid = static_cast<long long>(n_qblk) * p.Hq * p.B;
+  const int pair_heads = pair_heads_mode(p);
+  const int rows = pair_heads ? kBlockM : kRowsPerCta;
+  const int n_qblk = (p.L + rows - 1) / rows;
+  const long long grid = static_cast<long long>(n_qblk) * (p.Hq / (pair_heads ? 2 : 1)) * p.B;
   if (grid <= 0 || grid > 0x7fffffffLL) return B200_SDPA_ERR_UNSUPPORTED;
-  kern<<<static_cast<unsigned>(grid), kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, to, p, n_qblk, wait_limit_cycles());
+  kern<<<static_cast<unsigned>(grid), kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, to, p, n_qblk, pair_heads,
+                                                                         wait_limit_cycles());
   if (cudaGetLastError() != cudaSuccess) return B200_SDPA_ERR_CUDA;
   count_launch(KID_PREFILL);
   return B200_SDPA_OK;
@@ -768,11 +783,13 @@ bool prefill_eligible(const Problem& p, int dtype, bool* alignment_only_failure)
 
 int plan_prefill(const Problem& p, int dtype, B200SdpaPlan* plan) {
   if (!prefill_eligible(p, dtype, nullptr)) return B200_SDPA_ERR_UNSUPPORTED;
-  const int n_qblk = (p.L + kRowsPerCta - 1) / kRowsPerCta;
-  const long long grid = static_cast<long long>(n_qblk) * p.Hq * p.B;
+  const int pair_heads = pair_heads_mode(p);
+  const int rows = pair_heads ? kBlockM : kRowsPerCta;
+  const int n_qblk = (p.L + rows - 1) / rows;
+  const long long grid = static_cast<long long>(n_qblk) * (p.Hq / (pair_heads ? 2 : 1)) * p.B;
   if (grid > 0x7fffffffLL) return B200_SDPA_ERR_UNSUPPORTED;
   plan->path = B200_SDPA_PATH_PREFILL;
-  plan->block_m = kRowsPerCta;
+  plan->block_m = rows;
   plan->block_n = kBlockN;
   plan->grid_x = static_cast<int32_t>(grid);
   plan->grid_y = plan->grid_z = 1;
