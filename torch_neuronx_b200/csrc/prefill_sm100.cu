@@ -122,11 +122,6 @@ __device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
 __device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
   asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
 }
-__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
-  uint64_t r;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
-  return r;
-}
 __device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
   uint64_t r;
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
@@ -536,22 +531,17 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         if (r == 0) TRACE(t, j, 1);
         PHASE_ADD(2, r == 0);                       // 2: mask, max, vote, (rescale)
 
-        // probabilities, row sum (four chains), P -> TMEM over the first 64 columns of S.
-        // On tiles without masked columns a fixed share of the exponentials is
-        // evaluated on the FMA pipe so that the 16 MUFU lanes of the SM stop being the
-        // only limiter.
+        // probabilities, row sum (two packed accumulators), P -> TMEM over the first 64
+        // columns of S.  (Measured alternatives that lost: a polynomial exp2 on the FMA
+        // pipe for part of the row, and ex2 on packed 16-bit pairs.)
         uint64_t sum2[2] = {0ull, 0ull};           // two packed accumulators = four chains
-        const uint64_t sl2_2 = f2_pack(sl2, sl2), nms_2 = f2_pack(nms, nms);
 #pragma unroll
         for (int c = 0; c < kBlockN / 32; ++c) {
           uint32_t pk[16];
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            float x0, x1;
-            f2_unpack(f2_fma(f2_pack(__uint_as_float(sv[c * 32 + i]), __uint_as_float(sv[c * 32 + i + 1])), sl2_2, nms_2),
-                      x0, x1);
-            const float p0 = ex2(x0);
-            const float p1 = ex2(x1);
+            const float p0 = ex2(fmaf(__uint_as_float(sv[c * 32 + i]), sl2, nms));
+            const float p1 = ex2(fmaf(__uint_as_float(sv[c * 32 + i + 1]), sl2, nms));
             sum2[(i >> 1) & 1] = f2_add(sum2[(i >> 1) & 1], f2_pack(p0, p1));
             pk[i >> 1] = pack2<BF16>(p0, p1);
           }
