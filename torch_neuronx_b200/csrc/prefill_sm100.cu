@@ -205,6 +205,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) TRACE(0, 63, 0);
 
   // Work item: longest (latest) query blocks first, heads of one kv group adjacent.
   // Two layouts of the CTA's two 128-row tiles:
@@ -226,60 +227,72 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   const TileGeom tg1 = tile_geometry(p, qblk * rows_per_cta + (pair_heads ? 0 : kBlockM), kv_limit);
   const int n_iter = tg0.n_tiles > tg1.n_tiles ? tg0.n_tiles : tg1.n_tiles;
 
+
   const uint32_t q_smem[2] = {tiles, tiles + C::kTileBytes};
   const uint32_t kv_smem = tiles + kTilesPerCta * C::kTileBytes;
 
-  if (tid == 0) {
+  // Set-up is spread over the roles so that the first copies are in flight while
+  // barriers are initialised and tensor memory is allocated: the producer lane owns
+  // the barriers of its own copies and starts Q and the first ring slots at once.
+  int items_issued = 0;   // (producer lane) ring items already issued
+  if (warp == kProducerWarp && lane == 0) {
     mbar_init(smem_u32(&sync->q_full), 1);
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(smem_u32(&sync->kv_full[s]), 1);
       mbar_init(smem_u32(&sync->kv_empty[s]), 1);
     }
+    mbar_fence_init();
+    // A tile without visible keys never reads its Q: its shared-memory slot is used
+    // straight away to stage the all-zero output, so nothing may be in flight into it.
+    uint32_t q_bytes = 0;
+    if (tg0.n_tiles > 0) q_bytes += C::kTileBytes;
+    if (tg1.n_tiles > 0) q_bytes += C::kTileBytes;
+    const uint32_t qbar = smem_u32(&sync->q_full);
+    if (q_bytes > 0) mbar_arrive_expect_tx(qbar, q_bytes);
     for (int t = 0; t < 2; ++t) {
-      mbar_init(smem_u32(&sync->s_full[t]), 1);
-      mbar_init(smem_u32(&sync->p_ready[t][0]), kBlockM);
-      mbar_init(smem_u32(&sync->p_ready[t][1]), kBlockM);
-      mbar_init(smem_u32(&sync->o_done[t]), 1);
-      mbar_init(smem_u32(&sync->o_staged[t]), kBlockM);
+      const TileGeom& tg = t == 0 ? tg0 : tg1;
+      if (tg.n_tiles == 0) continue;
+      for (int bx = 0; bx < C::kBoxes; ++bx)
+        tma_load_4d(q_smem[t] + bx * kBoxBytes, &tm_q, qbar, bx * 64, tg.row0, head_of_tile[t], b);
     }
-    mbar_init(smem_u32(&sync->drain), 1);
-    sync->abort_flag = 0;
+    for (; items_issued < 2 * n_iter && items_issued < C::kStages; ++items_issued) {
+      const uint32_t bar = smem_u32(&sync->kv_full[items_issued]);
+      mbar_arrive_expect_tx(bar, C::kTileBytes);
+      const CUtensorMap* map = (items_issued & 1) ? &tm_v : &tm_k;
+      for (int bx = 0; bx < C::kBoxes; ++bx)
+        tma_load_4d(kv_smem + items_issued * C::kTileBytes + bx * kBoxBytes, map, bar, bx * 64,
+                    (items_issued >> 1) * kBlockN, hk, b);
+    }
+    prefetch_tmap(&tm_o);
+  }
+  if (tid < 2) {
+    const int t = tid;
+    mbar_init(smem_u32(&sync->s_full[t]), 1);
+    mbar_init(smem_u32(&sync->p_ready[t][0]), kBlockM);
+    mbar_init(smem_u32(&sync->p_ready[t][1]), kBlockM);
+    mbar_init(smem_u32(&sync->o_done[t]), 1);
+    mbar_init(smem_u32(&sync->o_staged[t]), kBlockM);
+    if (t == 0) {
+      mbar_init(smem_u32(&sync->drain), 1);
+      sync->abort_flag = 0;
+    }
     mbar_fence_init();
   }
   if (warp == kMmaWarp) {
     tmem_alloc(smem_u32(&sync->tmem_base), kTmemCols);
     tmem_relinquish();
   }
-  if (warp == kProducerWarp && lane == 0) {
-    prefetch_tmap(&tm_q);
-    prefetch_tmap(&tm_k);
-    prefetch_tmap(&tm_v);
-    prefetch_tmap(&tm_o);
-  }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = sync->tmem_base;
+  if (tid == 0) TRACE(0, 63, 1);
 
   if (warp == kProducerWarp) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      // A tile without visible keys never reads its Q: its shared-memory slot is
-      // used straight away to stage the all-zero output, so nothing may be in
-      // flight into it.
-      uint32_t q_bytes = 0;
-      if (tg0.n_tiles > 0) q_bytes += C::kTileBytes;
-      if (tg1.n_tiles > 0) q_bytes += C::kTileBytes;
-      const uint32_t qbar = smem_u32(&sync->q_full);
-      if (q_bytes > 0) mbar_arrive_expect_tx(qbar, q_bytes);
-      for (int t = 0; t < 2; ++t) {
-        const TileGeom& tg = t == 0 ? tg0 : tg1;
-        if (tg.n_tiles == 0) continue;
-        for (int bx = 0; bx < C::kBoxes; ++bx)
-          tma_load_4d(q_smem[t] + bx * kBoxBytes, &tm_q, qbar, bx * 64, tg.row0, head_of_tile[t], b);
-      }
       bool alive = true;
-      for (int item = 0; item < 2 * n_iter && alive; ++item) {
+      for (int item = items_issued; item < 2 * n_iter && alive; ++item) {
         const int j = item >> 1;
         const int stage = item % C::kStages;
         const uint32_t round = static_cast<uint32_t>(item / C::kStages);
@@ -576,6 +589,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       PHASE_ADD(9, false);
 
       // ------------------------------------------------------------- epilogue
+      if (r == 0) TRACE(t, 62, 0);
       if (alive && tg.n_tiles > 0) {
         bool ok = wait_clocked(smem_u32(&sync->o_done[t]), 0, abort_flag, wait_limit);
         ok = __all_sync(0xffffffffu, ok);
@@ -632,6 +646,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
   tc_fence_before_sync();
   __syncthreads();
+  if (tid == 0) TRACE(0, 63, 3);
   if (warp == kMmaWarp) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
