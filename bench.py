@@ -287,7 +287,8 @@ def run_ours(args, rank, local_rank, world):
     scale = 1.0 / math.sqrt(128)
 
     # ---------------- headline: configuration 3, inputs resident in HBM ----------------
-    q, k, v, lens = c3_inputs(2 + 1000 * rank, device=dev)
+    # every rank works on its own copy of the same seeded batch: identical work per GPU
+    q, k, v, lens = c3_inputs(2, device=dev)
     flops = c3_flops(lens.cpu())
     out = T.alloc_like_query(q, q.shape)
     lse = torch.empty(4, 32, 4096, dtype=torch.float32, device=dev)
@@ -329,7 +330,7 @@ def run_ours(args, rank, local_rank, world):
     # copies the output back to pinned host memory.  Copies and compute of consecutive steps
     # overlap (separate streams, two device buffer sets), as a serving loop would do it; the
     # timed region still contains every byte of every step.
-    qh, kh, vh, lh = c3_inputs(2 + 1000 * rank, pinned=True)
+    qh, kh, vh, lh = c3_inputs(2, pinned=True)
     oh = [torch.empty(4, 32, 4096, 128, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
     s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
     main = torch.cuda.current_stream(dev)
