@@ -1,4 +1,4 @@
-"""CPU oracle for the fused scaled-dot-product-attention forward.
+"""CPU oracle for the fused scaled-dot-product-attention forward and backward.
 
 TEST INFRASTRUCTURE ONLY.  Nothing in the product package may import this
 module; it exists so that the parity tests, the smoke check and the CPU leg of
@@ -6,9 +6,9 @@ the benchmark have an independent statement of what the CUDA path must
 produce.
 
 Parity status: PINNED.  ``tests/golden/`` holds outputs produced by the
-upstream file ``torch_neuronx/_sdpa_math.py`` (``compute_attention``) and
-``tests/test_oracle_golden.py`` requires this restatement to reproduce them
-bit for bit (fp32) on the same seeded inputs.
+upstream file ``torch_neuronx/_sdpa_math.py`` (``compute_attention`` and
+``compute_attention_backward``) and ``tests/test_oracle_golden.py`` requires
+this restatement to reproduce them bit for bit on the same seeded inputs.
 
 What is restated, and where it lives upstream:
 
@@ -18,6 +18,9 @@ What is restated, and where it lives upstream:
   (``:30-31``), row max with a guard for rows without any visible key
   (``:85-91``), ``lse = max + log(sum)``, probabilities rounded to the input
   dtype before the second matmul (``:94``).
+* ``torch_neuronx/_sdpa_math.py:98-176`` ``compute_attention_backward`` --
+  probabilities rebuilt from the saved log-sum-exp, ``dV = P^T dO``,
+  ``dP = dO V^T``, softmax Jacobian, ``dQ = dS K``, ``dK = dS^T Q``.
 * ``torch_neuronx/neuron_dynamo_backend/decompositions.py:2083-2128`` --
   how the op drives that function: grouped-query heads expanded with
   ``repeat_interleave`` (``:2088-2091``), default scale ``1/sqrt(E)``
@@ -235,3 +238,79 @@ def merge_partials(out_a, lse_a, out_b, lse_b):
     wb = torch.where(dead, 0.0, torch.exp(lse_b - torch.where(dead, 0.0, lse)))
     out = out_a.float() * wa.unsqueeze(-1) + out_b.float() * wb.unsqueeze(-1)
     return out, lse
+
+
+def attention_backward_core(
+    grad_out: torch.Tensor,
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    out: torch.Tensor,
+    lse: torch.Tensor,
+    bias: torch.Tensor | None,
+    scale: float,
+    causal: bool,
+):
+    """The backward arithmetic of ``compute_attention_backward`` at ``dropout_p == 0``
+    (``_sdpa_math.py:130-176``); k and v already carry as many heads as q.
+
+    Probabilities are rebuilt from the forward's log-sum-exp (rows whose lse is -inf
+    get zero probabilities), ``dV = P^T dO``, ``dP = dO V^T``, and the softmax
+    Jacobian is applied with the row term ``sum_j dP_j P_j + sum_d dO_d (out_d -
+    (P V)_d)`` -- which is ``sum_d dO_d out_d`` with the forward's own ``out``.
+    Returns ``(dq, dk, dv, dbias)`` in the input dtype; ``dbias`` is the gradient
+    of the logits, ``[B,H,L,S]`` without any reduction over broadcast bias
+    dimensions, or ``None`` when no bias took part (``:169``).
+    """
+    in_dtype = q.dtype
+    acc = accumulator_dtype(in_dtype)
+    g, qa, ka, va, oa = (t.to(acc) for t in (grad_out, q, k, v, out))
+    la = lse.to(acc)
+    if bias is not None and bias.numel() > 1:
+        bias = bias.to(acc)
+    else:
+        bias = None
+    scores = masked_logits(torch.matmul(qa, ka.transpose(-2, -1)) * scale, bias, causal)
+    dead = la == NEG_INF
+    probs = torch.exp(scores - torch.where(dead, 0.0, la).unsqueeze(-1))
+    probs = torch.where(dead.unsqueeze(-1), 0.0, probs)
+    dv = torch.matmul(probs.transpose(-2, -1), g)
+    dp = torch.matmul(g, va.transpose(-2, -1))
+    row = (dp * probs).sum(dim=-1, keepdim=True) + (g * (oa - torch.matmul(probs, va))).sum(dim=-1, keepdim=True)
+    dlogits = probs * (dp - row)
+    ds = dlogits * scale
+    dq = torch.matmul(ds, ka)
+    dk = torch.matmul(ds.transpose(-2, -1), qa)
+    dbias = dlogits.to(in_dtype) if bias is not None else None
+    return dq.to(in_dtype), dk.to(in_dtype), dv.to(in_dtype), dbias
+
+
+def sdpa_backward(
+    grad_out, q, k, v, out, lse, attn_mask=None, is_causal=False, scale=None, kv_lens=None,
+    compute_dtype: torch.dtype | None = None,
+):
+    """Backward of :func:`sdpa_forward` the way upstream drives it: grouped heads are
+    expanded before the math and the key/value gradients of a group are summed back
+    in the gradient dtype (``_prepare_backward_inputs`` / ``_reduce_gqa_gradients``,
+    ``neuron_dynamo_backend/decompositions.py:2535-2598``)."""
+    if compute_dtype is not None:
+        grad_out, q, k, v, out = (t.to(compute_dtype) for t in (grad_out, q, k, v, out))
+        if attn_mask is not None and attn_mask.dtype != torch.bool:
+            attn_mask = attn_mask.to(compute_dtype)
+    hq, hkv, n_k, e = q.shape[1], k.shape[1], k.shape[2], q.shape[3]
+    if scale is None:
+        scale = 1.0 / math.sqrt(e)
+    ke, ve = expand_kv_heads(q, k, v)
+    bias = additive_bias(attn_mask, q)
+    if kv_lens is not None:
+        pad = key_length_bias(kv_lens.cpu(), n_k, q.dtype)
+        bias = pad if bias is None else bias + pad
+    dq, dk, dv, dbias = attention_backward_core(grad_out, q, ke, ve, out, lse, bias, float(scale), bool(is_causal))
+    if attn_mask is None or attn_mask.dtype == torch.bool:
+        dbias = None
+    if hq != hkv:
+        g = hq // hkv
+        b_, _, s_, _ = dk.shape
+        dk = dk.view(b_, hkv, g, s_, dk.shape[-1]).sum(dim=2)
+        dv = dv.view(b_, hkv, g, s_, dv.shape[-1]).sum(dim=2)
+    return dq, dk, dv, dbias

@@ -31,3 +31,11 @@ def golden():
 
     path = os.path.join(ROOT, "tests", "golden", "sdpa_golden.pt")
     return torch.load(path, weights_only=False)["cases"]
+
+
+@pytest.fixture(scope="session")
+def golden_bwd():
+    import torch
+
+    path = os.path.join(ROOT, "tests", "golden", "sdpa_bwd_golden.pt")
+    return torch.load(path, weights_only=False)["cases"]

@@ -1,4 +1,4 @@
-"""Regenerate ``sdpa_golden.pt`` from the upstream CPU implementation.
+"""Regenerate ``sdpa_golden.pt`` and ``sdpa_bwd_golden.pt`` from the upstream CPU implementation.
 
 Run where the upstream checkout is available::
 
@@ -7,8 +7,8 @@ Run where the upstream checkout is available::
 The script loads the single upstream file ``torch_neuronx/_sdpa_math.py`` by
 path (it imports nothing but torch; the package itself needs a Trainium
 runtime and is never imported) and records ``compute_attention`` outputs for
-the cases below.  Inputs are always drawn from a seeded CPU generator in the
-order q, k, v[, mask].  Cases with a handful of elements store their inputs; the
+the cases below (``compute_attention_backward`` outputs for the backward file).  Inputs are always drawn from a seeded CPU generator in the
+order q, k, v[, mask][, grad_out].  Cases with a handful of elements store their inputs; the
 others store a checksum of the inputs, so that a torch build whose generator
 differs is noticed instead of silently changing the case.
 
@@ -23,6 +23,9 @@ Case families follow the upstream tests that pin this path:
   any visible key give exact zeros).
 * the first benchmark configuration: fp32 ``[2,8,512,64]``, seed 0, causal,
   scale 1/8 (output rows subsampled to keep the file small).
+* backward, ``tests/neuron_dynamo_backend/unit/test_decompositions.py:8700-8790``
+  -- the same small matrix with a seeded upstream gradient, and grouped heads
+  driven through expand / group-sum as ``decompositions.py:2535-2598`` does.
 """
 
 from __future__ import annotations
@@ -164,6 +167,84 @@ def main():
     torch.save(dict(meta=meta, cases=cases), os.path.join(HERE, "sdpa_golden.pt"))
     size = os.path.getsize(os.path.join(HERE, "sdpa_golden.pt"))
     print(f"wrote {len(cases)} cases, {size/1024:.0f} KiB")
+    backward_cases(mod)
+
+
+def drive_backward(mod, grad_out, q, k, v, mask, causal, scale):
+    """Forward then backward the way the upstream decompositions do: grouped heads
+    expanded first, key/value gradients of a group summed afterwards."""
+    hq, hkv = q.shape[1], k.shape[1]
+    ke, ve = k, v
+    if hq != hkv:
+        ke = k.repeat_interleave(hq // hkv, dim=1)
+        ve = v.repeat_interleave(hq // hkv, dim=1)
+    if mask is None:
+        bias = q.new_zeros((0,))
+    elif mask.dtype == torch.bool:
+        bias = torch.where(mask, 0.0, NEG_INF).to(q.dtype)
+    else:
+        bias = mask
+    none = q.new_zeros((0,))
+    out, lse = mod.compute_attention(q, ke, ve, bias, none, scale, causal, 0.0)
+    dq, dk, dv, dbias = mod.compute_attention_backward(grad_out, q, ke, ve, bias, none, out, lse,
+                                                       scale, causal, 0.0)
+    if hq != hkv:
+        b, _, s, _ = dk.shape
+        dk = dk.view(b, hkv, hq // hkv, s, dk.shape[-1]).sum(dim=2)
+        dv = dv.view(b, hkv, hq // hkv, s, dv.shape[-1]).sum(dim=2)
+    if mask is None or mask.dtype == torch.bool:
+        dbias = None
+    return out, lse, dq, dk, dv, dbias
+
+
+def backward_cases(mod):
+    cases = {}
+    for dtype in (torch.float32, torch.bfloat16):
+        for (lq, lk) in ((51, 51), (13, 51)):
+            for mask_kind in ("none", "float", "bool"):
+                for causal in (False, True):
+                    # the full matrix in one dtype per shape keeps the file small
+                    full_matrix = (dtype == torch.float32) == (lq == 51)
+                    if not full_matrix and not (mask_kind == "none" and causal):
+                        continue
+                    g = torch.Generator().manual_seed(0)
+                    q, k, v, mask = small_inputs(g, dtype, lq, lk, mask_kind)
+                    go = torch.randn(2, 2, lq, 48, generator=g).to(dtype)
+                    scale = 1.0 / math.sqrt(48)
+                    out, lse, dq, dk, dv, dbias = drive_backward(mod, go, q, k, v, mask, causal, scale)
+                    name = f"small_{str(dtype).split('.')[-1]}_{lq}x{lk}_{mask_kind}_{'causal' if causal else 'full'}"
+                    cases[name] = dict(seed=0, dtype=dtype, lq=lq, lk=lk, mask_kind=mask_kind, causal=causal,
+                                       scale=scale, dq=dq, dk=dk, dv=dv,
+                                       dbias_sum=None if dbias is None else dbias.double().sum().item(),
+                                       dbias_abs_sum=None if dbias is None else dbias.double().abs().sum().item(),
+                                       input_sum=input_checksum(q, k, v, go))
+    for (hq, hkv) in ((8, 2), (8, 1)):
+        for dtype in (torch.float32, torch.bfloat16):
+            g = torch.Generator().manual_seed(7)
+            q = torch.randn(1, hq, 40, 64, generator=g).to(dtype)
+            k = torch.randn(1, hkv, 77, 64, generator=g).to(dtype)
+            v = torch.randn(1, hkv, 77, 64, generator=g).to(dtype)
+            go = torch.randn(1, hq, 40, 64, generator=g).to(dtype)
+            out, lse, dq, dk, dv, _ = drive_backward(mod, go, q, k, v, None, True, 0.2)
+            cases[f"gqa_{hq}_{hkv}_{str(dtype).split('.')[-1]}"] = dict(
+                seed=7, dtype=dtype, hq=hq, hkv=hkv, causal=True, scale=0.2, dq=dq, dk=dk, dv=dv,
+                input_sum=input_checksum(q, k, v, go))
+    # rows without any visible key: their gradients are exact zeros
+    g = torch.Generator().manual_seed(0)
+    q = torch.rand(1, 4, 32, 32, generator=g) * 3
+    k = torch.rand(1, 4, 32, 32, generator=g) * 3
+    v = torch.rand(1, 4, 32, 32, generator=g) * 3
+    go = torch.randn(1, 4, 32, 32, generator=g)
+    mask = torch.ones(1, 1, 32, 32, dtype=torch.bool)
+    mask[..., :10, :] = False
+    mask[..., :, :10] = False
+    out, lse, dq, dk, dv, _ = drive_backward(mod, go, q, k, v, mask, False, 1.0 / math.sqrt(32))
+    cases["dead_rows_leftpad10"] = dict(q=q, k=k, v=v, mask=mask, grad_out=go, causal=False,
+                                        scale=1.0 / math.sqrt(32), dq=dq, dk=dk, dv=dv)
+    meta = dict(torch=torch.__version__, source="torch_neuronx/_sdpa_math.py::compute_attention_backward")
+    path = os.path.join(HERE, "sdpa_bwd_golden.pt")
+    torch.save(dict(meta=meta, cases=cases), path)
+    print(f"wrote {len(cases)} backward cases, {os.path.getsize(path)/1024:.0f} KiB")
 
 
 if __name__ == "__main__":

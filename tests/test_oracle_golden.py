@@ -13,7 +13,7 @@ import pytest
 import torch
 
 from oracle import sdpa_oracle as O
-from tests.golden_cases import expected_for, inputs_for
+from tests.golden_cases import backward_inputs_for, expected_for, inputs_for
 
 
 def _names():
@@ -114,3 +114,59 @@ def test_offsets_reproduce_a_block_of_a_longer_sequence():
     o, l = O.merge_partials(o1, l1, o2, l2)
     assert (o - full_o[:, :, 64:]).abs().max().item() < 2e-6
     assert (l - full_l[:, :, 64:]).abs().max().item() < 2e-6
+
+
+def _bwd_names():
+    import os
+
+    path = os.path.join(os.path.dirname(__file__), "golden", "sdpa_bwd_golden.pt")
+    return sorted(torch.load(path, weights_only=False)["cases"].keys())
+
+
+@pytest.mark.parametrize("name", _bwd_names())
+def test_oracle_backward_matches_upstream_bit_exact(golden_bwd, name):
+    case = golden_bwd[name]
+    q, k, v, mask, go = backward_inputs_for(name, case)
+    out, lse = O.sdpa_forward(q, k, v, attn_mask=mask, is_causal=case["causal"], scale=case["scale"])
+    dq, dk, dv, dbias = O.sdpa_backward(go, q, k, v, out, lse, attn_mask=mask, is_causal=case["causal"],
+                                        scale=case["scale"])
+    for got, want in ((dq, case["dq"]), (dk, case["dk"]), (dv, case["dv"])):
+        assert got.dtype == want.dtype and got.shape == want.shape
+        assert torch.equal(got, want), name
+    if case.get("dbias_sum") is not None:
+        assert dbias.double().sum().item() == case["dbias_sum"]
+        assert dbias.double().abs().sum().item() == case["dbias_abs_sum"]
+    else:
+        assert dbias is None
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("groups", [1, 4])
+def test_oracle_backward_against_autograd(causal, groups):
+    # upstream tests/neuron_dynamo_backend/unit/test_decompositions.py:8703 (backward formula vs autograd)
+    g = torch.Generator().manual_seed(11)
+    q = torch.randn(2, 4, 19, 16, generator=g, dtype=torch.float64, requires_grad=True)
+    k = torch.randn(2, 4 // groups, 23, 16, generator=g, dtype=torch.float64, requires_grad=True)
+    v = torch.randn(2, 4 // groups, 23, 16, generator=g, dtype=torch.float64, requires_grad=True)
+    bias = torch.randn(2, 4, 19, 23, generator=g, dtype=torch.float64, requires_grad=True)
+    go = torch.randn(2, 4, 19, 16, generator=g, dtype=torch.float64)
+    ke, ve = k.repeat_interleave(groups, 1), v.repeat_interleave(groups, 1)
+    s = q @ ke.transpose(-2, -1) / 4.0
+    if causal:
+        s = s.masked_fill(torch.ones(19, 23, dtype=torch.bool).triu(1), float("-inf"))
+    ref = torch.softmax(s + bias, -1) @ ve
+    ref.backward(go)
+    with torch.no_grad():
+        out, lse = O.sdpa_forward(q, k, v, attn_mask=bias, is_causal=causal)
+        dq, dk, dv, db = O.sdpa_backward(go, q, k, v, out, lse.double(), attn_mask=bias, is_causal=causal)
+    for got, want in ((dq, q.grad), (dk, k.grad), (dv, v.grad), (db, bias.grad)):
+        assert (got - want).abs().max().item() < 5e-6  # the forward keeps lse in fp32
+
+
+def test_oracle_backward_dead_rows_give_zero_gradients(golden_bwd):
+    case = golden_bwd["dead_rows_leftpad10"]
+    out, lse = O.sdpa_forward(case["q"], case["k"], case["v"], attn_mask=case["mask"], scale=case["scale"])
+    dq, dk, dv, _ = O.sdpa_backward(case["grad_out"], case["q"], case["k"], case["v"], out, lse,
+                                    attn_mask=case["mask"], scale=case["scale"])
+    assert torch.all(dq[..., :10, :] == 0) and torch.all(dk[..., :10, :] == 0) and torch.all(dv[..., :10, :] == 0)
+    assert torch.isfinite(dq).all() and torch.isfinite(dk).all() and torch.isfinite(dv).all()
