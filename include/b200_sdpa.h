@@ -1,6 +1,6 @@
 /*
  * b200_sdpa.h -- C ABI of the B200 (sm_100a) fused scaled-dot-product-attention
- * forward.
+ * forward (and its backward).
  *
  * This is the drop-in boundary for the one path this library accelerates.  The
  * upstream project reaches its device kernel through a Python/C++ kernel
@@ -167,6 +167,70 @@ typedef struct B200SdpaMergeParams {
   int32_t B, Hq, L, Dv;
 } B200SdpaMergeParams;
 
+/*
+ * Backward of one attention problem: given the upstream gradient `grad_out` and
+ * the forward's inputs, output and log-sum-exp,
+ *     P      = exp(scale * q.k^T + bias - lse)      (masked entries and rows with
+ *                                                    lse = -inf give 0)
+ *     grad_v = P^T grad_out                          summed over the heads of a group
+ *     dS     = P * (grad_out v^T - rowsum(grad_out * out))
+ *     grad_q = scale * dS k        grad_k = scale * dS^T q   (summed over the group)
+ *     grad_bias = dS               (optional, full (B,Hq,L,S), no broadcast reduction)
+ * Shapes, masks, offsets and `kv_lens` mean what they mean in B200SdpaParams; the
+ * gradients are written with the strides given, so they can take the layout of the
+ * tensors they belong to.  Arithmetic is fp32 whatever the storage dtype.
+ *
+ * Field semantics follow
+ *   torch_neuronx/_sdpa_math.py:98-176   (compute_attention_backward)
+ *   torch_neuronx/neuron_dynamo_backend/decompositions.py:2535-2598
+ *                                         (group expansion and gradient reduction)
+ *   torch_neuronx/csrc/core/dispatch/NeuronDispatcher.cpp:2523-2582
+ *                                         (gradients laid out like their inputs).
+ */
+typedef struct B200SdpaBwdParams {
+  uint32_t struct_size;    /* = sizeof(B200SdpaBwdParams)                              */
+  int32_t dtype;           /* dtype of q, k, v, out, grad_out and all gradients        */
+  int32_t device;
+  int32_t reserved;        /* 0                                                         */
+
+  const void* grad_out;    /* (B, Hq,  L, Dv)                                           */
+  const void* q;           /* (B, Hq,  L, E)                                            */
+  const void* k;           /* (B, Hkv, S, E)                                            */
+  const void* v;           /* (B, Hkv, S, Dv)                                           */
+  const void* out;         /* (B, Hq,  L, Dv) forward output                            */
+  const float* lse;        /* (B, Hq,  L) fp32 forward log-sum-exp                      */
+  void* grad_q;            /* (B, Hq,  L, E)                                            */
+  void* grad_k;            /* (B, Hkv, S, E)                                            */
+  void* grad_v;            /* (B, Hkv, S, Dv)                                           */
+  void* grad_bias;         /* optional (B, Hq, L, S) in dtype, or NULL                  */
+
+  int64_t grad_out_stride[4];
+  int64_t q_stride[4];
+  int64_t k_stride[4];
+  int64_t v_stride[4];
+  int64_t out_stride[4];
+  int64_t lse_stride[3];
+  int64_t grad_q_stride[4];
+  int64_t grad_k_stride[4];
+  int64_t grad_v_stride[4];
+  int64_t grad_bias_stride[4];
+
+  int32_t B, Hq, Hkv, L, S, E, Dv;
+  float scale;
+  int32_t is_causal;
+  int32_t bias_dtype;
+  int64_t q_offset;
+  int64_t k_offset;
+  const int32_t* kv_lens;
+  const void* bias;        /* the forward's additive bias, or NULL                      */
+  int64_t bias_stride[4];
+
+  void* workspace;         /* reserved for kernels that need scratch; the kernels in
+                              this build need none                                      */
+  uint64_t workspace_bytes;
+  int32_t* status;
+} B200SdpaBwdParams;
+
 /* ABI version of the loaded library (compare with B200_SDPA_ABI_VERSION). */
 int b200_sdpa_abi_version(void);
 
@@ -221,6 +285,16 @@ int b200_sdpa_decode(const B200SdpaParams* params, void* stream);
 #define B200_SDPA_STATIC_SCRATCH_BYTES (16u << 20)
 int b200_sdpa_decode_static(const B200SdpaParams* params, void* stream);
 
+/*
+ * Enqueue the attention backward on `stream`: one kernel for grad_q (and grad_bias)
+ * and one for grad_k / grad_v.  Head dims up to 256.
+ * Upstream counterpart: the backward op's eager launch and CPU definition
+ *   torch_neuronx/python_ops/scaled_dot_product_fused_attention.py:511-781
+ *   torch_neuronx/csrc/core/dispatch/NeuronDispatcher.cpp:2523-2582 (DispatchSdpaBwdImpl)
+ *   torch_neuronx/_sdpa_math.py:98-176.
+ */
+int b200_sdpa_bwd(const B200SdpaBwdParams* params, void* stream);
+
 /* Enqueue one ring-step merge (see B200SdpaMergeParams). */
 int b200_sdpa_merge(const B200SdpaMergeParams* params, void* stream);
 
@@ -228,7 +302,8 @@ int b200_sdpa_merge(const B200SdpaMergeParams* params, void* stream);
  * Launch counters, one per kernel family, so a caller can prove which kernel ran.
  * Upstream counterpart: executed-op tracking
  *   torch_neuronx/__init__.py:528-546, tests/utils/neuron_test_utils.py:18-135.
- * kernel ids: 0 generic, 1 prefill, 2 decode partial, 3 decode combine, 4 merge.
+ * kernel ids: 0 generic, 1 prefill, 2 decode partial, 3 decode combine, 4 merge,
+ * 5 backward grad_q, 6 backward grad_k/grad_v.
  */
 uint64_t b200_sdpa_launch_count(int kernel_id);
 void b200_sdpa_reset_launch_counts(void);

@@ -118,6 +118,9 @@ int main(void) {
   printf("%zu %zu %zu %zu %zu %zu %zu\n", sizeof(B200SdpaParams), offsetof(B200SdpaParams, q_offset),
          offsetof(B200SdpaParams, kv_lens), offsetof(B200SdpaParams, bias_stride), offsetof(B200SdpaParams, status),
          sizeof(B200SdpaPlan), sizeof(B200SdpaMergeParams));
+  printf("%zu %zu %zu %zu %zu %zu\n", sizeof(B200SdpaBwdParams), offsetof(B200SdpaBwdParams, grad_bias),
+         offsetof(B200SdpaBwdParams, lse_stride), offsetof(B200SdpaBwdParams, scale),
+         offsetof(B200SdpaBwdParams, q_offset), offsetof(B200SdpaBwdParams, status));
   return 0;
 }
 """
@@ -130,4 +133,24 @@ int main(void) {
     P = _lib.Params
     want = [C.sizeof(P), P.q_offset.offset, P.kv_lens.offset, P.bias_stride.offset, P.status.offset,
             C.sizeof(_lib.Plan), C.sizeof(_lib.MergeParams)]
+    W = _lib.BwdParams
+    want += [C.sizeof(W), W.grad_bias.offset, W.lse_stride.offset, W.scale.offset, W.q_offset.offset,
+             W.status.offset]
     assert got == want
+
+
+def test_backward_entry_rejects_bad_blocks():
+    lib = _lib.load()
+    assert lib.b200_sdpa_bwd(None, None) == _lib.ERR_NULL
+    p = _lib.BwdParams()
+    p.struct_size = 16
+    assert lib.b200_sdpa_bwd(C.byref(p), None) == _lib.ERR_STRUCT
+    p.struct_size = C.sizeof(_lib.BwdParams)
+    p.dtype = 9
+    assert lib.b200_sdpa_bwd(C.byref(p), None) == _lib.ERR_DTYPE
+    p.dtype = _lib.BF16
+    assert lib.b200_sdpa_bwd(C.byref(p), None) == _lib.ERR_SHAPE
+    p.B, p.Hq, p.Hkv, p.L, p.S, p.E, p.Dv = 1, 6, 4, 8, 8, 16, 16
+    assert lib.b200_sdpa_bwd(C.byref(p), None) == _lib.ERR_SHAPE
+    p.Hkv = 2
+    assert lib.b200_sdpa_bwd(C.byref(p), None) == _lib.ERR_NULL  # no pointers given

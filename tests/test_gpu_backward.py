@@ -1,0 +1,299 @@
+"""Backward parity on the GPU: ``b200_sdpa_bwd`` through the C ABI against the golden
+vectors made by upstream's ``compute_attention_backward``, against the oracle on a
+matrix of shapes and layouts, through autograd, and -- at full size -- through
+identities that hold whatever the size.
+
+Bars: fp32 gradients ``rtol 1e-4 / atol 1e-5`` (upstream's own bar for its backward
+formula, ``tests/neuron_dynamo_backend/unit/test_decompositions.py:8742``); half types
+``rtol 5e-2 / atol 5e-3`` against the fp32 oracle (upstream's device bar,
+``tests/python_ops/test_scaled_dot_product_attention.py:301``)."""
+
+import math
+
+import pytest
+import torch
+
+from oracle import sdpa_oracle as O
+from tests.golden_cases import backward_inputs_for
+
+pytestmark = pytest.mark.gpu
+
+FP32_GRAD = dict(rtol=1e-4, atol=1e-5)
+HALF_GRAD = dict(rtol=5e-2, atol=5e-3)
+
+
+def _names():
+    import os
+
+    path = os.path.join(os.path.dirname(__file__), "golden", "sdpa_bwd_golden.pt")
+    return sorted(torch.load(path, weights_only=False)["cases"].keys())
+
+
+def _cuda_backward(go, q, k, v, *, mask=None, is_causal=False, scale=None, kv_lens=None, need_grad_bias=False,
+                   out=None, lse=None, layout=None):
+    """Forward (unless out/lse are given) and backward on the GPU; gradient buffers are
+    NaN-poisoned first so that an unwritten element cannot pass."""
+    import torch_neuronx_b200 as T
+
+    dev = torch.device("cuda", 0)
+
+    def put(t):
+        t = t.to(dev)
+        if layout == "bshd":  # (B,S,H,D) storage seen as (B,H,S,D)
+            t = t.transpose(1, 2).contiguous().transpose(1, 2)
+        return t
+
+    qc, kc, vc, gc = put(q), put(k), put(v), put(go)
+    bias = None
+    if mask is not None:
+        bias = mask.to(dev)
+        if bias.dtype == torch.bool:
+            bias = torch.where(bias, 0.0, float("-inf")).to(qc.dtype)
+    lens = kv_lens.to(dev).to(torch.int32) if kv_lens is not None else None
+    if out is None:
+        oc, lc = T.sdpa_forward(qc, kc, vc, attn_bias=bias, is_causal=is_causal, scale=scale, kv_lens=lens)
+    else:
+        oc, lc = put(out), lse.to(dev)
+    gq = torch.full_like(qc, float("nan"))
+    gk = torch.full_like(kc, float("nan"))
+    gv = torch.full_like(vc, float("nan"))
+    T.reset_launch_counts()
+    gq, gk, gv, gb = T.sdpa_backward(gc, qc, kc, vc, oc, lc, attn_bias=bias, is_causal=is_causal, scale=scale,
+                                     kv_lens=lens, need_grad_bias=need_grad_bias, grad_q=gq, grad_k=gk, grad_v=gv)
+    torch.cuda.synchronize()
+    T.check_device_status()
+    counts = T.launch_counts()
+    assert counts["bwd_dq"] == 1 and counts["bwd_dkv"] == (1 if k.shape[2] > 0 else 0)
+    assert gq.stride() == qc.stride() and gk.stride() == kc.stride() and gv.stride() == vc.stride()
+    return gq.cpu(), gk.cpu(), gv.cpu(), (gb.cpu() if gb is not None else None)
+
+
+def _close(got, want, dtype, tag):
+    assert not torch.isnan(got.float()).any(), f"{tag}: NaN (unwritten or bad arithmetic)"
+    tol = FP32_GRAD if dtype == torch.float32 else HALF_GRAD
+    torch.testing.assert_close(got.float(), want.float(), msg=lambda m: f"{tag}: {m}", **tol)
+
+
+@pytest.mark.parametrize("name", _names())
+def test_backward_matches_upstream_golden(golden_bwd, name):
+    case = golden_bwd[name]
+    q, k, v, mask, go = backward_inputs_for(name, case)
+    gq, gk, gv, _ = _cuda_backward(go, q, k, v, mask=mask, is_causal=case["causal"], scale=case["scale"])
+    for got, key in ((gq, "dq"), (gk, "dk"), (gv, "dv")):
+        _close(got, case[key], q.dtype, f"{name} {key}")
+
+
+def test_backward_dead_rows_are_exact_zero(golden_bwd):
+    case = golden_bwd["dead_rows_leftpad10"]
+    gq, gk, gv, _ = _cuda_backward(case["grad_out"], case["q"], case["k"], case["v"], mask=case["mask"],
+                                   scale=case["scale"])
+    assert torch.all(gq[..., :10, :] == 0) and torch.all(gk[..., :10, :] == 0) and torch.all(gv[..., :10, :] == 0)
+
+
+def _oracle_backward(go, q, k, v, **kw):
+    """fp32 oracle: forward and backward with inputs upcast."""
+    f32 = torch.float32
+    out, lse = O.sdpa_forward(q, k, v, compute_dtype=f32, **kw)
+    return O.sdpa_backward(go, q, k, v, out, lse, compute_dtype=f32, **kw)
+
+
+SHAPES = [
+    # B, Hq, Hkv, L,   S,   E,   Dv
+    (2, 4, 4, 64, 64, 64, 64),
+    (1, 8, 2, 130, 97, 128, 128),    # ragged tails, grouped heads
+    (2, 6, 1, 33, 200, 32, 32),      # multi-query
+    (1, 2, 2, 77, 77, 16, 48),       # E != Dv
+    (1, 4, 2, 96, 160, 192, 128),    # upstream's asymmetric head dims (qk 192 / v 128)
+    (1, 2, 1, 50, 70, 256, 256),     # largest head dim served
+    (3, 4, 4, 1, 150, 64, 64),       # single query row
+    (1, 3, 3, 200, 1, 80, 80),       # single key
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_backward_against_oracle(shape, causal, dtype):
+    B, Hq, Hkv, L, S, E, Dv = shape
+    g = torch.Generator().manual_seed(hash(shape) % 1000 + (7 if causal else 0))
+    q = torch.randn(B, Hq, L, E, generator=g).to(dtype)
+    k = torch.randn(B, Hkv, S, E, generator=g).to(dtype)
+    v = torch.randn(B, Hkv, S, Dv, generator=g).to(dtype)
+    go = torch.randn(B, Hq, L, Dv, generator=g).to(dtype)
+    want = _oracle_backward(go, q, k, v, is_causal=causal)
+    got = _cuda_backward(go, q, k, v, is_causal=causal)
+    for a, b, n in zip(got[:3], want[:3], ("dq", "dk", "dv")):
+        _close(a, b, dtype, f"{shape} causal={causal} {n}")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_backward_transposed_storage_and_kv_lens(dtype):
+    g = torch.Generator().manual_seed(21)
+    B, Hq, Hkv, L, S, D = 3, 8, 2, 100, 140, 64
+    q = torch.randn(B, Hq, L, D, generator=g).to(dtype)
+    k = torch.randn(B, Hkv, S, D, generator=g).to(dtype)
+    v = torch.randn(B, Hkv, S, D, generator=g).to(dtype)
+    go = torch.randn(B, Hq, L, D, generator=g).to(dtype)
+    lens = torch.tensor([140, 0, 61])
+    want = _oracle_backward(go, q, k, v, is_causal=True, kv_lens=lens)
+    got = _cuda_backward(go, q, k, v, is_causal=True, kv_lens=lens, layout="bshd")
+    for a, b, n in zip(got[:3], want[:3], ("dq", "dk", "dv")):
+        _close(a, b, dtype, f"bshd kv_lens {n}")
+    assert torch.all(got[0][1] == 0) and torch.all(got[1][1] == 0) and torch.all(got[2][1] == 0)  # batch without keys
+    assert torch.all(got[1][2, :, 61:] == 0) and torch.all(got[2][2, :, 61:] == 0)                # padded keys
+
+
+@pytest.mark.parametrize("bias_shape", [(2, 4, 40, 56), (2, 1, 40, 56), (1, 1, 1, 56), (40, 56)])
+def test_backward_with_bias_and_logit_gradient(bias_shape):
+    g = torch.Generator().manual_seed(5)
+    q = torch.randn(2, 4, 40, 32, generator=g)
+    k = torch.randn(2, 2, 56, 32, generator=g)
+    v = torch.randn(2, 2, 56, 32, generator=g)
+    go = torch.randn(2, 4, 40, 32, generator=g)
+    bias = torch.randn(bias_shape, generator=g)
+    want = _oracle_backward(go, q, k, v, attn_mask=bias)
+    got = _cuda_backward(go, q, k, v, mask=bias, need_grad_bias=True)
+    for a, b, n in zip(got, want, ("dq", "dk", "dv", "dbias")):
+        assert a.shape == b.shape
+        _close(a, b, torch.float32, f"bias {bias_shape} {n}")
+
+
+def test_logit_gradient_is_written_beyond_the_causal_frontier():
+    # a float bias together with a causal frontier expressed through offsets: the logit
+    # gradient buffer must be fully written (zeros where masked)
+    import torch_neuronx_b200 as T
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(9)
+    q, k, v, go = (torch.randn(1, 2, 70, 16, generator=g).to(dev) for _ in range(4))
+    bias = torch.zeros(1, 1, 70, 70, device=dev)
+    out, lse = T.sdpa_forward(q, k, v, attn_bias=bias, is_causal=True)
+    _, _, _, gb = T.sdpa_backward(go, q, k, v, out, lse, attn_bias=bias, is_causal=True, need_grad_bias=True)
+    torch.cuda.synchronize()
+    upper = torch.ones(70, 70, dtype=torch.bool, device=dev).triu(1)
+    assert not torch.isnan(gb).any() and torch.all(gb[..., upper] == 0)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float64])
+@pytest.mark.parametrize("gqa", [False, True])
+def test_autograd_through_the_aten_op(dtype, gqa):
+    # upstream tests/python_ops/test_scaled_dot_product_attention.py:56-97: CPU autograd vs device autograd,
+    # and both device ops must have run
+    import torch_neuronx_b200 as T
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(42)
+    Hq, Hkv = (8, 2) if gqa else (4, 4)
+    q = torch.randn(2, Hq, 96, 64, generator=g, dtype=torch.float32)
+    k = torch.randn(2, Hkv, 96, 64, generator=g, dtype=torch.float32)
+    v = torch.randn(2, Hkv, 96, 64, generator=g, dtype=torch.float32)
+    go = torch.randn(2, Hq, 96, 64, generator=g, dtype=torch.float32)
+    qr, kr, vr = (t.clone().double().requires_grad_() for t in (q.to(dtype), k.to(dtype), v.to(dtype)))
+    ref = torch.nn.functional.scaled_dot_product_attention(qr, kr, vr, is_causal=True, enable_gqa=gqa)
+    ref.backward(go.to(dtype).double())
+
+    qd, kd, vd = (t.to(dtype).to(dev).requires_grad_() for t in (q, k, v))
+    T.reset_launch_counts()
+    out = T.scaled_dot_product_attention(qd, kd, vd, is_causal=True, enable_gqa=gqa)
+    out.backward(go.to(dtype).to(dev))
+    torch.cuda.synchronize()
+    counts = T.launch_counts()
+    assert counts["bwd_dq"] == 1 and counts["bwd_dkv"] == 1
+    for got, want, n in ((qd.grad, qr.grad, "dq"), (kd.grad, kr.grad, "dk"), (vd.grad, vr.grad, "dv")):
+        assert got.shape == want.shape and got.dtype == dtype
+        _close(got.cpu(), want, torch.float32 if dtype == torch.float64 else dtype, f"autograd {dtype} {n}")
+
+
+def test_autograd_reduces_the_logit_gradient_to_a_broadcast_bias():
+    import torch_neuronx_b200 as T
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(3)
+    q, k, v, go = (torch.randn(2, 4, 24, 32, generator=g) for _ in range(4))
+    bias = torch.randn(2, 1, 24, 24, generator=g)
+    qr, kr, vr, br = (t.clone().double().requires_grad_() for t in (q, k, v, bias))
+    torch.nn.functional.scaled_dot_product_attention(qr, kr, vr, attn_mask=br).backward(go.double())
+    qd, kd, vd, bd = (t.to(dev).requires_grad_() for t in (q, k, v, bias))
+    T.scaled_dot_product_attention(qd, kd, vd, attn_mask=bd).backward(go.to(dev))
+    torch.cuda.synchronize()
+    assert bd.grad.shape == bias.shape
+    _close(bd.grad.cpu(), br.grad, torch.float32, "dbias (broadcast over heads)")
+    _close(qd.grad.cpu(), qr.grad, torch.float32, "dq with bias")
+
+
+def test_routed_functional_call_trains():
+    import torch_neuronx_b200 as T
+
+    T.enable_sdpa_routing()
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(8)
+    q, k, v = (torch.randn(1, 4, 128, 64, generator=g).to(torch.bfloat16).to(dev).requires_grad_() for _ in range(3))
+    T.reset_launch_counts()
+    out = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True)
+    out.float().square().mean().backward()
+    torch.cuda.synchronize()
+    counts = T.launch_counts()
+    assert counts["prefill"] + counts["generic"] == 1 and counts["bwd_dq"] == 1 and counts["bwd_dkv"] == 1
+    assert all(torch.isfinite(t.grad.float()).all() for t in (q, k, v))
+
+
+def test_saturated_softmax_backward_tracks_float32():
+    # upstream tests/python_ops/test_sdpa_math.py:44-63: a bf16 backward keeps the fp32 gradient magnitude
+    for sat in (8, 32, 64):
+        amp = {}
+        for dtype in (torch.bfloat16, torch.float32):
+            torch.manual_seed(0)
+            q = (torch.randn(1, 4, 512, 128) * sat).to(dtype)
+            k = (torch.randn(1, 4, 512, 128) * sat).to(dtype)
+            v = torch.randn(1, 4, 512, 128).to(dtype)
+            go = torch.full((1, 4, 512, 128), 1e-7).to(dtype)
+            gq, gk, _, _ = _cuda_backward(go, q, k, v, is_causal=True, scale=128 ** -0.5)
+            assert torch.isfinite(gq.float()).all() and torch.isfinite(gk.float()).all()
+            amp[dtype] = (gq.float().abs().max().item() / 1e-7, gk.float().abs().max().item() / 1e-7)
+        for a, b in zip(amp[torch.bfloat16], amp[torch.float32]):
+            assert a == pytest.approx(b, rel=0.25)
+
+
+def test_backward_full_size_identities():
+    """Third benchmark configuration (bf16, 4 x 32/8 heads x 4096 x 128, causal, ragged
+    lengths).  Identities that need no reference: every probability row sums to one, so
+    the key-summed value gradient equals the row-summed upstream gradient per feature;
+    dS enters dQ and dK symmetrically, so sum(q * dq) == sum(k * dk) per kv-head group.
+    One (batch, kv head) group is also compared with the oracle."""
+    import torch_neuronx_b200 as T
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(2)
+    B, Hq, Hkv, L, D = 4, 32, 8, 4096, 128
+    q = torch.randn(B, Hq, L, D, generator=g).to(torch.bfloat16).to(dev)
+    k = torch.randn(B, Hkv, L, D, generator=g).to(torch.bfloat16).to(dev)
+    v = torch.randn(B, Hkv, L, D, generator=g).to(torch.bfloat16).to(dev)
+    go = torch.randn(B, Hq, L, D, generator=g).to(torch.bfloat16).to(dev)
+    lens = torch.tensor([4096, 3500, 2048, 4001], dtype=torch.int32, device=dev)
+    out, lse = T.sdpa_forward(q, k, v, is_causal=True, kv_lens=lens)
+    gq, gk, gv, _ = T.sdpa_backward(go, q, k, v, out, lse, is_causal=True, kv_lens=lens)
+    torch.cuda.synchronize()
+    T.check_device_status()
+    assert all(torch.isfinite(t.float()).all() for t in (gq, gk, gv))
+    # rows of batch b beyond lens[b] still see keys [0, lens[b]) -> all rows are live
+    # tolerances: the stored gradients carry one bf16 rounding each (relative 2^-9, random sign), so a
+    # sum of n of them is off by about 2^-9 * the 2-norm of the terms; eight such sigmas plus a small floor
+    eps = 8 * 2.0 ** -9
+    lhs = gv.float().sum(dim=2)
+    rhs = go.float().sum(dim=2).view(B, Hkv, Hq // Hkv, D).sum(dim=2)
+    tol = eps * gv.float().square().sum(dim=2).sqrt() + 1.0
+    assert bool(((lhs - rhs).abs() <= tol).all()), (lhs - rhs).abs().max().item()
+    qa, kb = q.float() * gq.float(), k.float() * gk.float()
+    a = qa.sum(dim=(2, 3)).view(B, Hkv, Hq // Hkv).sum(dim=2)
+    b = kb.sum(dim=(2, 3))
+    tol = eps * (qa.square().sum(dim=(2, 3)).view(B, Hkv, Hq // Hkv).sum(dim=2).sqrt()
+                 + kb.square().sum(dim=(2, 3)).sqrt()) + 1.0
+    assert bool(((a - b).abs() <= tol).all()), (a - b).abs().max().item()
+    # one group against the oracle (fp32 on the CPU)
+    bi, hk = 1, 5
+    hs = slice(hk * 4, hk * 4 + 4)
+    qs, ks, vs, gs = q[bi:bi + 1, hs].cpu(), k[bi:bi + 1, hk:hk + 1].cpu(), v[bi:bi + 1, hk:hk + 1].cpu(), go[bi:bi + 1, hs].cpu()
+    want = _oracle_backward(gs, qs, ks, vs, is_causal=True, kv_lens=lens[bi:bi + 1].cpu())
+    _close(gq[bi:bi + 1, hs].cpu(), want[0], torch.bfloat16, "full-size dq")
+    _close(gk[bi:bi + 1, hk:hk + 1].cpu(), want[1], torch.bfloat16, "full-size dk")
+    _close(gv[bi:bi + 1, hk:hk + 1].cpu(), want[2], torch.bfloat16, "full-size dv")

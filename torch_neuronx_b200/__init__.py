@@ -1,7 +1,8 @@
 """B200-native fused scaled-dot-product attention behind torch-neuronx's op API.
 
 Importing the package registers the CUDA implementation of
-``aten::_scaled_dot_product_fused_attention_overrideable`` and the kernel-level op
+``aten::_scaled_dot_product_fused_attention_overrideable`` (and of its ``_backward``
+companion) and the kernel-level op
 ``b200_sdpa::fwd``.  Compute needs ``libb200_sdpa.so`` (``python -m
 torch_neuronx_b200.build``) and a B200; nothing here falls back to another
 implementation.
@@ -13,10 +14,12 @@ from .ops import (
     check_device_status,
     enable_sdpa_routing,
     fused_attention_overrideable,
+    fused_attention_overrideable_backward,
     merge_partials,
     register_aten_override,
     scaled_dot_product_attention,
     scaled_dot_product_attention_kernel,
+    sdpa_backward,
     sdpa_forward,
 )
 from .ring import ring_attention, ring_attention_virtual, shard_sequence, unshard_sequence
@@ -29,8 +32,8 @@ reset_launch_counts = _lib.reset_launch_counts
 
 __all__ = [
     "alloc_like_query", "as_units", "check_device_status", "enable_sdpa_routing", "from_units",
-    "fused_attention_overrideable", "launch_counts", "local_units", "merge_partials", "partition_units",
+    "fused_attention_overrideable", "fused_attention_overrideable_backward", "launch_counts", "local_units", "merge_partials", "partition_units",
     "register_aten_override", "reset_launch_counts", "ring_attention", "ring_attention_virtual",
-    "scaled_dot_product_attention", "scaled_dot_product_attention_kernel", "sdpa_forward", "shard_sequence",
+    "scaled_dot_product_attention", "scaled_dot_product_attention_kernel", "sdpa_backward", "sdpa_forward", "shard_sequence",
     "unshard_sequence",
 ]

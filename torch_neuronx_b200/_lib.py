@@ -35,8 +35,8 @@ PATH_AUTO, PATH_GENERIC, PATH_PREFILL, PATH_DECODE = 0, 1, 2, 3
 PATH_NAMES = {PATH_AUTO: "auto", PATH_GENERIC: "generic", PATH_PREFILL: "prefill", PATH_DECODE: "decode"}
 
 # launch-counter ids
-KID_GENERIC, KID_PREFILL, KID_DECODE, KID_COMBINE, KID_MERGE = 0, 1, 2, 3, 4
-KERNEL_NAMES = ("generic", "prefill", "decode_partial", "decode_combine", "merge")
+KID_GENERIC, KID_PREFILL, KID_DECODE, KID_COMBINE, KID_MERGE, KID_BWD_DQ, KID_BWD_DKV = 0, 1, 2, 3, 4, 5, 6
+KERNEL_NAMES = ("generic", "prefill", "decode_partial", "decode_combine", "merge", "bwd_dq", "bwd_dkv")
 
 
 class Params(C.Structure):
@@ -121,6 +121,55 @@ class MergeParams(C.Structure):
     ]
 
 
+class BwdParams(C.Structure):
+    """Mirror of ``B200SdpaBwdParams``."""
+
+    _fields_ = [
+        ("struct_size", C.c_uint32),
+        ("dtype", C.c_int32),
+        ("device", C.c_int32),
+        ("reserved", C.c_int32),
+        ("grad_out", C.c_void_p),
+        ("q", C.c_void_p),
+        ("k", C.c_void_p),
+        ("v", C.c_void_p),
+        ("out", C.c_void_p),
+        ("lse", C.c_void_p),
+        ("grad_q", C.c_void_p),
+        ("grad_k", C.c_void_p),
+        ("grad_v", C.c_void_p),
+        ("grad_bias", C.c_void_p),
+        ("grad_out_stride", C.c_int64 * 4),
+        ("q_stride", C.c_int64 * 4),
+        ("k_stride", C.c_int64 * 4),
+        ("v_stride", C.c_int64 * 4),
+        ("out_stride", C.c_int64 * 4),
+        ("lse_stride", C.c_int64 * 3),
+        ("grad_q_stride", C.c_int64 * 4),
+        ("grad_k_stride", C.c_int64 * 4),
+        ("grad_v_stride", C.c_int64 * 4),
+        ("grad_bias_stride", C.c_int64 * 4),
+        ("B", C.c_int32),
+        ("Hq", C.c_int32),
+        ("Hkv", C.c_int32),
+        ("L", C.c_int32),
+        ("S", C.c_int32),
+        ("E", C.c_int32),
+        ("Dv", C.c_int32),
+        ("scale", C.c_float),
+        ("is_causal", C.c_int32),
+        ("bias_dtype", C.c_int32),
+        ("q_offset", C.c_int64),
+        ("k_offset", C.c_int64),
+        ("kv_lens", C.c_void_p),
+        ("bias", C.c_void_p),
+        ("bias_stride", C.c_int64 * 4),
+        ("workspace", C.c_void_p),
+        ("workspace_bytes", C.c_uint64),
+        ("status", C.c_void_p),
+    ]
+
+
 # Every symbol include/b200_sdpa.h declares: name -> (restype, argtypes)
 EXPORTS = {
     "b200_sdpa_abi_version": (C.c_int, []),
@@ -129,6 +178,7 @@ EXPORTS = {
     "b200_sdpa_fwd": (C.c_int, [C.POINTER(Params), C.c_void_p]),
     "b200_sdpa_decode": (C.c_int, [C.POINTER(Params), C.c_void_p]),
     "b200_sdpa_decode_static": (C.c_int, [C.POINTER(Params), C.c_void_p]),
+    "b200_sdpa_bwd": (C.c_int, [C.POINTER(BwdParams), C.c_void_p]),
     "b200_sdpa_merge": (C.c_int, [C.POINTER(MergeParams), C.c_void_p]),
     "b200_sdpa_launch_count": (C.c_uint64, [C.c_int]),
     "b200_sdpa_reset_launch_counts": (None, []),

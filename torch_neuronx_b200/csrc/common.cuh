@@ -33,7 +33,29 @@ struct Problem {
   int* status;
 };
 
-enum KernelId { KID_GENERIC = 0, KID_PREFILL = 1, KID_DECODE = 2, KID_COMBINE = 3, KID_MERGE = 4, KID_COUNT = 5 };
+// Backward: the forward's description (out and lse are inputs here) plus the upstream
+// gradient and the four gradient outputs.
+struct BwdProblem {
+  Problem f;
+  const void* dout;
+  int64_t dos[4];
+  void* dq;
+  void* dk;
+  void* dv;
+  void* dbias;  // optional: gradient of the logits, (B, Hq, L, S)
+  int64_t dqs[4], dks[4], dvs[4], dbs[4];
+};
+
+enum KernelId {
+  KID_GENERIC = 0,
+  KID_PREFILL = 1,
+  KID_DECODE = 2,
+  KID_COMBINE = 3,
+  KID_MERGE = 4,
+  KID_BWD_DQ = 5,
+  KID_BWD_DKV = 6,
+  KID_COUNT = 7
+};
 
 // Host launchers implemented in the per-kernel translation units.  Each returns
 // a b200_sdpa_status and never synchronises.
@@ -54,6 +76,8 @@ int plan_prefill(const Problem& p, int dtype, B200SdpaPlan* plan);
 bool prefill_eligible(const Problem& p, int dtype, bool* alignment_only_failure);
 
 int launch_merge(const B200SdpaMergeParams& m, cudaStream_t stream);
+
+int launch_bwd_generic(const BwdProblem& bp, int dtype, cudaStream_t stream);
 
 void count_launch(int kernel_id);
 
