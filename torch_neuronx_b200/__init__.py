@@ -18,10 +18,13 @@ from .ops import (
     merge_partials,
     register_aten_override,
     scaled_dot_product_attention,
+    scaled_dot_product_attention_backward_kernel,
     scaled_dot_product_attention_kernel,
+    set_mask_recognition,
     sdpa_backward,
     sdpa_forward,
 )
+from .masks import MaskStructure, classify_mask
 from .ring import ring_attention, ring_attention_virtual, shard_sequence, unshard_sequence
 from .sharding import as_units, from_units, local_units, partition_units
 
@@ -31,9 +34,10 @@ launch_counts = _lib.launch_counts
 reset_launch_counts = _lib.reset_launch_counts
 
 __all__ = [
-    "alloc_like_query", "as_units", "check_device_status", "enable_sdpa_routing", "from_units",
-    "fused_attention_overrideable", "fused_attention_overrideable_backward", "launch_counts", "local_units", "merge_partials", "partition_units",
-    "register_aten_override", "reset_launch_counts", "ring_attention", "ring_attention_virtual",
-    "scaled_dot_product_attention", "scaled_dot_product_attention_kernel", "sdpa_backward", "sdpa_forward", "shard_sequence",
-    "unshard_sequence",
+    "MaskStructure", "alloc_like_query", "as_units", "check_device_status", "classify_mask", "enable_sdpa_routing",
+    "from_units", "fused_attention_overrideable", "fused_attention_overrideable_backward", "launch_counts",
+    "local_units", "merge_partials", "partition_units", "register_aten_override", "reset_launch_counts",
+    "ring_attention", "ring_attention_virtual", "scaled_dot_product_attention",
+    "scaled_dot_product_attention_backward_kernel", "scaled_dot_product_attention_kernel", "sdpa_backward",
+    "sdpa_forward", "set_mask_recognition", "shard_sequence", "unshard_sequence",
 ]

@@ -1,0 +1,123 @@
+"""Structured-mask recognition: turn a dense boolean keep-mask that only expresses
+causality and/or right padding into ``is_causal`` / ``kv_lens``.
+
+A dense mask forces the generic CUDA-core kernel (the tensor-core kernels take no
+bias operand), exactly as a mask operand makes upstream's decomposition reject its
+flash kernel; upstream removes such masks with an FX pass at trace time
+(``torch_neuronx/neuron_dynamo_backend/fx/passes/sdpa_causal_mask.py:1-37``).  Here
+the op runs eagerly, so the mask is examined when it is first seen: a candidate
+structure is derived from the mask's last query row, the mask that structure would
+produce is rebuilt, and the two are compared cell by cell on the mask's own device.
+As upstream insists (``:33-36``) the comparison is exact -- no tolerance, no sampling --
+so a sliding-window or key-offset mask can never be mistaken for a causal one.  Only
+boolean masks are examined; an additive float mask is left alone because reading a
+"large negative" sentinel back depends on the float width (``:9-12``).
+
+One comparison costs a device-to-host read of two flags.  The verdict is cached per
+mask tensor (identity + version counter), so a mask built once and reused across
+layers and steps is examined once.
+"""
+
+from __future__ import annotations
+
+import weakref
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+
+@dataclass
+class MaskStructure:
+    """What a mask turned out to be.  ``residual`` is the original mask when it has no
+    recognised structure (then ``is_causal`` is False and ``kv_lens`` is None)."""
+
+    is_causal: bool
+    kv_lens: Optional[torch.Tensor]  # int32 (B,) on the mask's device
+    residual: Optional[torch.Tensor]
+
+    @property
+    def recognised(self) -> bool:
+        return self.residual is None
+
+
+_cache: dict[int, tuple] = {}
+_CACHE_MAX = 16
+stats = {"examined": 0, "cache_hits": 0, "recognised": 0}
+
+
+def _lookup(mask: torch.Tensor, key):
+    hit = _cache.get(id(mask))
+    if hit is None:
+        return None
+    ref, version, k, verdict = hit
+    if ref() is mask and version == mask._version and k == key:
+        return verdict
+    del _cache[id(mask)]
+    return None
+
+
+def _store(mask: torch.Tensor, key, verdict) -> None:
+    if len(_cache) >= _CACHE_MAX:
+        for dead in [i for i, (ref, *_rest) in _cache.items() if ref() is None]:
+            del _cache[dead]
+        while len(_cache) >= _CACHE_MAX:
+            del _cache[next(iter(_cache))]
+    _cache[id(mask)] = (weakref.ref(mask), mask._version, key, verdict)
+
+
+def classify_mask(mask: Optional[torch.Tensor], batch: int, n_q: int, n_k: int) -> MaskStructure:
+    """Examine a keep-mask for a ``(batch, *, n_q, n_k)`` attention call.
+
+    Recognised (exactly): all-True; the top-left aligned lower triangle (what
+    ``is_causal=True`` means); right padding -- every query row of batch ``b`` keeps
+    keys ``j < len_b``; and the intersection of the triangle with right padding when
+    ``n_q == n_k``.  The head dimension of the mask must be 1 (or absent).
+    """
+    if mask is None:
+        return MaskStructure(False, None, None)
+    if mask.dtype != torch.bool or mask.dim() > 4 or mask.dim() < 2:
+        return MaskStructure(False, None, mask)
+    key = (batch, n_q, n_k)
+    verdict = _lookup(mask, key)
+    if verdict is not None:
+        stats["cache_hits"] += 1
+        return verdict
+    verdict = _examine(mask, batch, n_q, n_k)
+    stats["examined"] += 1
+    stats["recognised"] += int(verdict.recognised)
+    _store(mask, key, verdict)
+    return verdict
+
+
+def _examine(mask: torch.Tensor, batch: int, n_q: int, n_k: int) -> MaskStructure:
+    m4 = mask.reshape((1,) * (4 - mask.dim()) + tuple(mask.shape))
+    mb, mh, mq, mk = m4.shape
+    if mh != 1 or mk != n_k or mb not in (1, batch) or mq not in (1, n_q) or n_k == 0:
+        return MaskStructure(False, None, mask)
+    dev = mask.device
+    rows = m4[:, 0]                                   # (mb, mq, n_k)
+    lens = rows[:, -1, :].sum(dim=-1)                 # keys the last query row keeps
+    cols = torch.arange(n_k, device=dev)
+    prefix = cols.view(1, 1, n_k) < lens.view(mb, 1, 1)
+    is_padding = (rows == prefix).all()
+    if mq == n_q and n_q > 1:
+        tri = cols.view(1, n_k) <= torch.arange(n_q, device=dev).view(n_q, 1)
+        # the triangle clips the last row to n_q keys when n_q < n_k; the padding length
+        # is then not observable from the mask, so the combined form needs n_q >= n_k
+        is_causal_padding = (rows == (prefix & tri)).all() if n_q >= n_k else (rows == tri).all()
+    else:
+        is_causal_padding = torch.zeros((), dtype=torch.bool, device=dev)
+    no_padding = (lens == n_k).all()
+    flags = torch.stack([is_padding, is_causal_padding, no_padding]).tolist()   # the one host read
+    if not (flags[0] or flags[1]):
+        return MaskStructure(False, None, mask)
+    causal = bool(flags[1]) and not bool(flags[0])
+    if causal and n_q < n_k:
+        return MaskStructure(True, None, None)
+    if flags[2]:
+        return MaskStructure(causal, None, None)
+    lens32 = lens.to(torch.int32)
+    if mb == 1 and batch != 1:
+        lens32 = lens32.expand(batch)
+    return MaskStructure(causal, lens32.contiguous(), None)

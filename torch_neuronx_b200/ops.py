@@ -33,7 +33,7 @@ from typing import Optional
 import torch
 import torch.overrides
 
-from . import _lib
+from . import _lib, masks
 
 _DTYPE_CODE = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
 
@@ -490,6 +490,35 @@ _LIB_IMPL.impl("fwd", _fwd_cuda, "CUDA")
 _LIB_IMPL.impl("fwd", _fwd_meta, "Meta")
 
 
+_LIB_DEF.define(
+    "bwd(Tensor grad_out, Tensor q, Tensor k, Tensor v, Tensor out, Tensor lse, bool is_causal=False, "
+    "float dropout_p=0.0, float? scale=None, int? seed=None, *, Tensor? kv_lens=None) -> (Tensor, Tensor, Tensor)"
+)
+
+
+def _bwd_cuda(grad_out, q, k, v, out, lse, is_causal=False, dropout_p=0.0, scale=None, seed=None, *, kv_lens=None):
+    _validate(q, k, v, None, dropout_p, False, False)
+    gq, gk, gv, _ = sdpa_backward(grad_out, q, k, v, out, lse, is_causal=is_causal, scale=scale, kv_lens=kv_lens)
+    return gq, gk, gv
+
+
+def _bwd_meta(grad_out, q, k, v, out, lse, is_causal=False, dropout_p=0.0, scale=None, seed=None, *, kv_lens=None):
+    return torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+
+
+_LIB_IMPL.impl("bwd", _bwd_cuda, "CUDA")
+_LIB_IMPL.impl("bwd", _bwd_meta, "Meta")
+
+
+def scaled_dot_product_attention_backward_kernel(
+    grad_out, q, k, v, out, lse, is_causal=False, dropout_p=0.0, scale=None, seed=None, kv_lens=None
+):
+    """Same call shape as upstream's ``scaled_dot_product_attention_backward_kernel``
+    (``nki_kernels/scaled_dot_product_attention_backward.py:9-50``): gradients for q, k
+    and v from the forward's output and fp32 ``(B, Hq, L)`` log-sum-exp."""
+    return torch.ops.b200_sdpa.bwd(grad_out, q, k, v, out, lse, is_causal, dropout_p, scale, seed, kv_lens=kv_lens)
+
+
 def scaled_dot_product_attention_kernel(
     q, k, v, is_causal=False, dropout_p=0.0, scale=None, training=False, seed=None, lse=None, kv_lens=None
 ):
@@ -557,8 +586,7 @@ class _SdpaRouting(torch.overrides.TorchFunctionMode):
                 and q.dtype == k.dtype == v.dtype
                 and (q.shape[1] == k.shape[1] or bound.get("enable_gqa", False))
             ):
-                return torch.ops.aten._scaled_dot_product_fused_attention_overrideable(
-                    q, k, v, mask, drop, causal, False, scale=bound.get("scale"))[0]
+                return scaled_dot_product_attention(q, k, v, mask, drop, causal, bound.get("scale"), True)
         return func(*args, **kwargs)
 
 
@@ -584,6 +612,36 @@ def enable_sdpa_routing() -> None:
 # ----------------------------------------------------------------------------
 
 
+class _AttentionWithKeyLengths(torch.autograd.Function):
+    """Autograd for the one call shape the ATen op cannot express: per-batch valid key
+    counts instead of a mask.  Forward and backward are the same two foreign calls the
+    ATen ops make."""
+
+    @staticmethod
+    def forward(ctx, query, key, value, kv_lens, is_causal, scale):
+        out, lse = sdpa_forward(query, key, value, is_causal=is_causal, scale=scale, kv_lens=kv_lens, need_lse=True)
+        ctx.save_for_backward(query, key, value, out, lse, kv_lens)
+        ctx.is_causal, ctx.scale = is_causal, scale
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        query, key, value, out, lse, kv_lens = ctx.saved_tensors
+        gq, gk, gv, _ = sdpa_backward(grad_out, query, key, value, out, lse, is_causal=ctx.is_causal,
+                                      scale=ctx.scale, kv_lens=kv_lens)
+        return gq, gk, gv, None, None, None
+
+
+_recognise_masks = True
+
+
+def set_mask_recognition(enabled: bool) -> None:
+    """Switch the examination of dense boolean masks (see ``masks.classify_mask``) on or
+    off for :func:`scaled_dot_product_attention` and the routed functional call."""
+    global _recognise_masks
+    _recognise_masks = bool(enabled)
+
+
 def scaled_dot_product_attention(
     query, key, value, attn_mask=None, dropout_p=0.0, is_causal=False, scale=None, enable_gqa=False, *, kv_lens=None
 ):
@@ -596,6 +654,14 @@ def scaled_dot_product_attention(
     _validate(query, key, value, attn_mask, dropout_p, is_causal, False)
     if not enable_gqa and query.shape[1] != key.shape[1]:
         raise RuntimeError("SDPA: number of heads differ between query and key; pass enable_gqa=True")
+    if (
+        _recognise_masks and attn_mask is not None and attn_mask.dtype == torch.bool and kv_lens is None
+        and not torch.cuda.is_current_stream_capturing()
+    ):
+        # a dense mask that only says "causal" and/or "right padding" keeps the tensor-core kernels
+        found = masks.classify_mask(attn_mask, query.shape[0], query.shape[2], key.shape[2])
+        if found.recognised:
+            attn_mask, is_causal, kv_lens = None, found.is_causal, found.kv_lens
     if kv_lens is None:
         return torch.ops.aten._scaled_dot_product_fused_attention_overrideable(
             query, key, value, attn_mask, dropout_p, is_causal, False, scale=scale
@@ -603,7 +669,12 @@ def scaled_dot_product_attention(
     in_dtype = query.dtype
     if in_dtype == torch.float64:
         query, key, value = query.float(), key.float(), value.float()
-    bias = _additive_bias(attn_mask, query)
-    out, _ = sdpa_forward(query, key, value, attn_bias=bias, is_causal=is_causal, scale=scale, kv_lens=kv_lens,
-                          need_lse=False)
+    if attn_mask is None:
+        out = _AttentionWithKeyLengths.apply(query, key, value, kv_lens, bool(is_causal), scale)
+    else:
+        if torch.is_grad_enabled() and (query.requires_grad or key.requires_grad or value.requires_grad):
+            raise NotImplementedError("kv_lens together with attn_mask is forward-only; fold the lengths into the mask")
+        bias = _additive_bias(attn_mask, query)
+        out, _ = sdpa_forward(query, key, value, attn_bias=bias, is_causal=is_causal, scale=scale, kv_lens=kv_lens,
+                              need_lse=False)
     return out.double() if in_dtype == torch.float64 else out
