@@ -321,3 +321,34 @@ def test_backward_full_size_identities():
     _close(gq[bi:bi + 1, hs].cpu(), want[0], torch.bfloat16, "full-size dq")
     _close(gk[bi:bi + 1, hk:hk + 1].cpu(), want[1], torch.bfloat16, "full-size dk")
     _close(gv[bi:bi + 1, hk:hk + 1].cpu(), want[2], torch.bfloat16, "full-size dv")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("layout", ["zigzag", "contiguous"])
+def test_ring_backward_with_virtual_ranks(layout, dtype):
+    """Four virtual ranks on one GPU: the per-block backward calls (global offsets, the
+    final out/lse as normalisers) must add up to the gradients of full attention."""
+    import torch_neuronx_b200 as T
+    from torch_neuronx_b200 import ring
+
+    dev = torch.device("cuda", 0)
+    world = 4
+    g = torch.Generator().manual_seed(12)
+    S = 128 * world
+    q = torch.randn(1, 8, S, 64, generator=g).to(dtype)
+    k = torch.randn(1, 2, S, 64, generator=g).to(dtype)
+    v = torch.randn(1, 2, S, 64, generator=g).to(dtype)
+    go = torch.randn(1, 8, S, 64, generator=g).to(dtype)
+    sh = lambda t: [ring.shard_sequence(t, r, world, layout).contiguous().to(dev) for r in range(world)]  # noqa: E731
+    qs, ks, vs, gos = sh(q), sh(k), sh(v), sh(go)
+    outs, lses, _ = T.ring_attention_virtual(qs, ks, vs, is_causal=True, layout=layout)
+    dq, dk, dv, calls = ring.ring_attention_backward_virtual(gos, qs, ks, vs, outs, lses, is_causal=True, layout=layout)
+    torch.cuda.synchronize()
+    T.check_device_status()
+    out = ring.unshard_sequence([o.cpu() for o in outs], layout)
+    lse = ring.unshard_sequence([l.cpu().unsqueeze(-1) for l in lses], layout).squeeze(-1)
+    want = _oracle_backward(go, q, k, v, forward=(out, lse), is_causal=True)
+    for got, w, n in zip((dq, dk, dv), want[:3], ("dq", "dk", "dv")):
+        _close(ring.unshard_sequence([t.cpu() for t in got], layout), w, dtype, f"ring {layout} {n}",
+               None if dtype == torch.float32 else dict(rtol=5e-2, atol=2e-2))
+    assert calls == (world * (world + 1) // 2 if layout == "contiguous" else world * world + world)

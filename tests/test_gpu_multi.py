@@ -70,3 +70,64 @@ def test_ring_and_partition_on_two_gpus(tmp_path):
         for layout in ("zigzag", "contiguous"):
             assert res[layout][0] <= 2e-2 and res[layout][1] <= 1e-3, (r, layout, res[layout])
         assert res["units"] <= 2e-2
+
+
+def _train_worker(rank, world, port, out_dir):
+    """Forward + backward of a sequence-sharded attention through torch's context-parallel
+    dispatch (DTensor inputs) and through the ring driver directly."""
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor import DTensor, Shard
+    from torch.distributed.tensor.experimental._context_parallel import _attention as cp
+
+    import torch_neuronx_b200 as T
+    from oracle import sdpa_oracle as O
+    from torch_neuronx_b200 import dtensor as D
+
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        mesh = init_device_mesh("cuda", (world,))
+        assert D.install_context_parallel_handler()
+        g = torch.Generator().manual_seed(0)
+        S = 256 * world
+        q = torch.randn(1, 8, S, 64, generator=g)
+        k = torch.randn(1, 2, S, 64, generator=g)
+        v = torch.randn(1, 2, S, 64, generator=g)
+        go = torch.randn(1, 8, S, 64, generator=g)
+        ref_o, ref_l = O.sdpa_forward(q, k, v, is_causal=True)
+        ref_g = O.sdpa_backward(go, q, k, v, ref_o, ref_l, is_causal=True)
+        res = {}
+        for layout in ("zigzag", "contiguous"):
+            D.set_sequence_layout(layout)
+            loc = [T.shard_sequence(t, rank, world, layout).contiguous().to(dev) for t in (q, k, v, go)]
+            qd, kd, vd = (DTensor.from_local(t, mesh, [Shard(2)]).requires_grad_() for t in loc[:3])
+            cp._enable_cp_dtensor_dispatcher()
+            try:
+                out = torch.ops.aten._scaled_dot_product_fused_attention_overrideable(qd, kd, vd, None, 0.0, True)[0]
+                out.backward(DTensor.from_local(loc[3], mesh, [Shard(2)]))
+            finally:
+                cp._disable_cp_dtensor_dispatcher()
+            torch.cuda.synchronize()
+            T.check_device_status()
+            errs = [(out.to_local().detach().cpu() - T.shard_sequence(ref_o, rank, world, layout)).abs().max().item()]
+            for got, want in zip((qd.grad, kd.grad, vd.grad), ref_g[:3]):
+                errs.append((got.to_local().cpu() - T.shard_sequence(want, rank, world, layout)).abs().max().item())
+            res[layout] = errs
+        torch.save(res, os.path.join(out_dir, f"r{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_context_parallel_training_step_on_two_gpus(tmp_path):
+    import torch.multiprocessing as mp
+
+    mp.spawn(_train_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    for r in range(2):
+        res = torch.load(tmp_path / f"r{r}.pt")
+        for layout, errs in res.items():
+            assert errs[0] <= 1e-5 and max(errs[1:]) <= 1e-4, (r, layout, errs)

@@ -39,6 +39,86 @@ def _oracle_merge(acc, acc_lse, part, part_lse, first):
         acc_lse.copy_(l)
 
 
+def _oracle_bwd(grad_out, q, k, v, out, lse, *, is_causal, scale, q_offset, k_offset):
+    """Block backward from the oracle's primitives: the block's visibility as an additive
+    bias, the local rows' FINAL out and lse as normalisers."""
+    from oracle import sdpa_oracle as O
+
+    bias = None
+    if is_causal:
+        bias = O.offset_causal_bias(q.shape[2], k.shape[2], q_offset, k_offset, q.dtype)
+    ke, ve = O.expand_kv_heads(q, k, v)
+    dq, dk, dv, _ = O.attention_backward_core(grad_out, q, ke, ve, out, lse, bias, float(scale), False)
+    g = q.shape[1] // k.shape[1]
+    if g > 1:
+        b, _, s, _ = dk.shape
+        dk = dk.view(b, k.shape[1], g, s, dk.shape[-1]).sum(dim=2)
+        dv = dv.view(b, k.shape[1], g, s, dv.shape[-1]).sum(dim=2)
+    return dq, dk, dv
+
+
+def _bwd_worker(rank, world, port, layout, causal, result_dir):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import sdpa_oracle as O
+        from torch_neuronx_b200 import ring
+
+        g = torch.Generator().manual_seed(1)
+        S = 16 * world
+        q = torch.randn(2, 4, S, 16, generator=g)
+        k = torch.randn(2, 2, S, 16, generator=g)
+        v = torch.randn(2, 2, S, 16, generator=g)
+        go = torch.randn(2, 4, S, 16, generator=g)
+        out, lse = O.sdpa_forward(q, k, v, is_causal=causal, scale=0.3)
+        want = O.sdpa_backward(go, q, k, v, out, lse, is_causal=causal, scale=0.3)
+        loc = [ring.shard_sequence(t, rank, world, layout).contiguous() for t in (go, q, k, v, out)]
+        lse_l = ring.shard_sequence(lse.unsqueeze(-1), rank, world, layout).squeeze(-1).contiguous()
+        dq, dk, dv = ring.ring_attention_backward(loc[0], loc[1], loc[2], loc[3], loc[4], lse_l, is_causal=causal,
+                                                  scale=0.3, layout=layout, bwd_fn=_oracle_bwd)
+        ok = all(
+            (got - ring.shard_sequence(w, rank, world, layout)).abs().max().item() < 2e-5
+            for got, w in zip((dq, dk, dv), want[:3])
+        )
+        torch.save(dict(ok=ok), os.path.join(result_dir, f"r{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,layout,causal", [(2, "zigzag", True), (3, "contiguous", True),
+                                                 (4, "zigzag", True), (2, "zigzag", False)])
+def test_ring_backward_over_gloo(tmp_path, world, layout, causal):
+    port = _free_port()
+    mp.spawn(_bwd_worker, args=(world, port, layout, causal, str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        assert torch.load(tmp_path / f"r{r}.pt")["ok"], f"rank {r}: ring gradients differ from full attention"
+
+
+@pytest.mark.parametrize("world,layout,causal", [(1, "zigzag", True), (4, "zigzag", True), (3, "contiguous", True),
+                                                 (4, "contiguous", False)])
+def test_ring_backward_virtual_ranks(world, layout, causal):
+    from oracle import sdpa_oracle as O
+    from torch_neuronx_b200 import ring
+
+    g = torch.Generator().manual_seed(2)
+    S = 24 * world
+    q = torch.randn(1, 6, S, 8, generator=g)
+    k = torch.randn(1, 3, S, 8, generator=g)
+    v = torch.randn(1, 3, S, 12, generator=g)
+    go = torch.randn(1, 6, S, 12, generator=g)
+    out, lse = O.sdpa_forward(q, k, v, is_causal=causal)
+    want = O.sdpa_backward(go, q, k, v, out, lse, is_causal=causal)
+    sh = lambda t: [ring.shard_sequence(t, r, world, layout) for r in range(world)]  # noqa: E731
+    lses = [x.squeeze(-1) for x in sh(lse.unsqueeze(-1))]
+    dq, dk, dv, calls = ring.ring_attention_backward_virtual(sh(go), sh(q), sh(k), sh(v), sh(out), lses,
+                                                             is_causal=causal, layout=layout, bwd_fn=_oracle_bwd)
+    for got, w in zip((dq, dk, dv), want[:3]):
+        assert (ring.unshard_sequence(got, layout) - w).abs().max().item() < 2e-5
+    assert calls >= world
+
+
 def _worker(rank, world, port, layout, causal, result_dir):
     sys.path.insert(0, ROOT)
     os.environ["MASTER_ADDR"] = "127.0.0.1"

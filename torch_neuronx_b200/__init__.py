@@ -25,7 +25,14 @@ from .ops import (
     sdpa_forward,
 )
 from .masks import MaskStructure, classify_mask
-from .ring import ring_attention, ring_attention_virtual, shard_sequence, unshard_sequence
+from .ring import (
+    ring_attention,
+    ring_attention_backward,
+    ring_attention_backward_virtual,
+    ring_attention_virtual,
+    shard_sequence,
+    unshard_sequence,
+)
 from .sharding import as_units, from_units, local_units, partition_units
 
 register_aten_override()
@@ -37,7 +44,7 @@ __all__ = [
     "MaskStructure", "alloc_like_query", "as_units", "check_device_status", "classify_mask", "enable_sdpa_routing",
     "from_units", "fused_attention_overrideable", "fused_attention_overrideable_backward", "launch_counts",
     "local_units", "merge_partials", "partition_units", "register_aten_override", "reset_launch_counts",
-    "ring_attention", "ring_attention_virtual", "scaled_dot_product_attention",
+    "ring_attention", "ring_attention_backward", "ring_attention_backward_virtual", "ring_attention_virtual", "scaled_dot_product_attention",
     "scaled_dot_product_attention_backward_kernel", "scaled_dot_product_attention_kernel", "sdpa_backward",
     "sdpa_forward", "set_mask_recognition", "shard_sequence", "unshard_sequence",
 ]

@@ -457,6 +457,16 @@ def fused_attention_overrideable_backward(
     return gq, gk, gv, gb
 
 
+def _overrideable_backward_meta(
+    grad_out, query, key, value, attn_bias, grad_input_mask, out, logsumexp, cum_seq_q, cum_seq_k, max_q, max_k,
+    dropout_p, is_causal, philox_seed, philox_offset, *, scale=None
+):
+    grad_bias = None
+    if attn_bias is not None and attn_bias.numel() > 1 and (len(grad_input_mask) < 4 or grad_input_mask[3]):
+        grad_bias = query.new_empty((query.shape[0], query.shape[1], query.shape[2], key.shape[2]))
+    return torch.empty_like(query), torch.empty_like(key), torch.empty_like(value), grad_bias
+
+
 # ----------------------------------------------------------------------------
 # kernel-level custom op (signature of upstream's nki_kernels op)
 # ----------------------------------------------------------------------------
@@ -548,6 +558,9 @@ def register_aten_override() -> None:
     lib.impl(
         "_scaled_dot_product_fused_attention_overrideable_backward", fused_attention_overrideable_backward, "CUDA"
     )
+    # torch ships a meta kernel for the forward op only; tracing and DTensor's sharding propagation need
+    # the backward's output shapes too
+    lib.impl("_scaled_dot_product_fused_attention_overrideable_backward", _overrideable_backward_meta, "Meta")
     _ATEN_IMPL = lib
 
 

@@ -269,3 +269,156 @@ def ring_attention_virtual(
                                attn_fn, merge_fn)
     outs = [st.finish(qs[0].dtype) for st in states]
     return [o for o, _ in outs], [l for _, l in outs], calls
+
+
+# ----------------------------------------------------------------------------
+# backward
+# ----------------------------------------------------------------------------
+
+
+def _default_bwd(grad_out, q, k, v, out, lse, *, is_causal, scale, q_offset, k_offset):
+    from . import ops
+
+    gq, gk, gv, _ = ops.sdpa_backward(grad_out, q, k, v, out, lse, is_causal=is_causal, scale=scale,
+                                      q_offset=q_offset, k_offset=k_offset)
+    return gq, gk, gv
+
+
+def ring_backward_step(grad_q: torch.Tensor, grad_kv: Sequence[torch.Tensor], grad_out, q, out, lse, kv_k, kv_v,
+                       rank: int, src: int, world: int, layout: str, causal: bool, scale, bwd_fn) -> int:
+    """Gradient contributions of this rank's query rows against one visiting key/value
+    block, through the same block calls as the forward (:func:`ring_schedule`).
+    ``grad_q`` (fp32, local rows) and ``grad_kv = (dk, dv)`` (fp32, the visiting block's
+    keys) are added to in place.  The forward's final ``out`` and ``lse`` of the local
+    rows normalise every block, so the per-block calls need no merge."""
+    calls = ring_schedule(rank, src, world, q.shape[2], layout, causal)
+    for c in calls:
+        rows = slice(c.q0, c.q1)
+        keys = slice(c.k0, c.k1)
+        gq, gk, gv = bwd_fn(grad_out[:, :, rows], q[:, :, rows], kv_k[:, :, keys], kv_v[:, :, keys],
+                            out[:, :, rows], lse[:, :, rows], is_causal=c.causal, scale=scale,
+                            q_offset=c.q_offset, k_offset=c.k_offset)
+        grad_q[:, :, rows] += gq
+        grad_kv[0][:, :, keys] += gk
+        grad_kv[1][:, :, keys] += gv
+    return len(calls)
+
+
+def ring_attention_backward(
+    grad_out: torch.Tensor,
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    out: torch.Tensor,
+    lse: torch.Tensor,
+    *,
+    group=None,
+    is_causal: bool = True,
+    scale: Optional[float] = None,
+    layout: str = ZIGZAG,
+    bwd_fn: Optional[Callable] = None,
+):
+    """Backward of :func:`ring_attention` for this rank's shard; returns ``(dq, dk, dv)``
+    in the input dtype.  Upstream's counterpart circulates the query side
+    (``cp_ring_handler.py:321-395``) or runs torch's templated ring backward over the op
+    (``:429-453``); here the key/value blocks travel as in the forward and their fp32
+    gradient accumulators follow one step behind:
+
+    * step s: post send/recv of the next key/value block, and receive the accumulator of
+      the block now held from the rank that worked on it in step s-1; compute this rank's
+      contribution meanwhile; add the two; the sum is sent on in step s+1;
+    * after the last step the accumulator makes one more hop and is home.
+
+    Transfers therefore always overlap a step of compute, and every remote buffer lands
+    in local memory before a kernel reads it."""
+    import torch.distributed as dist
+
+    bwd_fn = bwd_fn or _default_bwd
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    if scale is None:
+        scale = q.shape[3] ** -0.5
+    f32 = torch.float32
+    grad_q = torch.zeros(q.shape, dtype=f32, device=q.device)
+
+    def kv_zeros():
+        return [torch.zeros(k.shape, dtype=f32, device=k.device), torch.zeros(v.shape, dtype=f32, device=v.device)]
+
+    if world == 1:
+        own = kv_zeros()
+        ring_backward_step(grad_q, own, grad_out, q, out, lse, k, v, 0, 0, 1, layout, is_causal, scale, bwd_fn)
+        return grad_q.to(q.dtype), own[0].to(k.dtype), own[1].to(v.dtype)
+
+    send_to = dist.get_global_rank(group, (rank + 1) % world) if group is not None else (rank + 1) % world
+    recv_from = dist.get_global_rank(group, (rank - 1) % world) if group is not None else (rank - 1) % world
+    cur = [k.contiguous(), v.contiguous()]
+    nxt = [torch.empty_like(cur[0]), torch.empty_like(cur[1])]
+    # three accumulator sets rotate through the roles (being sent, being received, being computed)
+    sending, receiving, computing = kv_zeros(), kv_zeros(), kv_zeros()
+
+    for step in range(world):
+        ops_ = []
+        if step + 1 < world:
+            ops_ += [dist.P2POp(dist.isend, b, send_to, group) for b in cur]
+            ops_ += [dist.P2POp(dist.irecv, b, recv_from, group) for b in nxt]
+        if step > 0:
+            ops_ += [dist.P2POp(dist.isend, b, send_to, group) for b in sending]
+            ops_ += [dist.P2POp(dist.irecv, b, recv_from, group) for b in receiving]
+        reqs = dist.batch_isend_irecv(ops_) if ops_ else []
+        src = (rank - step) % world
+        if step > 0:
+            computing[0].zero_()
+            computing[1].zero_()
+        ring_backward_step(grad_q, computing, grad_out, q, out, lse, cur[0], cur[1], rank, src, world, layout,
+                           is_causal, scale, bwd_fn)
+        for r in reqs:
+            r.wait()
+        if step > 0:  # what the ranks before this one found for the same block
+            computing[0] += receiving[0]
+            computing[1] += receiving[1]
+        sending, receiving, computing = computing, sending, receiving
+        cur, nxt = nxt, cur
+    # the block held last belongs to the next rank: one more hop brings every accumulator home
+    reqs = dist.batch_isend_irecv(
+        [dist.P2POp(dist.isend, b, send_to, group) for b in sending]
+        + [dist.P2POp(dist.irecv, b, recv_from, group) for b in receiving]
+    )
+    for r in reqs:
+        r.wait()
+    return grad_q.to(q.dtype), receiving[0].to(k.dtype), receiving[1].to(v.dtype)
+
+
+def ring_attention_backward_virtual(
+    grad_outs: Sequence[torch.Tensor],
+    qs: Sequence[torch.Tensor],
+    ks: Sequence[torch.Tensor],
+    vs: Sequence[torch.Tensor],
+    outs: Sequence[torch.Tensor],
+    lses: Sequence[torch.Tensor],
+    *,
+    is_causal: bool = True,
+    scale: Optional[float] = None,
+    layout: str = ZIGZAG,
+    bwd_fn: Optional[Callable] = None,
+):
+    """Every rank in this process (see :func:`ring_attention_virtual`): the accumulator
+    of block ``src`` is simply indexed instead of travelling."""
+    bwd_fn = bwd_fn or _default_bwd
+    world = len(qs)
+    if scale is None:
+        scale = qs[0].shape[3] ** -0.5
+    f32 = torch.float32
+    grad_q = [torch.zeros(q.shape, dtype=f32, device=q.device) for q in qs]
+    grad_kv = [[torch.zeros(k.shape, dtype=f32, device=k.device), torch.zeros(v.shape, dtype=f32, device=v.device)]
+               for k, v in zip(ks, vs)]
+    calls = 0
+    for step in range(world):
+        for rank in range(world):
+            src = (rank - step) % world
+            calls += ring_backward_step(grad_q[rank], grad_kv[src], grad_outs[rank], qs[rank], outs[rank],
+                                        lses[rank], ks[src], vs[src], rank, src, world, layout, is_causal, scale,
+                                        bwd_fn)
+    dq = [g.to(qs[0].dtype) for g in grad_q]
+    dk = [g[0].to(ks[0].dtype) for g in grad_kv]
+    dv = [g[1].to(vs[0].dtype) for g in grad_kv]
+    return dq, dk, dv, calls
