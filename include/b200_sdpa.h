@@ -191,7 +191,7 @@ typedef struct B200SdpaBwdParams {
   uint32_t struct_size;    /* = sizeof(B200SdpaBwdParams)                              */
   int32_t dtype;           /* dtype of q, k, v, out, grad_out and all gradients        */
   int32_t device;
-  int32_t reserved;        /* 0                                                         */
+  int32_t force_path;      /* AUTO, GENERIC (CUDA-core kernels) or PREFILL (tcgen05 kernels) */
 
   const void* grad_out;    /* (B, Hq,  L, Dv)                                           */
   const void* q;           /* (B, Hq,  L, E)                                            */
@@ -225,8 +225,9 @@ typedef struct B200SdpaBwdParams {
   const void* bias;        /* the forward's additive bias, or NULL                      */
   int64_t bias_stride[4];
 
-  void* workspace;         /* reserved for kernels that need scratch; the kernels in
-                              this build need none                                      */
+  void* workspace;         /* scratch of the tensor-core kernels (16-byte aligned);
+                              b200_sdpa_bwd_query_plan() says how much.  Without it
+                              an AUTO request runs the CUDA-core kernels              */
   uint64_t workspace_bytes;
   int32_t* status;
 } B200SdpaBwdParams;
@@ -286,8 +287,18 @@ int b200_sdpa_decode(const B200SdpaParams* params, void* stream);
 int b200_sdpa_decode_static(const B200SdpaParams* params, void* stream);
 
 /*
- * Enqueue the attention backward on `stream`: one kernel for grad_q (and grad_bias)
- * and one for grad_k / grad_v.  Head dims up to 256.
+ * Kernel family, launch geometry (grid_x: grad_q kernel, grid_y: grad_k/grad_v kernel)
+ * and scratch size of a backward request, without launching.  Host-only.
+ * `path` is B200_SDPA_PATH_PREFILL for the tcgen05 kernels (f16/bf16, E == Dv in
+ * {64,128}, no bias, unit inner strides, 16-byte aligned bases and outer strides of
+ * q, k, v, grad_out and the three gradients) and B200_SDPA_PATH_GENERIC otherwise.
+ */
+int b200_sdpa_bwd_query_plan(const B200SdpaBwdParams* params, B200SdpaPlan* plan);
+
+/*
+ * Enqueue the attention backward on `stream`: a grad_q kernel (which also writes
+ * grad_bias) and a grad_k / grad_v kernel, preceded on the tensor-core path by a small
+ * row-statistics kernel.  Head dims up to 256 on the CUDA-core path.
  * Upstream counterpart: the backward op's eager launch and CPU definition
  *   torch_neuronx/python_ops/scaled_dot_product_fused_attention.py:511-781
  *   torch_neuronx/csrc/core/dispatch/NeuronDispatcher.cpp:2523-2582 (DispatchSdpaBwdImpl)
@@ -303,7 +314,7 @@ int b200_sdpa_merge(const B200SdpaMergeParams* params, void* stream);
  * Upstream counterpart: executed-op tracking
  *   torch_neuronx/__init__.py:528-546, tests/utils/neuron_test_utils.py:18-135.
  * kernel ids: 0 generic, 1 prefill, 2 decode partial, 3 decode combine, 4 merge,
- * 5 backward grad_q, 6 backward grad_k/grad_v.
+ * 5 backward grad_q, 6 backward grad_k/grad_v, 7 backward row statistics.
  */
 uint64_t b200_sdpa_launch_count(int kernel_id);
 void b200_sdpa_reset_launch_counts(void);

@@ -36,7 +36,7 @@ def _names():
 
 
 def _cuda_backward(go, q, k, v, *, mask=None, is_causal=False, scale=None, kv_lens=None, need_grad_bias=False,
-                   out=None, lse=None, layout=None):
+                   out=None, lse=None, layout=None, force_path=0):
     """Forward (unless out/lse are given) and backward on the GPU; gradient buffers are
     NaN-poisoned first so that an unwritten element cannot pass."""
     import torch_neuronx_b200 as T
@@ -65,11 +65,15 @@ def _cuda_backward(go, q, k, v, *, mask=None, is_causal=False, scale=None, kv_le
     gv = torch.full_like(vc, float("nan"))
     T.reset_launch_counts()
     gq, gk, gv, gb = T.sdpa_backward(gc, qc, kc, vc, oc, lc, attn_bias=bias, is_causal=is_causal, scale=scale,
-                                     kv_lens=lens, need_grad_bias=need_grad_bias, grad_q=gq, grad_k=gk, grad_v=gv)
+                                     kv_lens=lens, need_grad_bias=need_grad_bias, grad_q=gq, grad_k=gk, grad_v=gv,
+                                     force_path=force_path)
     torch.cuda.synchronize()
     T.check_device_status()
     counts = T.launch_counts()
     assert counts["bwd_dq"] == 1 and counts["bwd_dkv"] == (1 if k.shape[2] > 0 else 0)
+    from torch_neuronx_b200 import ops as _ops
+    assert counts["bwd_prep"] == (1 if _ops.last_bwd_plan["path"] == "prefill" else 0)
+    _cuda_backward.path = _ops.last_bwd_plan["path"]
     assert gq.stride() == qc.stride() and gk.stride() == kc.stride() and gv.stride() == vc.stride()
     _cuda_backward.forward = (oc.cpu(), lc.cpu())
     return gq.cpu(), gk.cpu(), gv.cpu(), (gb.cpu() if gb is not None else None)
@@ -352,3 +356,73 @@ def test_ring_backward_with_virtual_ranks(layout, dtype):
         _close(ring.unshard_sequence([t.cpu() for t in got], layout), w, dtype, f"ring {layout} {n}",
                None if dtype == torch.float32 else dict(rtol=5e-2, atol=2e-2))
     assert calls == (world * (world + 1) // 2 if layout == "contiguous" else world * world + world)
+
+
+TC_SHAPES = [
+    # B, Hq, Hkv, L,    S,    D
+    (1, 2, 2, 128, 128, 128),
+    (2, 4, 2, 256, 384, 128),
+    (1, 8, 2, 130, 97, 128),      # ragged tails on both axes, grouped heads
+    (1, 4, 1, 333, 517, 64),      # multi-query, head dim 64
+    (2, 2, 2, 1, 300, 64),        # single query row
+    (1, 2, 2, 300, 1, 128),       # single key
+    (1, 4, 4, 1024, 1024, 128),   # eight tiles each way
+    (1, 8, 2, 640, 256, 64),      # more rows than keys
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("shape", TC_SHAPES)
+def test_tensor_core_backward_against_oracle(shape, causal, dtype):
+    from torch_neuronx_b200 import _lib
+
+    B, Hq, Hkv, L, S, D = shape
+    g = torch.Generator().manual_seed(sum(shape) + (3 if causal else 0))
+    q = torch.randn(B, Hq, L, D, generator=g).to(dtype)
+    k = torch.randn(B, Hkv, S, D, generator=g).to(dtype)
+    v = torch.randn(B, Hkv, S, D, generator=g).to(dtype)
+    go = torch.randn(B, Hq, L, D, generator=g).to(dtype)
+    got = _cuda_backward(go, q, k, v, is_causal=causal, force_path=_lib.PATH_PREFILL)
+    assert _cuda_backward.path == "prefill"
+    fwd = _cuda_backward.forward
+    want = _oracle_backward(go, q, k, v, forward=fwd, is_causal=causal)
+    ref = _cuda_backward(go, q, k, v, is_causal=causal, force_path=_lib.PATH_GENERIC, out=fwd[0], lse=fwd[1])
+    assert _cuda_backward.path == "generic"
+    for a, b, c, n in zip(got[:3], want[:3], ref[:3], ("dq", "dk", "dv")):
+        # P and dS are rounded to the 16-bit type before their second product: allow the
+        # forward's half-precision max-abs bar beside the relative term
+        _close(a, b, dtype, f"tc {shape} causal={causal} {n}", dict(rtol=5e-2, atol=2e-2))
+        err = (a.float() - b.float()).abs().mean().item()
+        assert err <= 2e-3 * max(1.0, b.float().abs().mean().item() * 10), f"{n}: mean-abs {err:.3e}"
+        _close(a, c, dtype, f"tc vs cuda-core {shape} causal={causal} {n}", dict(rtol=5e-2, atol=2e-2))
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_tensor_core_backward_ragged_lengths_and_transposed_storage(causal):
+    from torch_neuronx_b200 import _lib
+
+    g = torch.Generator().manual_seed(31)
+    B, Hq, Hkv, L, S, D = 3, 8, 2, 200, 260, 128
+    q = torch.randn(B, Hq, L, D, generator=g).to(torch.bfloat16)
+    k = torch.randn(B, Hkv, S, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(B, Hkv, S, D, generator=g).to(torch.bfloat16)
+    go = torch.randn(B, Hq, L, D, generator=g).to(torch.bfloat16)
+    lens = torch.tensor([260, 0, 131])
+    got = _cuda_backward(go, q, k, v, is_causal=causal, kv_lens=lens, layout="bshd", force_path=_lib.PATH_PREFILL)
+    want = _oracle_backward(go, q, k, v, forward=_cuda_backward.forward, is_causal=causal, kv_lens=lens)
+    for a, b, n in zip(got[:3], want[:3], ("dq", "dk", "dv")):
+        _close(a, b, torch.bfloat16, f"tc bshd kv_lens {n}", dict(rtol=5e-2, atol=2e-2))
+    assert all(torch.all(t[1] == 0) for t in got[:3])                                  # batch without keys
+    assert torch.all(got[1][2, :, 131:] == 0) and torch.all(got[2][2, :, 131:] == 0)   # padded keys
+
+
+def test_tensor_core_backward_is_deterministic():
+    from torch_neuronx_b200 import _lib
+
+    g = torch.Generator().manual_seed(77)
+    q, k, v, go = (torch.randn(1, 4, 512, 128, generator=g).to(torch.bfloat16) for _ in range(4))
+    a = _cuda_backward(go, q, k, v, is_causal=True, force_path=_lib.PATH_PREFILL)
+    b = _cuda_backward(go, q, k, v, is_causal=True, force_path=_lib.PATH_PREFILL, out=_cuda_backward.forward[0],
+                       lse=_cuda_backward.forward[1])
+    assert all(torch.equal(x, y) for x, y in zip(a[:3], b[:3]))

@@ -35,8 +35,8 @@ PATH_AUTO, PATH_GENERIC, PATH_PREFILL, PATH_DECODE = 0, 1, 2, 3
 PATH_NAMES = {PATH_AUTO: "auto", PATH_GENERIC: "generic", PATH_PREFILL: "prefill", PATH_DECODE: "decode"}
 
 # launch-counter ids
-KID_GENERIC, KID_PREFILL, KID_DECODE, KID_COMBINE, KID_MERGE, KID_BWD_DQ, KID_BWD_DKV = 0, 1, 2, 3, 4, 5, 6
-KERNEL_NAMES = ("generic", "prefill", "decode_partial", "decode_combine", "merge", "bwd_dq", "bwd_dkv")
+KID_GENERIC, KID_PREFILL, KID_DECODE, KID_COMBINE, KID_MERGE, KID_BWD_DQ, KID_BWD_DKV, KID_BWD_PREP = range(8)
+KERNEL_NAMES = ("generic", "prefill", "decode_partial", "decode_combine", "merge", "bwd_dq", "bwd_dkv", "bwd_prep")
 
 
 class Params(C.Structure):
@@ -128,7 +128,7 @@ class BwdParams(C.Structure):
         ("struct_size", C.c_uint32),
         ("dtype", C.c_int32),
         ("device", C.c_int32),
-        ("reserved", C.c_int32),
+        ("force_path", C.c_int32),
         ("grad_out", C.c_void_p),
         ("q", C.c_void_p),
         ("k", C.c_void_p),
@@ -178,6 +178,7 @@ EXPORTS = {
     "b200_sdpa_fwd": (C.c_int, [C.POINTER(Params), C.c_void_p]),
     "b200_sdpa_decode": (C.c_int, [C.POINTER(Params), C.c_void_p]),
     "b200_sdpa_decode_static": (C.c_int, [C.POINTER(Params), C.c_void_p]),
+    "b200_sdpa_bwd_query_plan": (C.c_int, [C.POINTER(BwdParams), C.POINTER(Plan)]),
     "b200_sdpa_bwd": (C.c_int, [C.POINTER(BwdParams), C.c_void_p]),
     "b200_sdpa_merge": (C.c_int, [C.POINTER(MergeParams), C.c_void_p]),
     "b200_sdpa_launch_count": (C.c_uint64, [C.c_int]),

@@ -94,6 +94,76 @@ int select_device(int device) {
   return B200_SDPA_OK;
 }
 
+int validate_bwd(const B200SdpaBwdParams* a, BwdProblem& bp) {
+  if (a == nullptr) return B200_SDPA_ERR_NULL;
+  if (a->struct_size != sizeof(B200SdpaBwdParams)) return B200_SDPA_ERR_STRUCT;
+  if (a->dtype != B200_SDPA_F32 && a->dtype != B200_SDPA_F16 && a->dtype != B200_SDPA_BF16) return B200_SDPA_ERR_DTYPE;
+  if (a->B <= 0 || a->Hq <= 0 || a->Hkv <= 0 || a->L <= 0 || a->S < 0 || a->E <= 0 || a->Dv <= 0)
+    return B200_SDPA_ERR_SHAPE;
+  if (a->Hq % a->Hkv != 0) return B200_SDPA_ERR_SHAPE;
+  if (a->grad_out == nullptr || a->q == nullptr || a->out == nullptr || a->lse == nullptr || a->grad_q == nullptr)
+    return B200_SDPA_ERR_NULL;
+  if (a->S > 0 && (a->k == nullptr || a->v == nullptr || a->grad_k == nullptr || a->grad_v == nullptr))
+    return B200_SDPA_ERR_NULL;
+  if (a->bias != nullptr && a->bias_dtype != B200_SDPA_F32 && a->bias_dtype != B200_SDPA_F16 &&
+      a->bias_dtype != B200_SDPA_BF16)
+    return B200_SDPA_ERR_DTYPE;
+  Problem& p = bp.f;
+  p.q = a->q;
+  p.k = a->k;
+  p.v = a->v;
+  p.out = const_cast<void*>(a->out);
+  p.lse = const_cast<float*>(a->lse);
+  bp.dout = a->grad_out;
+  bp.dq = a->grad_q;
+  bp.dk = a->grad_k;
+  bp.dv = a->grad_v;
+  bp.dbias = a->grad_bias;
+  for (int i = 0; i < 4; ++i) {
+    p.qs[i] = a->q_stride[i];
+    p.ks[i] = a->k_stride[i];
+    p.vs[i] = a->v_stride[i];
+    p.os[i] = a->out_stride[i];
+    p.bs[i] = a->bias_stride[i];
+    bp.dos[i] = a->grad_out_stride[i];
+    bp.dqs[i] = a->grad_q_stride[i];
+    bp.dks[i] = a->grad_k_stride[i];
+    bp.dvs[i] = a->grad_v_stride[i];
+    bp.dbs[i] = a->grad_bias_stride[i];
+  }
+  for (int i = 0; i < 3; ++i) p.ls[i] = a->lse_stride[i];
+  p.B = a->B;
+  p.Hq = a->Hq;
+  p.Hkv = a->Hkv;
+  p.L = a->L;
+  p.S = a->S;
+  p.E = a->E;
+  p.Dv = a->Dv;
+  p.group = a->Hq / a->Hkv;
+  p.scale = a->scale;
+  p.causal = a->is_causal != 0;
+  p.causal_shift = a->q_offset - a->k_offset;
+  p.kv_lens = a->kv_lens;
+  p.bias = a->bias;
+  p.bias_dtype = a->bias_dtype;
+  p.status = a->status;
+  if (a->force_path != B200_SDPA_PATH_AUTO && a->force_path != B200_SDPA_PATH_GENERIC &&
+      a->force_path != B200_SDPA_PATH_PREFILL)
+    return B200_SDPA_ERR_UNSUPPORTED;
+  return B200_SDPA_OK;
+}
+
+// Backward kernel family: tensor-core kernels when eligible (and, for a launch, when the
+// scratch is there), otherwise the CUDA-core kernels.
+int choose_bwd(const B200SdpaBwdParams* a, const BwdProblem& bp, int* path) {
+  bool align_only = false;
+  const bool tc_ok = bwd_tc_eligible(bp, a->dtype, &align_only);
+  if (a->force_path == B200_SDPA_PATH_PREFILL && !tc_ok)
+    return align_only ? B200_SDPA_ERR_ALIGNMENT : B200_SDPA_ERR_UNSUPPORTED;
+  *path = (a->force_path != B200_SDPA_PATH_GENERIC && tc_ok) ? B200_SDPA_PATH_PREFILL : B200_SDPA_PATH_GENERIC;
+  return B200_SDPA_OK;
+}
+
 }  // namespace
 
 void count_launch(int kernel_id) {
@@ -186,63 +256,34 @@ int b200_sdpa_decode_static(const B200SdpaParams* params, void* stream) {
   return launch_decode_static(p, params->dtype, params->kv_chunk, reinterpret_cast<cudaStream_t>(stream));
 }
 
-int b200_sdpa_bwd(const B200SdpaBwdParams* a, void* stream) {
-  if (a == nullptr) return B200_SDPA_ERR_NULL;
-  if (a->struct_size != sizeof(B200SdpaBwdParams)) return B200_SDPA_ERR_STRUCT;
-  if (a->dtype != B200_SDPA_F32 && a->dtype != B200_SDPA_F16 && a->dtype != B200_SDPA_BF16) return B200_SDPA_ERR_DTYPE;
-  if (a->B <= 0 || a->Hq <= 0 || a->Hkv <= 0 || a->L <= 0 || a->S < 0 || a->E <= 0 || a->Dv <= 0)
-    return B200_SDPA_ERR_SHAPE;
-  if (a->Hq % a->Hkv != 0) return B200_SDPA_ERR_SHAPE;
-  if (a->grad_out == nullptr || a->q == nullptr || a->out == nullptr || a->lse == nullptr || a->grad_q == nullptr)
-    return B200_SDPA_ERR_NULL;
-  if (a->S > 0 && (a->k == nullptr || a->v == nullptr || a->grad_k == nullptr || a->grad_v == nullptr))
-    return B200_SDPA_ERR_NULL;
-  if (a->bias != nullptr && a->bias_dtype != B200_SDPA_F32 && a->bias_dtype != B200_SDPA_F16 &&
-      a->bias_dtype != B200_SDPA_BF16)
-    return B200_SDPA_ERR_DTYPE;
+int b200_sdpa_bwd_query_plan(const B200SdpaBwdParams* a, B200SdpaPlan* plan) {
+  if (plan == nullptr) return B200_SDPA_ERR_NULL;
+  if (plan->struct_size != sizeof(B200SdpaPlan)) return B200_SDPA_ERR_STRUCT;
   BwdProblem bp;
-  Problem& p = bp.f;
-  p.q = a->q;
-  p.k = a->k;
-  p.v = a->v;
-  p.out = const_cast<void*>(a->out);
-  p.lse = const_cast<float*>(a->lse);
-  bp.dout = a->grad_out;
-  bp.dq = a->grad_q;
-  bp.dk = a->grad_k;
-  bp.dv = a->grad_v;
-  bp.dbias = a->grad_bias;
-  for (int i = 0; i < 4; ++i) {
-    p.qs[i] = a->q_stride[i];
-    p.ks[i] = a->k_stride[i];
-    p.vs[i] = a->v_stride[i];
-    p.os[i] = a->out_stride[i];
-    p.bs[i] = a->bias_stride[i];
-    bp.dos[i] = a->grad_out_stride[i];
-    bp.dqs[i] = a->grad_q_stride[i];
-    bp.dks[i] = a->grad_k_stride[i];
-    bp.dvs[i] = a->grad_v_stride[i];
-    bp.dbs[i] = a->grad_bias_stride[i];
-  }
-  for (int i = 0; i < 3; ++i) p.ls[i] = a->lse_stride[i];
-  p.B = a->B;
-  p.Hq = a->Hq;
-  p.Hkv = a->Hkv;
-  p.L = a->L;
-  p.S = a->S;
-  p.E = a->E;
-  p.Dv = a->Dv;
-  p.group = a->Hq / a->Hkv;
-  p.scale = a->scale;
-  p.causal = a->is_causal != 0;
-  p.causal_shift = a->q_offset - a->k_offset;
-  p.kv_lens = a->kv_lens;
-  p.bias = a->bias;
-  p.bias_dtype = a->bias_dtype;
-  p.status = a->status;
-  int rc = select_device(a->device);
+  int rc = validate_bwd(a, bp);
   if (rc != B200_SDPA_OK) return rc;
-  return launch_bwd_generic(bp, a->dtype, reinterpret_cast<cudaStream_t>(stream));
+  int path = 0;
+  rc = choose_bwd(a, bp, &path);
+  if (rc != B200_SDPA_OK) return rc;
+  return path == B200_SDPA_PATH_PREFILL ? plan_bwd_tc(bp, a->dtype, plan) : plan_bwd_generic(bp, a->dtype, plan);
+}
+
+int b200_sdpa_bwd(const B200SdpaBwdParams* a, void* stream) {
+  BwdProblem bp;
+  int rc = validate_bwd(a, bp);
+  if (rc != B200_SDPA_OK) return rc;
+  int path = 0;
+  rc = choose_bwd(a, bp, &path);
+  if (rc != B200_SDPA_OK) return rc;
+  rc = select_device(a->device);
+  if (rc != B200_SDPA_OK) return rc;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (path == B200_SDPA_PATH_PREFILL) {
+    rc = launch_bwd_tc(bp, a->dtype, a->workspace, a->workspace_bytes, st);
+    // without scratch an automatic choice falls through to the kernels that need none
+    if (rc != B200_SDPA_ERR_WORKSPACE || a->force_path == B200_SDPA_PATH_PREFILL) return rc;
+  }
+  return launch_bwd_generic(bp, a->dtype, st);
 }
 
 int b200_sdpa_merge(const B200SdpaMergeParams* m, void* stream) {

@@ -390,6 +390,27 @@ int launch_bwd_typed(const BwdProblem& bp, const BwdConfig& cfg, cudaStream_t st
 
 }  // namespace
 
+int plan_bwd_generic(const BwdProblem& bp, int dtype, B200SdpaPlan* plan) {
+  (void)dtype;
+  BwdConfig cfg;
+  if (!pick_bwd_config(bp.f, &cfg)) return B200_SDPA_ERR_UNSUPPORTED;
+  const Problem& p = bp.f;
+  const int64_t grid_q = static_cast<int64_t>((p.L + cfg.tile - 1) / cfg.tile) * p.Hq * p.B;
+  const int64_t grid_kv = static_cast<int64_t>((p.S + cfg.tile - 1) / cfg.tile) * p.Hkv * p.B;
+  if (grid_q > 0x7fffffffLL || grid_kv > 0x7fffffffLL) return B200_SDPA_ERR_UNSUPPORTED;
+  plan->path = B200_SDPA_PATH_GENERIC;
+  plan->block_m = plan->block_n = cfg.tile;
+  plan->grid_x = static_cast<int32_t>(grid_q);
+  plan->grid_y = static_cast<int32_t>(grid_kv);
+  plan->grid_z = 1;
+  plan->threads = kThreads;
+  plan->smem_bytes = cfg.smem_dkv;
+  plan->kv_splits = 1;
+  plan->launches = grid_kv > 0 ? 2 : 1;
+  plan->workspace_bytes = 0;
+  return B200_SDPA_OK;
+}
+
 int launch_bwd_generic(const BwdProblem& bp, int dtype, cudaStream_t stream) {
   BwdConfig cfg;
   if (!pick_bwd_config(bp.f, &cfg)) return B200_SDPA_ERR_UNSUPPORTED;

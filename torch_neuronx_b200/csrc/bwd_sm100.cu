@@ -1,0 +1,726 @@
+// Tensor-core backward for sm_100a: TMA -> shared memory -> tcgen05 with every
+// accumulator and every 16-bit intermediate (P, dS) in tensor memory.
+//
+// Three launches, no atomics, no [L,S] matrix in HBM:
+//   bwd_prep_kernel     delta[b,h,i] = sum_d dO*out and the forward's log-sum-exp in log2
+//                       units (rows without a visible key, and pad rows, get +inf so that
+//                       their rebuilt probabilities are exactly 0)
+//   bwd_dq_tc_kernel    one CTA per 128 query rows of one head; walks the key tiles:
+//                         S = Q K^T, dP = dO V^T            (SS MMAs, accumulators in TMEM)
+//                         dS = exp2(S*c - lse2) * (dP - delta)   -> 16-bit, over dP in TMEM
+//                         dQ += dS K                         (TS MMA: A operand from TMEM)
+//   bwd_dkv_tc_kernel   one CTA per 128 keys of one kv head; walks the group's query heads
+//                       and their row tiles in the transposed orientation (TMEM lane = key):
+//                         S^T = K Q^T, dP^T = V dO^T
+//                         P^T -> over S^T, dS^T -> over dP^T (16-bit, in TMEM)
+//                         dV += P^T dO, dK += dS^T Q         (TS MMAs)
+//                       so the grouped-query sum is part of the accumulation.
+// The two main kernels recompute S and dP independently (7 tile products instead of 5);
+// in exchange dQ needs neither atomics nor an fp32 scratch tensor, and results are
+// deterministic.  Arithmetic: torch_neuronx/_sdpa_math.py:133-176 with P and dS rounded
+// to the input dtype before their second product (upstream rounds P the same way in the
+// forward, :94).  Roles per CTA (192 threads): warps 0-3 elementwise (one thread per TMEM
+// lane), warp 4 TMA producer, warp 5 MMA issuer.  Every wait is bounded (see tc_common.cuh).
+#include "tc_common.cuh"
+
+namespace b200 {
+
+namespace {
+
+using namespace ptx;
+using namespace tc;
+
+constexpr int kT = 128;                 // tile edge: query rows, keys, TMEM lanes
+constexpr int kThreads = 192;
+constexpr int kProducerWarp = 4;
+constexpr int kMmaWarp = 5;
+constexpr uint32_t kTmemCols = 512;
+constexpr int kMaxStages = 4;
+
+template <int D> struct BCfg {
+  static constexpr int kBoxes = D / 64;
+  static constexpr int kTileBytes = kT * D * 2;
+  static constexpr int kStages = (D == 128) ? 2 : 4;           // ring slots of two tiles each
+  static constexpr int kSmemTiles = (2 + 2 * kStages) * kTileBytes;
+  static constexpr int kStatBytes = kStages * 2 * kT * 4;       // (lse2, delta) of a query tile per slot
+  static constexpr int kSmemBytes = kSmemTiles + kStatBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+struct BSync {
+  uint64_t fixed_full;
+  uint64_t ring_full[kMaxStages];
+  uint64_t ring_empty[kMaxStages];
+  uint64_t sp_full;     // both score-shaped accumulators of an iteration are complete
+  uint64_t e_ready;     // the elementwise role has written its 16-bit operands
+  uint64_t acc_done;    // last accumulating MMA has retired
+  uint64_t staged;
+  uint64_t drain;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+// ------------------------------------------------------------------ prep --
+
+template <typename T>
+__global__ void bwd_prep_kernel(const BwdProblem bp, float* __restrict__ lse2, float* __restrict__ delta,
+                                const int l_pad) {
+  const Problem& p = bp.f;
+  const long long warp_id = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long total = static_cast<long long>(p.B) * p.Hq * l_pad;
+  if (warp_id >= total) return;
+  const int i = static_cast<int>(warp_id % l_pad);
+  const long long bh = warp_id / l_pad;
+  const int h = static_cast<int>(bh % p.Hq);
+  const int b = static_cast<int>(bh / p.Hq);
+  float d = 0.f, l2 = CUDART_INF_F;
+  if (i < p.L) {
+    const T* __restrict__ go = reinterpret_cast<const T*>(bp.dout) + b * bp.dos[0] + h * bp.dos[1] + i * bp.dos[2];
+    const T* __restrict__ o = reinterpret_cast<const T*>(p.out) + b * p.os[0] + h * p.os[1] + i * p.os[2];
+    for (int e = lane; e < p.Dv; e += 32) d = fmaf(to_f32<T>(go[e * bp.dos[3]]), to_f32<T>(o[e * p.os[3]]), d);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
+    const float l = p.lse[b * p.ls[0] + h * p.ls[1] + i * p.ls[2]];
+    l2 = (l == -CUDART_INF_F) ? CUDART_INF_F : l * kLog2e;
+  }
+  if (lane == 0) {
+    lse2[warp_id] = l2;
+    delta[warp_id] = d;
+  }
+}
+
+// --------------------------------------------------------------- shared bits --
+
+// K-major operand descriptor of a 128-row tile; k-step kk covers 16 elements of D.
+__device__ __forceinline__ uint64_t kmajor_desc(uint32_t tile) { return smem_desc_sw128(tile, 16, 1024); }
+__device__ __forceinline__ uint64_t kmajor_step(int kk) {
+  return static_cast<uint64_t>(((kk >> 2) * kBoxBytes + (kk & 3) * 32) >> 4);
+}
+// MN-major B operand descriptor of the same tile (rows are the contraction axis);
+// k-step kk covers 16 rows.
+__device__ __forceinline__ uint64_t mnmajor_desc(uint32_t tile) { return smem_desc_sw128(tile, kBoxBytes, 1024); }
+__device__ __forceinline__ uint64_t mnmajor_step(int kk) { return static_cast<uint64_t>(kk * (2048 >> 4)); }
+
+// acc[tmem d] = A[smem, K-major] * B[smem, K-major]^T over D
+template <int D>
+__device__ __forceinline__ void issue_ss(uint32_t d_tmem, uint32_t a_tile, uint32_t b_tile, uint32_t idesc) {
+  const uint64_t ad = kmajor_desc(a_tile), bd = kmajor_desc(b_tile);
+  if (elect_one()) {
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) mma_ss(d_tmem, ad + kmajor_step(kk), bd + kmajor_step(kk), idesc, kk > 0 ? 1u : 0u);
+  }
+}
+// acc[tmem d] (+)= A[tmem, 16-bit pairs in 64 columns] * B[smem tile, MN-major] over the tile's 128 rows
+__device__ __forceinline__ void issue_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_tile, uint32_t idesc,
+                                         bool accumulate) {
+  const uint64_t bd = mnmajor_desc(b_tile);
+  if (elect_one()) {
+#pragma unroll
+    for (int kk = 0; kk < kT / 16; ++kk)
+      mma_ts(d_tmem, a_tmem + static_cast<uint32_t>(kk * 8), bd + mnmajor_step(kk), idesc, (kk > 0 || accumulate) ? 1u : 0u);
+  }
+}
+
+// One thread's accumulator row (TMEM lane) -> 16-bit -> the 128-byte-swizzled staging
+// tile a TMA store expects.
+template <int D, bool BF16>
+__device__ __forceinline__ void stage_row(uint32_t acc_addr, bool have_acc, float mul, uint8_t* stage, int r) {
+#pragma unroll
+  for (int c = 0; c < D / 32; ++c) {
+    uint32_t v[32];
+    if (have_acc) {
+      tmem_ld_32x32(acc_addr + c * 32, v);
+      tmem_ld_wait();
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = 0u;
+    }
+    uint32_t pk[16];
+#pragma unroll
+    for (int i = 0; i < 32; i += 2)
+      pk[i >> 1] = pack2<BF16>(__uint_as_float(v[i]) * mul, __uint_as_float(v[i + 1]) * mul);
+    uint8_t* box = stage + (c >> 1) * kBoxBytes + r * 128;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int unit = ((c & 1) * 4 + u) ^ (r & 7);
+      *reinterpret_cast<uint4*>(box + unit * 16) = make_uint4(pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
+    }
+  }
+}
+
+__device__ __forceinline__ void init_common_barriers(BSync* sync) {
+  mbar_init(smem_u32(&sync->sp_full), 1);
+  mbar_init(smem_u32(&sync->e_ready), kT);
+  mbar_init(smem_u32(&sync->acc_done), 1);
+  mbar_init(smem_u32(&sync->staged), kT);
+  mbar_init(smem_u32(&sync->drain), 1);
+  sync->abort_flag = 0;
+  mbar_fence_init();
+}
+
+__device__ __forceinline__ void drain_after_abort(BSync* sync, long long wait_limit) {
+  // let whatever was issued retire before tensor memory is released
+  if (elect_one()) mma_commit(smem_u32(&sync->drain));
+  const long long t0 = clock64();
+  while (!mbar_try_wait(smem_u32(&sync->drain), 0) && clock64() - t0 < wait_limit) {
+  }
+}
+
+// ------------------------------------------------------------------ dQ kernel --
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(kThreads, 1)
+bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+                 const __grid_constant__ CUtensorMap tm_dq, const Problem p, const float* __restrict__ lse2,
+                 const float* __restrict__ delta, const int l_pad, const int n_qblk, const long long wait_limit) {
+  using C = BCfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t tiles = (raw_addr + 1023u) & ~1023u;
+  BSync* sync = reinterpret_cast<BSync*>(smem_raw + (tiles - raw_addr) + C::kSmemTiles + C::kStatBytes);
+  volatile int* abort_flag = &sync->abort_flag;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+
+  // latest query blocks (most key tiles under a causal mask) first
+  const int per_blk = p.Hq * p.B;
+  const int qblk = n_qblk - 1 - static_cast<int>(blockIdx.x / per_blk);
+  const int rem = static_cast<int>(blockIdx.x % per_blk);
+  const int h = rem % p.Hq;
+  const int b = rem / p.Hq;
+  const int hk = h / p.group;
+  const int row0 = qblk * kT;
+  const int kv_limit = valid_keys(p, b);
+  long long end = kv_limit, first = kv_limit;
+  if (p.causal) {
+    const int last_row = (row0 + kT < p.L ? row0 + kT : p.L) - 1;
+    const long long e = static_cast<long long>(last_row) + p.causal_shift + 1;
+    const long long f = static_cast<long long>(row0) + p.causal_shift + 1;
+    end = e < end ? e : end;
+    first = f < first ? f : first;
+  }
+  if (end < 0) end = 0;
+  if (first < -1) first = -1;
+  const int n_tiles = static_cast<int>((end + kT - 1) / kT);
+  const int min_lim = static_cast<int>(first);
+
+  const uint32_t q_tile = tiles, do_tile = tiles + C::kTileBytes;
+  const uint32_t ring = tiles + 2 * C::kTileBytes;   // slot s: K at ring + 2 s tile, V right after
+
+  if (warp == kProducerWarp && lane == 0) {
+    mbar_init(smem_u32(&sync->fixed_full), 1);
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(smem_u32(&sync->ring_full[s]), 1);
+      mbar_init(smem_u32(&sync->ring_empty[s]), 1);
+    }
+    mbar_fence_init();
+    if (n_tiles > 0) {
+      const uint32_t bar = smem_u32(&sync->fixed_full);
+      mbar_arrive_expect_tx(bar, 2 * C::kTileBytes);
+      for (int bx = 0; bx < C::kBoxes; ++bx) {
+        tma_load_4d(q_tile + bx * kBoxBytes, &tm_q, bar, bx * 64, row0, h, b);
+        tma_load_4d(do_tile + bx * kBoxBytes, &tm_do, bar, bx * 64, row0, h, b);
+      }
+    }
+    prefetch_tmap(&tm_dq);
+  }
+  if (tid == 0) init_common_barriers(sync);
+  if (warp == kMmaWarp) {
+    tmem_alloc(smem_u32(&sync->tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = sync->tmem_base;
+  constexpr uint32_t kColS = 0, kColDP = 128, kColDQ = 256;
+
+  if (warp == kProducerWarp) {
+    if (lane == 0) {
+      for (int j = 0; j < n_tiles; ++j) {
+        const int stage = j % C::kStages;
+        const uint32_t round = static_cast<uint32_t>(j / C::kStages);
+        if (round > 0 && !wait_clocked(smem_u32(&sync->ring_empty[stage]), (round - 1) & 1u, abort_flag, wait_limit)) {
+          report(p.status, 11, j, stage);
+          break;
+        }
+        const uint32_t bar = smem_u32(&sync->ring_full[stage]);
+        const uint32_t dst = ring + stage * 2 * C::kTileBytes;
+        mbar_arrive_expect_tx(bar, 2 * C::kTileBytes);
+        for (int bx = 0; bx < C::kBoxes; ++bx) {
+          tma_load_4d(dst + bx * kBoxBytes, &tm_k, bar, bx * 64, j * kT, hk, b);
+          tma_load_4d(dst + C::kTileBytes + bx * kBoxBytes, &tm_v, bar, bx * 64, j * kT, hk, b);
+        }
+      }
+      if (*abort_flag != 0) {
+        for (int i = 0; i < 200; ++i) __nanosleep(1000);   // copies in flight must land before exit
+      }
+    }
+    __syncwarp();
+  } else if (warp == kMmaWarp) {
+    constexpr uint32_t idesc_score = make_idesc(BF16, false, kT, kT);
+    constexpr uint32_t idesc_acc = make_idesc(BF16, true, kT, D);
+    bool alive = n_tiles > 0;
+    if (alive) {
+      alive = wait_clocked(smem_u32(&sync->fixed_full), 0, abort_flag, wait_limit);
+      if (!alive && lane == 0) report(p.status, 12, -1, 0);
+    }
+    for (int j = 0; j < n_tiles && alive; ++j) {
+      const int stage = j % C::kStages;
+      const uint32_t round = static_cast<uint32_t>(j / C::kStages);
+      alive = wait_clocked(smem_u32(&sync->ring_full[stage]), round & 1u, abort_flag, wait_limit);
+      if (!alive) {
+        if (lane == 0) report(p.status, 12, j, stage);
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t k_tile = ring + stage * 2 * C::kTileBytes, v_tile = k_tile + C::kTileBytes;
+      issue_ss<D>(tmem_base + kColS, q_tile, k_tile, idesc_score);
+      issue_ss<D>(tmem_base + kColDP, do_tile, v_tile, idesc_score);
+      if (elect_one()) mma_commit(smem_u32(&sync->sp_full));
+      alive = wait_clocked(smem_u32(&sync->e_ready), j & 1, abort_flag, wait_limit);
+      if (!alive) {
+        if (lane == 0) report(p.status, 13, j, 0);
+        break;
+      }
+      tc_fence_after_sync();
+      issue_ts(tmem_base + kColDQ, tmem_base + kColDP, k_tile, idesc_acc, j > 0);
+      if (elect_one()) {
+        mma_commit(smem_u32(&sync->ring_empty[stage]));
+        if (j + 1 == n_tiles) mma_commit(smem_u32(&sync->acc_done));
+      }
+    }
+    if (*abort_flag != 0) drain_after_abort(sync, wait_limit);
+    __syncwarp();
+  } else {
+    // -------------------------------------------------------- elementwise role
+    const int r = tid;                         // query row inside the tile = TMEM lane
+    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t s_addr = tmem_base + lane_off + kColS;
+    const uint32_t dp_addr = tmem_base + lane_off + kColDP;
+    const uint32_t dq_addr = tmem_base + lane_off + kColDQ;
+    const int row_g = row0 + r;
+    int lim = kv_limit;
+    if (p.causal) {
+      const long long c = static_cast<long long>(row_g) + p.causal_shift + 1;
+      lim = c < lim ? static_cast<int>(c < 0 ? 0 : c) : lim;
+    }
+    const long long stat_idx = (static_cast<long long>(b) * p.Hq + h) * l_pad + row_g;
+    const float neg_l2 = -lse2[stat_idx];      // -inf for rows without a visible key
+    const float dl = delta[stat_idx];
+    const float sl2 = p.scale * kLog2e;
+    bool alive = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      bool ok = wait_clocked(smem_u32(&sync->sp_full), j & 1, abort_flag, wait_limit);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) report(p.status, 14, j, warp);
+        alive = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const int col0 = j * kT;
+      const bool need_mask = col0 + kT > min_lim;
+#pragma unroll
+      for (int c = 0; c < kT / 32; ++c) {
+        uint32_t sv[32], dv[32];
+        tmem_ld_32x32(s_addr + c * 32, sv);
+        tmem_ld_32x32(dp_addr + c * 32, dv);
+        tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float p0 = ex2(fmaf(__uint_as_float(sv[i]), sl2, neg_l2));
+          float p1 = ex2(fmaf(__uint_as_float(sv[i + 1]), sl2, neg_l2));
+          if (need_mask) {
+            p0 = (col0 + c * 32 + i < lim) ? p0 : 0.f;
+            p1 = (col0 + c * 32 + i + 1 < lim) ? p1 : 0.f;
+          }
+          pk[i >> 1] = pack2<BF16>(p0 * (__uint_as_float(dv[i]) - dl), p1 * (__uint_as_float(dv[i + 1]) - dl));
+        }
+        // 16 packed columns land on dP columns this thread has already read
+        tmem_st_32x16(dp_addr + c * 16, pk);
+      }
+      tmem_st_wait();
+      tc_fence_before_sync();
+      mbar_arrive(smem_u32(&sync->e_ready));
+    }
+    if (alive && n_tiles > 0) {
+      bool ok = wait_clocked(smem_u32(&sync->acc_done), 0, abort_flag, wait_limit);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) report(p.status, 15, 0, warp);
+        alive = false;
+      }
+      tc_fence_after_sync();
+    }
+    if (alive) {
+      uint8_t* stage = smem_raw + (q_tile - raw_addr);   // Q is no longer needed
+      stage_row<D, BF16>(dq_addr, n_tiles > 0, p.scale, stage, r);
+      fence_proxy_async_smem();
+      mbar_arrive(smem_u32(&sync->staged));
+      if (r == 0 && wait_clocked(smem_u32(&sync->staged), 0, abort_flag, wait_limit)) {
+        for (int bx = 0; bx < C::kBoxes; ++bx) tma_store_4d(&tm_dq, q_tile + bx * kBoxBytes, bx * 64, row0, h, b);
+        tma_store_commit();
+        tma_store_wait_all();
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == kMmaWarp) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// --------------------------------------------------------------- dK/dV kernel --
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(kThreads, 1)
+bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                  const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+                  const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv,
+                  const Problem p, const float* __restrict__ lse2, const float* __restrict__ delta, const int l_pad,
+                  const int n_kblk, const long long wait_limit) {
+  using C = BCfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t tiles = (raw_addr + 1023u) & ~1023u;
+  float* stats = reinterpret_cast<float*>(smem_raw + (tiles - raw_addr) + C::kSmemTiles);
+  BSync* sync = reinterpret_cast<BSync*>(smem_raw + (tiles - raw_addr) + C::kSmemTiles + C::kStatBytes);
+  volatile int* abort_flag = &sync->abort_flag;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+
+  // earliest key blocks (seen by the most query tiles under a causal mask) first
+  const int per_blk = p.Hkv * p.B;
+  const int kblk = static_cast<int>(blockIdx.x / per_blk);
+  const int rem = static_cast<int>(blockIdx.x % per_blk);
+  const int hk = rem % p.Hkv;
+  const int b = rem / p.Hkv;
+  const int j0 = kblk * kT;
+  const int n_keys = valid_keys(p, b);
+  const int n_qt = (p.L + kT - 1) / kT;
+  int i_first = 0;
+  if (p.causal) {
+    const long long f = static_cast<long long>(j0) - p.causal_shift;   // first row that sees key j0
+    i_first = f <= 0 ? 0 : (f >= p.L ? n_qt : static_cast<int>(f / kT));
+  }
+  const int per_head = (j0 < n_keys && n_qt > i_first) ? n_qt - i_first : 0;
+  const int n_items = per_head * p.group;
+
+  const uint32_t k_tile = tiles, v_tile = tiles + C::kTileBytes;
+  const uint32_t ring = tiles + 2 * C::kTileBytes;   // slot s: Q at ring + 2 s tile, dO right after
+
+  if (warp == kProducerWarp && lane == 0) {
+    mbar_init(smem_u32(&sync->fixed_full), 1);
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(smem_u32(&sync->ring_full[s]), 1);
+      mbar_init(smem_u32(&sync->ring_empty[s]), 1);
+    }
+    mbar_fence_init();
+    if (n_items > 0) {
+      const uint32_t bar = smem_u32(&sync->fixed_full);
+      mbar_arrive_expect_tx(bar, 2 * C::kTileBytes);
+      for (int bx = 0; bx < C::kBoxes; ++bx) {
+        tma_load_4d(k_tile + bx * kBoxBytes, &tm_k, bar, bx * 64, j0, hk, b);
+        tma_load_4d(v_tile + bx * kBoxBytes, &tm_v, bar, bx * 64, j0, hk, b);
+      }
+    }
+    prefetch_tmap(&tm_dk);
+    prefetch_tmap(&tm_dv);
+  }
+  if (tid == 0) init_common_barriers(sync);
+  if (warp == kMmaWarp) {
+    tmem_alloc(smem_u32(&sync->tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = sync->tmem_base;
+  constexpr uint32_t kColS = 0, kColDP = 128, kColDV = 256, kColDK = 256 + D;
+
+  if (warp == kProducerWarp) {
+    // the whole warp runs the loop: the lanes copy the query tile's row statistics into
+    // the slot, lane 0 then arms the barrier (its release makes the copies visible) and
+    // starts the tile copies
+    bool alive = true;
+    for (int it = 0; it < n_items && alive; ++it) {
+      const int stage = it % C::kStages;
+      const uint32_t round = static_cast<uint32_t>(it / C::kStages);
+      if (round > 0) {
+        alive = wait_clocked(smem_u32(&sync->ring_empty[stage]), (round - 1) & 1u, abort_flag, wait_limit);
+        alive = __all_sync(0xffffffffu, alive);
+        if (!alive) {
+          if (lane == 0) report(p.status, 21, it, stage);
+          break;
+        }
+      }
+      const int h = hk * p.group + it / per_head;
+      const int qrow0 = (i_first + it % per_head) * kT;
+      const long long src = (static_cast<long long>(b) * p.Hq + h) * l_pad + qrow0;
+      float4* dst = reinterpret_cast<float4*>(stats + stage * 2 * kT);
+      dst[lane] = reinterpret_cast<const float4*>(lse2 + src)[lane];
+      dst[32 + lane] = reinterpret_cast<const float4*>(delta + src)[lane];
+      __syncwarp();
+      if (lane == 0) {
+        const uint32_t bar = smem_u32(&sync->ring_full[stage]);
+        const uint32_t q_dst = ring + stage * 2 * C::kTileBytes;
+        mbar_arrive_expect_tx(bar, 2 * C::kTileBytes);
+        for (int bx = 0; bx < C::kBoxes; ++bx) {
+          tma_load_4d(q_dst + bx * kBoxBytes, &tm_q, bar, bx * 64, qrow0, h, b);
+          tma_load_4d(q_dst + C::kTileBytes + bx * kBoxBytes, &tm_do, bar, bx * 64, qrow0, h, b);
+        }
+      }
+    }
+    if (*abort_flag != 0 && lane == 0) {
+      for (int i = 0; i < 200; ++i) __nanosleep(1000);
+    }
+    __syncwarp();
+  } else if (warp == kMmaWarp) {
+    constexpr uint32_t idesc_score = make_idesc(BF16, false, kT, kT);
+    constexpr uint32_t idesc_acc = make_idesc(BF16, true, kT, D);
+    bool alive = n_items > 0;
+    if (alive) {
+      alive = wait_clocked(smem_u32(&sync->fixed_full), 0, abort_flag, wait_limit);
+      if (!alive && lane == 0) report(p.status, 22, -1, 0);
+    }
+    for (int it = 0; it < n_items && alive; ++it) {
+      const int stage = it % C::kStages;
+      const uint32_t round = static_cast<uint32_t>(it / C::kStages);
+      alive = wait_clocked(smem_u32(&sync->ring_full[stage]), round & 1u, abort_flag, wait_limit);
+      if (!alive) {
+        if (lane == 0) report(p.status, 22, it, stage);
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t q_tile = ring + stage * 2 * C::kTileBytes, do_tile = q_tile + C::kTileBytes;
+      issue_ss<D>(tmem_base + kColS, k_tile, q_tile, idesc_score);     // S^T  = K Q^T
+      issue_ss<D>(tmem_base + kColDP, v_tile, do_tile, idesc_score);   // dP^T = V dO^T
+      if (elect_one()) mma_commit(smem_u32(&sync->sp_full));
+      alive = wait_clocked(smem_u32(&sync->e_ready), it & 1, abort_flag, wait_limit);
+      if (!alive) {
+        if (lane == 0) report(p.status, 23, it, 0);
+        break;
+      }
+      tc_fence_after_sync();
+      issue_ts(tmem_base + kColDV, tmem_base + kColS, do_tile, idesc_acc, it > 0);   // dV += P^T dO
+      issue_ts(tmem_base + kColDK, tmem_base + kColDP, q_tile, idesc_acc, it > 0);   // dK += dS^T Q
+      if (elect_one()) {
+        mma_commit(smem_u32(&sync->ring_empty[stage]));
+        if (it + 1 == n_items) mma_commit(smem_u32(&sync->acc_done));
+      }
+    }
+    if (*abort_flag != 0) drain_after_abort(sync, wait_limit);
+    __syncwarp();
+  } else {
+    // -------------------------------------------------------- elementwise role
+    const int r = tid;                         // key inside the tile = TMEM lane
+    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t s_addr = tmem_base + lane_off + kColS;
+    const uint32_t dp_addr = tmem_base + lane_off + kColDP;
+    const int key_g = j0 + r;
+    // query rows i >= i_min see this key; a padded key is seen by nobody
+    int i_min = 0;
+    if (p.causal) {
+      const long long v = static_cast<long long>(key_g) - p.causal_shift;
+      i_min = v < 0 ? 0 : (v > (1 << 30) ? (1 << 30) : static_cast<int>(v));
+    }
+    if (key_g >= n_keys) i_min = 1 << 30;
+    const bool tile_has_padding = j0 + kT > n_keys;
+    const float sl2 = p.scale * kLog2e;
+    bool alive = true;
+    for (int it = 0; it < n_items; ++it) {
+      bool ok = wait_clocked(smem_u32(&sync->sp_full), it & 1, abort_flag, wait_limit);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) report(p.status, 24, it, warp);
+        alive = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const int stage = it % C::kStages;
+      const int qrow0 = (i_first + it % per_head) * kT;
+      const float4* st4 = reinterpret_cast<const float4*>(stats + stage * 2 * kT);
+      // some key of this tile hides some row of this query tile
+      const bool need_mask = tile_has_padding ||
+                             (p.causal && static_cast<long long>(qrow0) < static_cast<long long>(j0) + kT - 1 - p.causal_shift);
+#pragma unroll
+      for (int c = 0; c < kT / 32; ++c) {
+        uint32_t sv[32], dv[32];
+        tmem_ld_32x32(s_addr + c * 32, sv);
+        tmem_ld_32x32(dp_addr + c * 32, dv);
+        tmem_ld_wait();
+        uint32_t pkp[16], pkd[16];
+#pragma unroll
+        for (int q4 = 0; q4 < 8; ++q4) {
+          const float4 l4 = st4[c * 8 + q4];
+          const float4 d4 = st4[32 + c * 8 + q4];
+          const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
+          const float ds_[4] = {d4.x, d4.y, d4.z, d4.w};
+          float pr[4], dsv[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int i = q4 * 4 + e;
+            float pe = ex2(fmaf(__uint_as_float(sv[i]), sl2, -ls[e]));
+            if (need_mask) pe = (qrow0 + c * 32 + i >= i_min) ? pe : 0.f;
+            pr[e] = pe;
+            dsv[e] = pe * (__uint_as_float(dv[i]) - ds_[e]);
+          }
+          pkp[q4 * 2] = pack2<BF16>(pr[0], pr[1]);
+          pkp[q4 * 2 + 1] = pack2<BF16>(pr[2], pr[3]);
+          pkd[q4 * 2] = pack2<BF16>(dsv[0], dsv[1]);
+          pkd[q4 * 2 + 1] = pack2<BF16>(dsv[2], dsv[3]);
+        }
+        tmem_st_32x16(s_addr + c * 16, pkp);
+        tmem_st_32x16(dp_addr + c * 16, pkd);
+      }
+      tmem_st_wait();
+      tc_fence_before_sync();
+      mbar_arrive(smem_u32(&sync->e_ready));
+    }
+    if (alive && n_items > 0) {
+      bool ok = wait_clocked(smem_u32(&sync->acc_done), 0, abort_flag, wait_limit);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) report(p.status, 25, 0, warp);
+        alive = false;
+      }
+      tc_fence_after_sync();
+    }
+    if (alive) {
+      // ring slot 0 is idle by now: its two tiles stage dK and dV
+      uint8_t* stage_k = smem_raw + (ring - raw_addr);
+      uint8_t* stage_v = stage_k + C::kTileBytes;
+      stage_row<D, BF16>(tmem_base + lane_off + kColDK, n_items > 0, p.scale, stage_k, r);
+      stage_row<D, BF16>(tmem_base + lane_off + kColDV, n_items > 0, 1.f, stage_v, r);
+      fence_proxy_async_smem();
+      mbar_arrive(smem_u32(&sync->staged));
+      if (r == 0 && wait_clocked(smem_u32(&sync->staged), 0, abort_flag, wait_limit)) {
+        for (int bx = 0; bx < C::kBoxes; ++bx) {
+          tma_store_4d(&tm_dk, ring + bx * kBoxBytes, bx * 64, j0, hk, b);
+          tma_store_4d(&tm_dv, ring + C::kTileBytes + bx * kBoxBytes, bx * 64, j0, hk, b);
+        }
+        tma_store_commit();
+        tma_store_wait_all();
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == kMmaWarp) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------ host side --
+
+int padded_rows(const Problem& p) { return (p.L + kT - 1) / kT * kT; }
+
+template <int D, bool BF16>
+int launch_tc(const BwdProblem& bp, float* lse2, float* delta, cudaStream_t stream) {
+  using C = BCfg<D>;
+  const Problem& p = bp.f;
+  CUtensorMap tq, tk, tv, tdo, tdq, tdk, tdv;
+  if (!make_map(&tq, p.q, BF16, D, p.L, p.Hq, p.B, p.qs) || !make_map(&tk, p.k, BF16, D, p.S, p.Hkv, p.B, p.ks) ||
+      !make_map(&tv, p.v, BF16, D, p.S, p.Hkv, p.B, p.vs) || !make_map(&tdo, bp.dout, BF16, D, p.L, p.Hq, p.B, bp.dos) ||
+      !make_map(&tdq, bp.dq, BF16, D, p.L, p.Hq, p.B, bp.dqs) ||
+      !make_map(&tdk, bp.dk, BF16, D, p.S, p.Hkv, p.B, bp.dks) ||
+      !make_map(&tdv, bp.dv, BF16, D, p.S, p.Hkv, p.B, bp.dvs))
+    return B200_SDPA_ERR_CUDA;
+  auto kq = bwd_dq_tc_kernel<D, BF16>;
+  auto kkv = bwd_dkv_tc_kernel<D, BF16>;
+  if (cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess ||
+      cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess) {
+    cudaGetLastError();
+    return B200_SDPA_ERR_CUDA;
+  }
+  const int l_pad = padded_rows(p);
+  {
+    const long long warps = static_cast<long long>(p.B) * p.Hq * l_pad;
+    const long long blocks = (warps * 32 + 255) / 256;
+    if (blocks > 0x7fffffffLL) return B200_SDPA_ERR_UNSUPPORTED;
+    if (BF16) {
+      bwd_prep_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(bp, lse2, delta, l_pad);
+    } else {
+      bwd_prep_kernel<__half><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(bp, lse2, delta, l_pad);
+    }
+    if (cudaGetLastError() != cudaSuccess) return B200_SDPA_ERR_CUDA;
+    count_launch(KID_BWD_PREP);
+  }
+  const int n_qblk = (p.L + kT - 1) / kT, n_kblk = (p.S + kT - 1) / kT;
+  const long long grid_q = static_cast<long long>(n_qblk) * p.Hq * p.B;
+  const long long grid_kv = static_cast<long long>(n_kblk) * p.Hkv * p.B;
+  if (grid_q > 0x7fffffffLL || grid_kv > 0x7fffffffLL) return B200_SDPA_ERR_UNSUPPORTED;
+  const long long limit = wait_limit_cycles();
+  kq<<<static_cast<unsigned>(grid_q), kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, tdq, p, lse2, delta, l_pad,
+                                                                        n_qblk, limit);
+  if (cudaGetLastError() != cudaSuccess) return B200_SDPA_ERR_CUDA;
+  count_launch(KID_BWD_DQ);
+  kkv<<<static_cast<unsigned>(grid_kv), kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, tdk, tdv, p, lse2, delta,
+                                                                          l_pad, n_kblk, limit);
+  if (cudaGetLastError() != cudaSuccess) return B200_SDPA_ERR_CUDA;
+  count_launch(KID_BWD_DKV);
+  return B200_SDPA_OK;
+}
+
+}  // namespace
+
+bool bwd_tc_eligible(const BwdProblem& bp, int dtype, bool* alignment_only_failure) {
+  const Problem& p = bp.f;
+  if (alignment_only_failure) *alignment_only_failure = false;
+  if (dtype != B200_SDPA_F16 && dtype != B200_SDPA_BF16) return false;
+  if (p.E != p.Dv || (p.E != 64 && p.E != 128)) return false;
+  if (p.bias != nullptr || bp.dbias != nullptr) return false;
+  if (!(p.scale > 0.f) || !(p.scale < 1e30f)) return false;
+  if (p.L < 1 || p.S < 1) return false;
+  const bool ok = strides_ok(p.q, p.qs, p.L, p.Hq, p.B) && strides_ok(p.k, p.ks, p.S, p.Hkv, p.B) &&
+                  strides_ok(p.v, p.vs, p.S, p.Hkv, p.B) && strides_ok(bp.dout, bp.dos, p.L, p.Hq, p.B) &&
+                  strides_ok(bp.dq, bp.dqs, p.L, p.Hq, p.B) && strides_ok(bp.dk, bp.dks, p.S, p.Hkv, p.B) &&
+                  strides_ok(bp.dv, bp.dvs, p.S, p.Hkv, p.B);
+  if (!ok && alignment_only_failure) *alignment_only_failure = true;
+  return ok;
+}
+
+uint64_t bwd_tc_workspace_bytes(const BwdProblem& bp) {
+  return 2ull * sizeof(float) * static_cast<uint64_t>(bp.f.B) * bp.f.Hq * padded_rows(bp.f);
+}
+
+int plan_bwd_tc(const BwdProblem& bp, int dtype, B200SdpaPlan* plan) {
+  const Problem& p = bp.f;
+  (void)dtype;
+  plan->path = B200_SDPA_PATH_PREFILL;
+  plan->block_m = kT;
+  plan->block_n = kT;
+  plan->grid_x = static_cast<int32_t>(static_cast<long long>((p.L + kT - 1) / kT) * p.Hq * p.B);
+  plan->grid_y = static_cast<int32_t>(static_cast<long long>((p.S + kT - 1) / kT) * p.Hkv * p.B);
+  plan->grid_z = 1;
+  plan->threads = kThreads;
+  plan->smem_bytes = p.E == 128 ? BCfg<128>::kSmemBytes : BCfg<64>::kSmemBytes;
+  plan->kv_splits = 1;
+  plan->launches = 3;
+  plan->workspace_bytes = bwd_tc_workspace_bytes(bp);
+  return B200_SDPA_OK;
+}
+
+int launch_bwd_tc(const BwdProblem& bp, int dtype, void* workspace, uint64_t workspace_bytes, cudaStream_t stream) {
+  if (!bwd_tc_eligible(bp, dtype, nullptr)) return B200_SDPA_ERR_UNSUPPORTED;
+  const uint64_t need = bwd_tc_workspace_bytes(bp);
+  if (workspace == nullptr || workspace_bytes < need || reinterpret_cast<uintptr_t>(workspace) % 16)
+    return B200_SDPA_ERR_WORKSPACE;
+  float* lse2 = reinterpret_cast<float*>(workspace);
+  float* delta = lse2 + need / (2 * sizeof(float));
+  const bool bf16 = dtype == B200_SDPA_BF16;
+  if (bp.f.E == 128) return bf16 ? launch_tc<128, true>(bp, lse2, delta, stream) : launch_tc<128, false>(bp, lse2, delta, stream);
+  return bf16 ? launch_tc<64, true>(bp, lse2, delta, stream) : launch_tc<64, false>(bp, lse2, delta, stream);
+}
+
+}  // namespace b200

@@ -54,7 +54,8 @@ enum KernelId {
   KID_MERGE = 4,
   KID_BWD_DQ = 5,
   KID_BWD_DKV = 6,
-  KID_COUNT = 7
+  KID_BWD_PREP = 7,
+  KID_COUNT = 8
 };
 
 // Host launchers implemented in the per-kernel translation units.  Each returns
@@ -78,6 +79,11 @@ bool prefill_eligible(const Problem& p, int dtype, bool* alignment_only_failure)
 int launch_merge(const B200SdpaMergeParams& m, cudaStream_t stream);
 
 int launch_bwd_generic(const BwdProblem& bp, int dtype, cudaStream_t stream);
+int plan_bwd_generic(const BwdProblem& bp, int dtype, B200SdpaPlan* plan);
+bool bwd_tc_eligible(const BwdProblem& bp, int dtype, bool* alignment_only_failure);
+uint64_t bwd_tc_workspace_bytes(const BwdProblem& bp);
+int plan_bwd_tc(const BwdProblem& bp, int dtype, B200SdpaPlan* plan);
+int launch_bwd_tc(const BwdProblem& bp, int dtype, void* workspace, uint64_t workspace_bytes, cudaStream_t stream);
 
 void count_launch(int kernel_id);
 

@@ -1,0 +1,154 @@
+// Helpers shared by the tcgen05 kernels (forward prefill and backward): fast math,
+// packed conversions, bounded barrier waits with a CTA-wide abort flag, the device
+// status word, and host-side TMA tensor-map construction.
+#pragma once
+
+#include "common.cuh"
+#include "ptx_sm100.cuh"
+
+#include <mutex>
+
+namespace b200 {
+namespace tc {
+
+using namespace ptx;
+
+constexpr int kTileRows = 128;                    // rows of every operand tile (= TMEM lanes)
+constexpr int kBoxBytes = kTileRows * 128;        // one TMA box: 128 rows x 64 16-bit elements
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float lg2(float x) {
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+// packed fp32 pairs (one instruction for two lanes of arithmetic)
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+
+template <bool BF16> __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  uint32_t r;
+  if (BF16) {
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  } else {
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  }
+  return r;
+}
+
+__device__ __forceinline__ bool wait_clocked(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                             long long limit_cycles) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 15u) == 0u) {
+      if (*abort_flag != 0) return false;
+      if (clock64() - t0 > limit_cycles) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void report(int* status, int role, int step, int extra) {
+  if (status == nullptr) return;
+  if (atomicCAS(status, 0, B200_SDPA_ERR_TIMEOUT) == 0) {
+    status[1] = role;
+    status[2] = step;
+    status[3] = extra;
+  }
+}
+
+
+// ------------------------------------------------------------------ host side --
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    } else {
+      cudaGetLastError();
+    }
+  });
+  return fn;
+}
+
+// (D, rows, heads, batch) view of a (B, H, S, D) tensor with unit inner stride.
+inline bool make_map(CUtensorMap* map, const void* base, bool bf16, int d, int rows, int heads, int batch,
+              const int64_t* stride /* elements, (B,H,S,D) order */) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return false;
+  const cuuint64_t dims[4] = {static_cast<cuuint64_t>(d), static_cast<cuuint64_t>(rows),
+                              static_cast<cuuint64_t>(heads), static_cast<cuuint64_t>(batch)};
+  auto fix = [&](int64_t s, int n) -> cuuint64_t {
+    // a dimension of extent 1 is never stepped; give it any legal stride
+    return static_cast<cuuint64_t>((n == 1 ? static_cast<int64_t>(d) : s) * 2);
+  };
+  const cuuint64_t strides[3] = {fix(stride[2], rows), fix(stride[1], heads), fix(stride[0], batch)};
+  const cuuint32_t box[4] = {64, static_cast<cuuint32_t>(kTileRows), 1, 1};
+  const cuuint32_t elem[4] = {1, 1, 1, 1};
+  const CUresult rc = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                         const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return rc == CUDA_SUCCESS;
+}
+
+inline bool strides_ok(const void* base, const int64_t* s, int rows, int heads, int batch) {
+  if (reinterpret_cast<uintptr_t>(base) % 16) return false;
+  if (s[3] != 1) return false;
+  const int n[3] = {batch, heads, rows};
+  for (int i = 0; i < 3; ++i) {
+    if (n[i] == 1) continue;
+    if (s[i] <= 0 || (s[i] * 2) % 16 != 0 || s[i] * 2 >= (1LL << 40)) return false;
+  }
+  return true;
+}
+
+inline long long wait_limit_cycles() {
+  // about two seconds at 2 GHz; B200_SDPA_WAIT_LIMIT overrides (cycles)
+  static long long v = [] {
+    const char* e = getenv("B200_SDPA_WAIT_LIMIT");
+    long long x = e ? atoll(e) : 0;
+    return x > 0 ? x : (1LL << 32);
+  }();
+  return v;
+}
+
+
+}  // namespace tc
+}  // namespace b200

@@ -45,6 +45,7 @@ _status_words: dict[int, torch.Tensor] = {}
 _zero_scalars: dict[int, torch.Tensor] = {}
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
 last_plan: dict = {}
+last_bwd_plan: dict = {}
 
 
 def _device_index(t: torch.Tensor) -> int:
@@ -281,6 +282,7 @@ def sdpa_backward(
     grad_q: Optional[torch.Tensor] = None,
     grad_k: Optional[torch.Tensor] = None,
     grad_v: Optional[torch.Tensor] = None,
+    force_path: int = _lib.PATH_AUTO,
 ):
     """Launch the backward on the current CUDA stream; returns ``(grad_q, grad_k,
     grad_v, grad_bias)``.  Each gradient is allocated with the layout of the tensor
@@ -300,6 +302,8 @@ def sdpa_backward(
         raise RuntimeError("SDPA backward: logsumexp must be a float32 tensor of shape (B, Hq, L)")
     if scale is None:
         scale = 1.0 / math.sqrt(E)
+    if grad_out.stride(3) != 1 or any((st * grad_out.element_size()) % 16 for st in grad_out.stride()[:3]):
+        grad_out = grad_out.contiguous()   # e.g. the expanded gradient of a reduction: stride 0 everywhere
     grad_q = torch.empty_like(query) if grad_q is None else grad_q
     grad_k = torch.empty_like(key) if grad_k is None else grad_k
     grad_v = torch.empty_like(value) if grad_v is None else grad_v
@@ -345,9 +349,23 @@ def sdpa_backward(
         p.bias_dtype = _DTYPE_CODE[attn_bias.dtype]
         p.bias_stride[:] = _bias_strides(attn_bias, (B, Hq, L, S))
     p.status = _status_word(dev).data_ptr()
+    p.force_path = force_path
+    plan = _lib.Plan()
+    plan.struct_size = C.sizeof(_lib.Plan)
+    rc = lib.b200_sdpa_bwd_query_plan(C.byref(p), C.byref(plan))
+    if rc != _lib.OK:
+        raise RuntimeError(f"b200_sdpa_bwd_query_plan: {_lib.strerror(rc)}")
+    ws = None
+    if plan.workspace_bytes:
+        ws = _workspace(dev, int(plan.workspace_bytes))
+        p.workspace = ws.data_ptr()
+        p.workspace_bytes = ws.numel()
     rc = lib.b200_sdpa_bwd(C.byref(p), C.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
     if rc != _lib.OK:
         raise RuntimeError(f"b200_sdpa_bwd: {_lib.strerror(rc)}")
+    last_bwd_plan.clear()
+    last_bwd_plan.update(path=_lib.PATH_NAMES.get(plan.path, str(plan.path)), launches=plan.launches,
+                         workspace_bytes=int(plan.workspace_bytes))
     return grad_q, grad_k, grad_v, grad_bias
 
 
