@@ -26,6 +26,9 @@ pytestmark = pytest.mark.gpu
 
 FP32_GRAD = dict(rtol=1e-4, atol=1e-5)
 HALF_GRAD = dict(rtol=5e-2, atol=5e-3)
+# The tensor-core kernels round P and dS to the 16-bit type before their second product (the
+# CUDA-core kernels keep them fp32): the forward's half-precision max-abs bar beside the relative term.
+HALF_GRAD_TC = dict(rtol=5e-2, atol=2e-2)
 
 
 def _names():
@@ -81,7 +84,9 @@ def _cuda_backward(go, q, k, v, *, mask=None, is_causal=False, scale=None, kv_le
 
 def _close(got, want, dtype, tag, tol=None):
     assert not torch.isnan(got.float()).any(), f"{tag}: NaN (unwritten or bad arithmetic)"
-    tol = tol or (FP32_GRAD if dtype == torch.float32 else HALF_GRAD)
+    if tol is None:
+        tensor_core = getattr(_cuda_backward, "path", "generic") == "prefill"
+        tol = FP32_GRAD if dtype == torch.float32 else (HALF_GRAD_TC if tensor_core else HALF_GRAD)
     torch.testing.assert_close(got.float(), want.float(), msg=lambda m: f"{tag}: {m}", **tol)
 
 
