@@ -262,6 +262,15 @@ def run_profile_case(args):
         out = torch.empty_like(q)
         lse = torch.empty(8, 12, 1024, dtype=torch.float32, device=dev)
         fn = lambda: T.sdpa_forward(q, k, v, is_causal=True, scale=0.125, out=out, lse=lse)  # noqa: E731
+    elif args.profile == "bwd":
+        # the headline batch cut to one sequence (84 MB of operands, still around L2 size) keeps captures short
+        q, k, v, lens = c3_inputs(2, device=dev)
+        q, k, v, lens = q[:1].contiguous(), k[:1].contiguous(), v[:1].contiguous(), lens[:1].contiguous()
+        out, lse = T.sdpa_forward(q, k, v, is_causal=True, scale=scale, kv_lens=lens)
+        go = torch.randn(q.shape, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16).to(dev)
+        gq, gk, gv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        fn = lambda: T.sdpa_backward(go, q, k, v, out, lse, is_causal=True, scale=scale, kv_lens=lens,  # noqa: E731
+                                     grad_q=gq, grad_k=gk, grad_v=gv)
     else:
         q, k, v, lens = c4_inputs(dev, batch=16)
         lens = lens.to(dev)
@@ -446,6 +455,33 @@ def run_ours(args, rank, local_rank, world):
                          "unit": "TFLOP/s", "frac": gflops / (gms * 1e-3) / 1e12 / peaks["bf16_tflops"],
                          "traffic": None, "peak_kind": f"bf16_tflops of {peaks['source']}"},
         }
+        # ---------------- backward of the headline configuration (tensor-core kernels) ----------------
+        bgo = torch.randn(q.shape, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16).to(dev)
+        bgq, bgk, bgv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        step()
+
+        def bstep():
+            T.sdpa_backward(bgo, q, k, v, out, lse, is_causal=True, scale=scale, kv_lens=lens, grad_q=bgq, grad_k=bgk,
+                            grad_v=bgv)
+
+        for _ in range(3):
+            bstep()
+        torch.cuda.synchronize()
+        T.check_device_status()
+        bms = time_steps_flushed(bstep, max(5, min(args.steps, 20)), flush)
+        bflops = 2.5 * flops                      # five tile products against the forward's two
+        btf = bflops / (bms * 1e-3) / 1e12
+        extra["backward_config3"] = {
+            "workload": "backward of configuration 3 (bf16, causal, ragged lengths): grad_q, grad_k, grad_v",
+            "value": btf, "unit": "TFLOP/s (2.5 x forward FLOPs: the 5-product count)", "ms": bms,
+            "path": T.ops.last_bwd_plan.get("path"), "launches": T.ops.last_bwd_plan.get("launches"),
+            "l2": "flushed before every timed call",
+            # the two kernels recompute S and dP independently: 7 tile products are executed for the 5 counted
+            "roofline": {"bound": "tensor", "achieved": btf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                         "frac": btf / peaks["bf16_tflops"], "executed_over_counted": 1.4, "traffic": None,
+                         "peak_kind": f"bf16_tflops of {peaks['source']}"},
+        }
+        del bgo, bgq, bgk, bgv
         # ---------------- fp32 parity configuration: latency only ----------------
         g = torch.Generator().manual_seed(0)
         fq, fk, fv = (torch.randn(2, 8, 512, 64, generator=g).to(dev) for _ in range(3))
@@ -536,7 +572,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--profile", default=None, choices=["prefill", "decode", "gpt2"],
+    ap.add_argument("--profile", default=None, choices=["prefill", "decode", "gpt2", "bwd"],
                     help="bare kernel loop on one GPU for profiler captures")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the decode / GPT-2 / fp32 extras")

@@ -19,8 +19,18 @@
 // in exchange dQ needs neither atomics nor an fp32 scratch tensor, and results are
 // deterministic.  Arithmetic: torch_neuronx/_sdpa_math.py:133-176 with P and dS rounded
 // to the input dtype before their second product (upstream rounds P the same way in the
-// forward, :94).  Roles per CTA (192 threads): warps 0-3 elementwise (one thread per TMEM
-// lane), warp 4 TMA producer, warp 5 MMA issuer.  Every wait is bounded (see tc_common.cuh).
+// forward, :94).  Roles per CTA (320 threads): warps 0-7 elementwise (two threads per TMEM
+// lane), warp 8 TMA producer, warp 9 MMA issuer.
+//
+// Both kernels work in units of 64 score columns (half an operand tile) with the two
+// score-shaped accumulators double-buffered in tensor memory, so the elementwise role
+// works on unit u+1 while the tensor cores run the accumulating products of unit u and the
+// score products of unit u+2:
+//   TMEM columns  [0,64) [64,128)  S   buffers 0/1      [128,192) [192,256)  dP  buffers 0/1
+//                 [256, ...)       the fp32 gradient accumulators (dQ, or dV and dK)
+// The MMA pipe executes in issue order, which is what makes "score products of u+2 after
+// the accumulating products of u" safe on the shared buffer.  Every wait is bounded (see
+// tc_common.cuh).
 #include "tc_common.cuh"
 
 namespace b200 {
@@ -31,9 +41,12 @@ using namespace ptx;
 using namespace tc;
 
 constexpr int kT = 128;                 // tile edge: query rows, keys, TMEM lanes
-constexpr int kThreads = 192;
-constexpr int kProducerWarp = 4;
-constexpr int kMmaWarp = 5;
+constexpr int kThreads = 320;
+constexpr int kEThreads = 256;            // elementwise role: two column halves x 128 lanes
+constexpr int kU = 64;                    // score columns per unit
+constexpr uint32_t kColS = 0, kColDP = 128, kColAcc = 256;   // TMEM layout (buffer b at + 64 b)
+constexpr int kProducerWarp = 8;
+constexpr int kMmaWarp = 9;
 constexpr uint32_t kTmemCols = 512;
 constexpr int kMaxStages = 4;
 
@@ -50,8 +63,8 @@ struct BSync {
   uint64_t fixed_full;
   uint64_t ring_full[kMaxStages];
   uint64_t ring_empty[kMaxStages];
-  uint64_t sp_full;     // both score-shaped accumulators of an iteration are complete
-  uint64_t e_ready;     // the elementwise role has written its 16-bit operands
+  uint64_t sp_full[2];  // both score-shaped accumulators of a unit are complete (per buffer)
+  uint64_t e_ready[2];  // the elementwise role has written the unit's 16-bit operands
   uint64_t acc_done;    // last accumulating MMA has retired
   uint64_t staged;
   uint64_t drain;
@@ -63,7 +76,7 @@ struct BSync {
 
 template <typename T>
 __global__ void bwd_prep_kernel(const BwdProblem bp, float* __restrict__ lse2, float* __restrict__ delta,
-                                const int l_pad) {
+                                const int l_pad, const int vec4) {
   const Problem& p = bp.f;
   const long long warp_id = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
@@ -77,7 +90,18 @@ __global__ void bwd_prep_kernel(const BwdProblem bp, float* __restrict__ lse2, f
   if (i < p.L) {
     const T* __restrict__ go = reinterpret_cast<const T*>(bp.dout) + b * bp.dos[0] + h * bp.dos[1] + i * bp.dos[2];
     const T* __restrict__ o = reinterpret_cast<const T*>(p.out) + b * p.os[0] + h * p.os[1] + i * p.os[2];
-    for (int e = lane; e < p.Dv; e += 32) d = fmaf(to_f32<T>(go[e * bp.dos[3]]), to_f32<T>(o[e * p.os[3]]), d);
+    if (vec4) {   // unit inner strides, rows 8-byte aligned: four elements per load
+      for (int e = lane * 4; e < p.Dv; e += 128) {
+        const uint2 a = *reinterpret_cast<const uint2*>(go + e);
+        const uint2 c = *reinterpret_cast<const uint2*>(o + e);
+        const T* av = reinterpret_cast<const T*>(&a);
+        const T* cv = reinterpret_cast<const T*>(&c);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) d = fmaf(to_f32<T>(av[u]), to_f32<T>(cv[u]), d);
+      }
+    } else {
+      for (int e = lane; e < p.Dv; e += 32) d = fmaf(to_f32<T>(go[e * bp.dos[3]]), to_f32<T>(o[e * p.os[3]]), d);
+    }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
     const float l = p.lse[b * p.ls[0] + h * p.ls[1] + i * p.ls[2]];
@@ -101,32 +125,38 @@ __device__ __forceinline__ uint64_t kmajor_step(int kk) {
 __device__ __forceinline__ uint64_t mnmajor_desc(uint32_t tile) { return smem_desc_sw128(tile, kBoxBytes, 1024); }
 __device__ __forceinline__ uint64_t mnmajor_step(int kk) { return static_cast<uint64_t>(kk * (2048 >> 4)); }
 
-// acc[tmem d] = A[smem, K-major] * B[smem, K-major]^T over D
+// acc[tmem d, 128 x 64] = A[smem tile, K-major] * B[rows 64 hh .. 64 hh + 63 of a smem tile, K-major]^T over D
 template <int D>
-__device__ __forceinline__ void issue_ss(uint32_t d_tmem, uint32_t a_tile, uint32_t b_tile, uint32_t idesc) {
-  const uint64_t ad = kmajor_desc(a_tile), bd = kmajor_desc(b_tile);
+__device__ __forceinline__ void issue_ss(uint32_t d_tmem, uint32_t a_tile, uint32_t b_tile, int hh, uint32_t idesc) {
+  const uint64_t ad = kmajor_desc(a_tile), bd = kmajor_desc(b_tile + static_cast<uint32_t>(hh) * (kU * 128));
   if (elect_one()) {
 #pragma unroll
     for (int kk = 0; kk < D / 16; ++kk) mma_ss(d_tmem, ad + kmajor_step(kk), bd + kmajor_step(kk), idesc, kk > 0 ? 1u : 0u);
   }
 }
-// acc[tmem d] (+)= A[tmem, 16-bit pairs in 64 columns] * B[smem tile, MN-major] over the tile's 128 rows
-__device__ __forceinline__ void issue_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_tile, uint32_t idesc,
+// acc[tmem d] (+)= A[tmem] * B[rows 64 hh .. 64 hh + 63 of a smem tile, MN-major].  The 16-bit A
+// operand sits where the two column halves of the elementwise role left it: contraction
+// indices 0-31 packed into columns [0,16) of the unit's buffer, 32-63 into columns [32,48).
+__device__ __forceinline__ void issue_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_tile, int hh, uint32_t idesc,
                                          bool accumulate) {
-  const uint64_t bd = mnmajor_desc(b_tile);
+  const uint64_t bd = mnmajor_desc(b_tile) + mnmajor_step(4 * hh);
   if (elect_one()) {
 #pragma unroll
-    for (int kk = 0; kk < kT / 16; ++kk)
-      mma_ts(d_tmem, a_tmem + static_cast<uint32_t>(kk * 8), bd + mnmajor_step(kk), idesc, (kk > 0 || accumulate) ? 1u : 0u);
+    for (int kk = 0; kk < kU / 16; ++kk)
+      mma_ts(d_tmem, a_tmem + static_cast<uint32_t>((kk >> 1) * 32 + (kk & 1) * 8), bd + mnmajor_step(kk), idesc,
+             (kk > 0 || accumulate) ? 1u : 0u);
   }
 }
 
 // One thread's accumulator row (TMEM lane) -> 16-bit -> the 128-byte-swizzled staging
 // tile a TMA store expects.
 template <int D, bool BF16>
-__device__ __forceinline__ void stage_row(uint32_t acc_addr, bool have_acc, float mul, uint8_t* stage, int r) {
+__device__ __forceinline__ void stage_row(uint32_t acc_addr, bool have_acc, float mul, uint8_t* stage, int r,
+                                          int half) {
+  // the two threads of a lane share the row: D/64 chunks of 32 columns each
 #pragma unroll
-  for (int c = 0; c < D / 32; ++c) {
+  for (int cc = 0; cc < D / 64; ++cc) {
+    const int c = half * (D / 64) + cc;
     uint32_t v[32];
     if (have_acc) {
       tmem_ld_32x32(acc_addr + c * 32, v);
@@ -149,10 +179,12 @@ __device__ __forceinline__ void stage_row(uint32_t acc_addr, bool have_acc, floa
 }
 
 __device__ __forceinline__ void init_common_barriers(BSync* sync) {
-  mbar_init(smem_u32(&sync->sp_full), 1);
-  mbar_init(smem_u32(&sync->e_ready), kT);
+  for (int i = 0; i < 2; ++i) {
+    mbar_init(smem_u32(&sync->sp_full[i]), 1);
+    mbar_init(smem_u32(&sync->e_ready[i]), kEThreads);
+  }
   mbar_init(smem_u32(&sync->acc_done), 1);
-  mbar_init(smem_u32(&sync->staged), kT);
+  mbar_init(smem_u32(&sync->staged), kEThreads);
   mbar_init(smem_u32(&sync->drain), 1);
   sync->abort_flag = 0;
   mbar_fence_init();
@@ -204,6 +236,7 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   if (end < 0) end = 0;
   if (first < -1) first = -1;
   const int n_tiles = static_cast<int>((end + kT - 1) / kT);
+  const int n_units = static_cast<int>((end + kU - 1) / kU);   // 64-key units; the last tile may need only one
   const int min_lim = static_cast<int>(first);
 
   const uint32_t q_tile = tiles, do_tile = tiles + C::kTileBytes;
@@ -235,7 +268,7 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = sync->tmem_base;
-  constexpr uint32_t kColS = 0, kColDP = 128, kColDQ = 256;
+  constexpr uint32_t kColDQ = kColAcc;
 
   if (warp == kProducerWarp) {
     if (lane == 0) {
@@ -260,46 +293,59 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     }
     __syncwarp();
   } else if (warp == kMmaWarp) {
-    constexpr uint32_t idesc_score = make_idesc(BF16, false, kT, kT);
+    constexpr uint32_t idesc_score = make_idesc(BF16, false, kT, kU);
     constexpr uint32_t idesc_acc = make_idesc(BF16, true, kT, D);
-    bool alive = n_tiles > 0;
+    bool alive = n_units > 0;
     if (alive) {
       alive = wait_clocked(smem_u32(&sync->fixed_full), 0, abort_flag, wait_limit);
       if (!alive && lane == 0) report(p.status, 12, -1, 0);
     }
-    for (int j = 0; j < n_tiles && alive; ++j) {
+    // S_u = Q K_u^T and dP_u = dO V_u^T into buffer u & 1 (waits for the key tile when the unit opens it)
+    auto issue_scores = [&](int u) -> bool {
+      const int j = u >> 1, hh = u & 1, buf = u & 1;
       const int stage = j % C::kStages;
-      const uint32_t round = static_cast<uint32_t>(j / C::kStages);
-      alive = wait_clocked(smem_u32(&sync->ring_full[stage]), round & 1u, abort_flag, wait_limit);
-      if (!alive) {
-        if (lane == 0) report(p.status, 12, j, stage);
-        break;
+      if (hh == 0) {
+        const uint32_t round = static_cast<uint32_t>(j / C::kStages);
+        if (!wait_clocked(smem_u32(&sync->ring_full[stage]), round & 1u, abort_flag, wait_limit)) {
+          if (lane == 0) report(p.status, 12, j, stage);
+          return false;
+        }
+        tc_fence_after_sync();
       }
-      tc_fence_after_sync();
       const uint32_t k_tile = ring + stage * 2 * C::kTileBytes, v_tile = k_tile + C::kTileBytes;
-      issue_ss<D>(tmem_base + kColS, q_tile, k_tile, idesc_score);
-      issue_ss<D>(tmem_base + kColDP, do_tile, v_tile, idesc_score);
-      if (elect_one()) mma_commit(smem_u32(&sync->sp_full));
-      alive = wait_clocked(smem_u32(&sync->e_ready), j & 1, abort_flag, wait_limit);
+      issue_ss<D>(tmem_base + kColS + buf * kU, q_tile, k_tile, hh, idesc_score);
+      issue_ss<D>(tmem_base + kColDP + buf * kU, do_tile, v_tile, hh, idesc_score);
+      if (elect_one()) mma_commit(smem_u32(&sync->sp_full[buf]));
+      return true;
+    };
+    if (alive) alive = issue_scores(0);
+    if (alive && n_units > 1) alive = issue_scores(1);
+    for (int u = 0; u < n_units && alive; ++u) {
+      const int j = u >> 1, hh = u & 1, buf = u & 1;
+      const int stage = j % C::kStages;
+      alive = wait_clocked(smem_u32(&sync->e_ready[buf]), (u >> 1) & 1, abort_flag, wait_limit);
       if (!alive) {
-        if (lane == 0) report(p.status, 13, j, 0);
+        if (lane == 0) report(p.status, 13, u, 0);
         break;
       }
       tc_fence_after_sync();
-      issue_ts(tmem_base + kColDQ, tmem_base + kColDP, k_tile, idesc_acc, j > 0);
+      const uint32_t k_tile = ring + stage * 2 * C::kTileBytes;
+      issue_ts(tmem_base + kColDQ, tmem_base + kColDP + buf * kU, k_tile, hh, idesc_acc, u > 0);   // dQ += dS_u K_u
       if (elect_one()) {
-        mma_commit(smem_u32(&sync->ring_empty[stage]));
-        if (j + 1 == n_tiles) mma_commit(smem_u32(&sync->acc_done));
+        if (hh == 1 || u + 1 == n_units) mma_commit(smem_u32(&sync->ring_empty[stage]));
+        if (u + 1 == n_units) mma_commit(smem_u32(&sync->acc_done));
       }
+      if (u + 2 < n_units) alive = issue_scores(u + 2);
     }
     if (*abort_flag != 0) drain_after_abort(sync, wait_limit);
     __syncwarp();
   } else {
     // -------------------------------------------------------- elementwise role
-    const int r = tid;                         // query row inside the tile = TMEM lane
-    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
-    const uint32_t s_addr = tmem_base + lane_off + kColS;
-    const uint32_t dp_addr = tmem_base + lane_off + kColDP;
+    const int r = tid & (kT - 1);              // query row inside the tile = TMEM lane
+    const int half = tid >> 7;                 // which 32 of the unit's 64 score columns
+    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t s_addr = tmem_base + lane_off + kColS + half * 32;
+    const uint32_t dp_addr = tmem_base + lane_off + kColDP + half * 32;
     const uint32_t dq_addr = tmem_base + lane_off + kColDQ;
     const int row_g = row0 + r;
     int lim = kv_limit;
@@ -312,40 +358,39 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const float dl = delta[stat_idx];
     const float sl2 = p.scale * kLog2e;
     bool alive = true;
-    for (int j = 0; j < n_tiles; ++j) {
-      bool ok = wait_clocked(smem_u32(&sync->sp_full), j & 1, abort_flag, wait_limit);
+    for (int u = 0; u < n_units; ++u) {
+      const int buf = u & 1;
+      bool ok = wait_clocked(smem_u32(&sync->sp_full[buf]), (u >> 1) & 1, abort_flag, wait_limit);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
-        if (lane == 0) report(p.status, 14, j, warp);
+        if (lane == 0) report(p.status, 14, u, warp);
         alive = false;
         break;
       }
       tc_fence_after_sync();
-      const int col0 = j * kT;
-      const bool need_mask = col0 + kT > min_lim;
+      const int col0 = u * kU + half * 32;
+      const bool need_mask = u * kU + kU > min_lim;
+      uint32_t sv[32], dv[32];
+      tmem_ld_32x32(s_addr + buf * kU, sv);
+      tmem_ld_32x32(dp_addr + buf * kU, dv);
+      tmem_ld_wait();
+      uint32_t pk[16];
 #pragma unroll
-      for (int c = 0; c < kT / 32; ++c) {
-        uint32_t sv[32], dv[32];
-        tmem_ld_32x32(s_addr + c * 32, sv);
-        tmem_ld_32x32(dp_addr + c * 32, dv);
-        tmem_ld_wait();
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p0 = ex2(fmaf(__uint_as_float(sv[i]), sl2, neg_l2));
-          float p1 = ex2(fmaf(__uint_as_float(sv[i + 1]), sl2, neg_l2));
-          if (need_mask) {
-            p0 = (col0 + c * 32 + i < lim) ? p0 : 0.f;
-            p1 = (col0 + c * 32 + i + 1 < lim) ? p1 : 0.f;
-          }
-          pk[i >> 1] = pack2<BF16>(p0 * (__uint_as_float(dv[i]) - dl), p1 * (__uint_as_float(dv[i + 1]) - dl));
+      for (int i = 0; i < 32; i += 2) {
+        float p0 = ex2(fmaf(__uint_as_float(sv[i]), sl2, neg_l2));
+        float p1 = ex2(fmaf(__uint_as_float(sv[i + 1]), sl2, neg_l2));
+        if (need_mask) {
+          p0 = (col0 + i < lim) ? p0 : 0.f;
+          p1 = (col0 + i + 1 < lim) ? p1 : 0.f;
         }
-        // 16 packed columns land on dP columns this thread has already read
-        tmem_st_32x16(dp_addr + c * 16, pk);
+        pk[i >> 1] = pack2<BF16>(p0 * (__uint_as_float(dv[i]) - dl), p1 * (__uint_as_float(dv[i + 1]) - dl));
       }
+      // 16 packed columns land on dP columns this thread has just read (and that the other
+      // column half never touches)
+      tmem_st_32x16(dp_addr + buf * kU, pk);
       tmem_st_wait();
       tc_fence_before_sync();
-      mbar_arrive(smem_u32(&sync->e_ready));
+      mbar_arrive(smem_u32(&sync->e_ready[buf]));
     }
     if (alive && n_tiles > 0) {
       bool ok = wait_clocked(smem_u32(&sync->acc_done), 0, abort_flag, wait_limit);
@@ -358,10 +403,10 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     }
     if (alive) {
       uint8_t* stage = smem_raw + (q_tile - raw_addr);   // Q is no longer needed
-      stage_row<D, BF16>(dq_addr, n_tiles > 0, p.scale, stage, r);
+      stage_row<D, BF16>(dq_addr, n_tiles > 0, p.scale, stage, r, half);
       fence_proxy_async_smem();
       mbar_arrive(smem_u32(&sync->staged));
-      if (r == 0 && wait_clocked(smem_u32(&sync->staged), 0, abort_flag, wait_limit)) {
+      if (tid == 0 && wait_clocked(smem_u32(&sync->staged), 0, abort_flag, wait_limit)) {
         for (int bx = 0; bx < C::kBoxes; ++bx) tma_store_4d(&tm_dq, q_tile + bx * kBoxBytes, bx * 64, row0, h, b);
         tma_store_commit();
         tma_store_wait_all();
@@ -444,7 +489,8 @@ bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = sync->tmem_base;
-  constexpr uint32_t kColS = 0, kColDP = 128, kColDV = 256, kColDK = 256 + D;
+  constexpr uint32_t kColDV = kColAcc, kColDK = kColAcc + D;
+  const int n_units = 2 * n_items;
 
   if (warp == kProducerWarp) {
     // the whole warp runs the loop: the lanes copy the query tile's row statistics into
@@ -484,47 +530,60 @@ bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     }
     __syncwarp();
   } else if (warp == kMmaWarp) {
-    constexpr uint32_t idesc_score = make_idesc(BF16, false, kT, kT);
+    constexpr uint32_t idesc_score = make_idesc(BF16, false, kT, kU);
     constexpr uint32_t idesc_acc = make_idesc(BF16, true, kT, D);
     bool alive = n_items > 0;
     if (alive) {
       alive = wait_clocked(smem_u32(&sync->fixed_full), 0, abort_flag, wait_limit);
       if (!alive && lane == 0) report(p.status, 22, -1, 0);
     }
-    for (int it = 0; it < n_items && alive; ++it) {
+    // S^T_u = K Q_u^T and dP^T_u = V dO_u^T into buffer u & 1 (waits for the query tile when the unit opens it)
+    auto issue_scores = [&](int u) -> bool {
+      const int it = u >> 1, hh = u & 1, buf = u & 1;
       const int stage = it % C::kStages;
-      const uint32_t round = static_cast<uint32_t>(it / C::kStages);
-      alive = wait_clocked(smem_u32(&sync->ring_full[stage]), round & 1u, abort_flag, wait_limit);
+      if (hh == 0) {
+        const uint32_t round = static_cast<uint32_t>(it / C::kStages);
+        if (!wait_clocked(smem_u32(&sync->ring_full[stage]), round & 1u, abort_flag, wait_limit)) {
+          if (lane == 0) report(p.status, 22, it, stage);
+          return false;
+        }
+        tc_fence_after_sync();
+      }
+      const uint32_t q_tile = ring + stage * 2 * C::kTileBytes, do_tile = q_tile + C::kTileBytes;
+      issue_ss<D>(tmem_base + kColS + buf * kU, k_tile, q_tile, hh, idesc_score);
+      issue_ss<D>(tmem_base + kColDP + buf * kU, v_tile, do_tile, hh, idesc_score);
+      if (elect_one()) mma_commit(smem_u32(&sync->sp_full[buf]));
+      return true;
+    };
+    if (alive) alive = issue_scores(0);
+    if (alive) alive = issue_scores(1);
+    for (int u = 0; u < n_units && alive; ++u) {
+      const int it = u >> 1, hh = u & 1, buf = u & 1;
+      const int stage = it % C::kStages;
+      alive = wait_clocked(smem_u32(&sync->e_ready[buf]), (u >> 1) & 1, abort_flag, wait_limit);
       if (!alive) {
-        if (lane == 0) report(p.status, 22, it, stage);
+        if (lane == 0) report(p.status, 23, u, 0);
         break;
       }
       tc_fence_after_sync();
       const uint32_t q_tile = ring + stage * 2 * C::kTileBytes, do_tile = q_tile + C::kTileBytes;
-      issue_ss<D>(tmem_base + kColS, k_tile, q_tile, idesc_score);     // S^T  = K Q^T
-      issue_ss<D>(tmem_base + kColDP, v_tile, do_tile, idesc_score);   // dP^T = V dO^T
-      if (elect_one()) mma_commit(smem_u32(&sync->sp_full));
-      alive = wait_clocked(smem_u32(&sync->e_ready), it & 1, abort_flag, wait_limit);
-      if (!alive) {
-        if (lane == 0) report(p.status, 23, it, 0);
-        break;
-      }
-      tc_fence_after_sync();
-      issue_ts(tmem_base + kColDV, tmem_base + kColS, do_tile, idesc_acc, it > 0);   // dV += P^T dO
-      issue_ts(tmem_base + kColDK, tmem_base + kColDP, q_tile, idesc_acc, it > 0);   // dK += dS^T Q
+      issue_ts(tmem_base + kColDV, tmem_base + kColS + buf * kU, do_tile, hh, idesc_acc, u > 0);   // dV += P^T_u dO_u
+      issue_ts(tmem_base + kColDK, tmem_base + kColDP + buf * kU, q_tile, hh, idesc_acc, u > 0);   // dK += dS^T_u Q_u
       if (elect_one()) {
-        mma_commit(smem_u32(&sync->ring_empty[stage]));
-        if (it + 1 == n_items) mma_commit(smem_u32(&sync->acc_done));
+        if (hh == 1) mma_commit(smem_u32(&sync->ring_empty[stage]));
+        if (u + 1 == n_units) mma_commit(smem_u32(&sync->acc_done));
       }
+      if (u + 2 < n_units) alive = issue_scores(u + 2);
     }
     if (*abort_flag != 0) drain_after_abort(sync, wait_limit);
     __syncwarp();
   } else {
     // -------------------------------------------------------- elementwise role
-    const int r = tid;                         // key inside the tile = TMEM lane
-    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
-    const uint32_t s_addr = tmem_base + lane_off + kColS;
-    const uint32_t dp_addr = tmem_base + lane_off + kColDP;
+    const int r = tid & (kT - 1);              // key inside the tile = TMEM lane
+    const int half = tid >> 7;                 // which 32 of the unit's 64 query columns
+    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t s_addr = tmem_base + lane_off + kColS + half * 32;
+    const uint32_t dp_addr = tmem_base + lane_off + kColDP + half * 32;
     const int key_g = j0 + r;
     // query rows i >= i_min see this key; a padded key is seen by nobody
     int i_min = 0;
@@ -536,54 +595,53 @@ bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const bool tile_has_padding = j0 + kT > n_keys;
     const float sl2 = p.scale * kLog2e;
     bool alive = true;
-    for (int it = 0; it < n_items; ++it) {
-      bool ok = wait_clocked(smem_u32(&sync->sp_full), it & 1, abort_flag, wait_limit);
+    for (int u = 0; u < n_units; ++u) {
+      const int it = u >> 1, hh = u & 1, buf = u & 1;
+      bool ok = wait_clocked(smem_u32(&sync->sp_full[buf]), (u >> 1) & 1, abort_flag, wait_limit);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
-        if (lane == 0) report(p.status, 24, it, warp);
+        if (lane == 0) report(p.status, 24, u, warp);
         alive = false;
         break;
       }
       tc_fence_after_sync();
       const int stage = it % C::kStages;
-      const int qrow0 = (i_first + it % per_head) * kT;
-      const float4* st4 = reinterpret_cast<const float4*>(stats + stage * 2 * kT);
-      // some key of this tile hides some row of this query tile
+      const int unit_row0 = (i_first + it % per_head) * kT + hh * kU;   // first query row of the unit
+      const int qrow0 = unit_row0 + half * 32;                          // ... and of this thread's columns
+      const float4* st4 = reinterpret_cast<const float4*>(stats + stage * 2 * kT) + hh * 16 + half * 8;
+      // some key of this tile hides some row of this unit
       const bool need_mask = tile_has_padding ||
-                             (p.causal && static_cast<long long>(qrow0) < static_cast<long long>(j0) + kT - 1 - p.causal_shift);
+                             (p.causal && static_cast<long long>(unit_row0) < static_cast<long long>(j0) + kT - 1 - p.causal_shift);
+      uint32_t sv[32], dv[32];
+      tmem_ld_32x32(s_addr + buf * kU, sv);
+      tmem_ld_32x32(dp_addr + buf * kU, dv);
+      tmem_ld_wait();
+      uint32_t pkp[16], pkd[16];
 #pragma unroll
-      for (int c = 0; c < kT / 32; ++c) {
-        uint32_t sv[32], dv[32];
-        tmem_ld_32x32(s_addr + c * 32, sv);
-        tmem_ld_32x32(dp_addr + c * 32, dv);
-        tmem_ld_wait();
-        uint32_t pkp[16], pkd[16];
+      for (int q4 = 0; q4 < 8; ++q4) {
+        const float4 l4 = st4[q4];
+        const float4 d4 = st4[32 + q4];
+        const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
+        const float ds_[4] = {d4.x, d4.y, d4.z, d4.w};
+        float pr[4], dsv[4];
 #pragma unroll
-        for (int q4 = 0; q4 < 8; ++q4) {
-          const float4 l4 = st4[c * 8 + q4];
-          const float4 d4 = st4[32 + c * 8 + q4];
-          const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
-          const float ds_[4] = {d4.x, d4.y, d4.z, d4.w};
-          float pr[4], dsv[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int i = q4 * 4 + e;
-            float pe = ex2(fmaf(__uint_as_float(sv[i]), sl2, -ls[e]));
-            if (need_mask) pe = (qrow0 + c * 32 + i >= i_min) ? pe : 0.f;
-            pr[e] = pe;
-            dsv[e] = pe * (__uint_as_float(dv[i]) - ds_[e]);
-          }
-          pkp[q4 * 2] = pack2<BF16>(pr[0], pr[1]);
-          pkp[q4 * 2 + 1] = pack2<BF16>(pr[2], pr[3]);
-          pkd[q4 * 2] = pack2<BF16>(dsv[0], dsv[1]);
-          pkd[q4 * 2 + 1] = pack2<BF16>(dsv[2], dsv[3]);
+        for (int e = 0; e < 4; ++e) {
+          const int i = q4 * 4 + e;
+          float pe = ex2(fmaf(__uint_as_float(sv[i]), sl2, -ls[e]));
+          if (need_mask) pe = (qrow0 + i >= i_min) ? pe : 0.f;
+          pr[e] = pe;
+          dsv[e] = pe * (__uint_as_float(dv[i]) - ds_[e]);
         }
-        tmem_st_32x16(s_addr + c * 16, pkp);
-        tmem_st_32x16(dp_addr + c * 16, pkd);
+        pkp[q4 * 2] = pack2<BF16>(pr[0], pr[1]);
+        pkp[q4 * 2 + 1] = pack2<BF16>(pr[2], pr[3]);
+        pkd[q4 * 2] = pack2<BF16>(dsv[0], dsv[1]);
+        pkd[q4 * 2 + 1] = pack2<BF16>(dsv[2], dsv[3]);
       }
+      tmem_st_32x16(s_addr + buf * kU, pkp);
+      tmem_st_32x16(dp_addr + buf * kU, pkd);
       tmem_st_wait();
       tc_fence_before_sync();
-      mbar_arrive(smem_u32(&sync->e_ready));
+      mbar_arrive(smem_u32(&sync->e_ready[buf]));
     }
     if (alive && n_items > 0) {
       bool ok = wait_clocked(smem_u32(&sync->acc_done), 0, abort_flag, wait_limit);
@@ -598,11 +656,11 @@ bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       // ring slot 0 is idle by now: its two tiles stage dK and dV
       uint8_t* stage_k = smem_raw + (ring - raw_addr);
       uint8_t* stage_v = stage_k + C::kTileBytes;
-      stage_row<D, BF16>(tmem_base + lane_off + kColDK, n_items > 0, p.scale, stage_k, r);
-      stage_row<D, BF16>(tmem_base + lane_off + kColDV, n_items > 0, 1.f, stage_v, r);
+      stage_row<D, BF16>(tmem_base + lane_off + kColDK, n_items > 0, p.scale, stage_k, r, half);
+      stage_row<D, BF16>(tmem_base + lane_off + kColDV, n_items > 0, 1.f, stage_v, r, half);
       fence_proxy_async_smem();
       mbar_arrive(smem_u32(&sync->staged));
-      if (r == 0 && wait_clocked(smem_u32(&sync->staged), 0, abort_flag, wait_limit)) {
+      if (tid == 0 && wait_clocked(smem_u32(&sync->staged), 0, abort_flag, wait_limit)) {
         for (int bx = 0; bx < C::kBoxes; ++bx) {
           tma_store_4d(&tm_dk, ring + bx * kBoxBytes, bx * 64, j0, hk, b);
           tma_store_4d(&tm_dv, ring + C::kTileBytes + bx * kBoxBytes, bx * 64, j0, hk, b);
@@ -648,10 +706,14 @@ int launch_tc(const BwdProblem& bp, float* lse2, float* delta, cudaStream_t stre
     const long long warps = static_cast<long long>(p.B) * p.Hq * l_pad;
     const long long blocks = (warps * 32 + 255) / 256;
     if (blocks > 0x7fffffffLL) return B200_SDPA_ERR_UNSUPPORTED;
+    auto rows_aligned = [](const void* base, const int64_t* st) {
+      return st[3] == 1 && reinterpret_cast<uintptr_t>(base) % 8 == 0 && st[0] % 4 == 0 && st[1] % 4 == 0 && st[2] % 4 == 0;
+    };
+    const int vec4 = (p.Dv % 4 == 0 && rows_aligned(bp.dout, bp.dos) && rows_aligned(p.out, p.os)) ? 1 : 0;
     if (BF16) {
-      bwd_prep_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(bp, lse2, delta, l_pad);
+      bwd_prep_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(bp, lse2, delta, l_pad, vec4);
     } else {
-      bwd_prep_kernel<__half><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(bp, lse2, delta, l_pad);
+      bwd_prep_kernel<__half><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(bp, lse2, delta, l_pad, vec4);
     }
     if (cudaGetLastError() != cudaSuccess) return B200_SDPA_ERR_CUDA;
     count_launch(KID_BWD_PREP);
