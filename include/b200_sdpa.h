@@ -33,7 +33,7 @@
 extern "C" {
 #endif
 
-#define B200_SDPA_ABI_VERSION 1
+#define B200_SDPA_ABI_VERSION 2
 
 typedef enum b200_sdpa_status {
   B200_SDPA_OK = 0,
@@ -122,6 +122,17 @@ typedef struct B200SdpaParams {
   uint64_t workspace_bytes;
   int32_t* status;        /* optional device int32[4]: [0] = first error code seen by
                              a kernel (0 = none), [1..3] = where; caller zeroes it     */
+
+  /* Paged key/value cache (decode, L == 1, f16/bf16 only); NULL = dense cache.
+   * With a block table, k and v point at page pools, k_stride / v_stride are the
+   * (page, head, row-in-page, element) strides of a pool, S is the largest context
+   * (<= block_table_stride * page_size), kv_lens is required, and key s of batch b
+   * is row s % page_size of page block_table[b * block_table_stride + s / page_size].
+   * Upstream keeps a dense cache only; this is the layout of the serving engines
+   * that would call the decode kernel.                                               */
+  const int32_t* block_table;   /* (B, block_table_stride) page numbers               */
+  int32_t block_table_stride;
+  int32_t page_size;            /* rows per page, a power of two                      */
 } B200SdpaParams;
 
 /* What the library would do (or did) for a parameter block. */

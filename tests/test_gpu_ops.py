@@ -9,7 +9,7 @@ import torch
 import torch.nn.functional as F
 
 from oracle import sdpa_oracle as O
-from tests.util import HALF_MAX_ABS, make_qkv
+from tests.util import HALF_MAX_ABS, check_against_oracle, make_qkv
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -189,3 +189,33 @@ def test_host_overhead_smoke():
         torch.cuda.synchronize()
         times.append(time.perf_counter() - t0)
     assert sorted(times)[len(times) // 2] < 10e-3
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,causal", [(torch.float32, False), (torch.float32, True), (torch.bfloat16, True)])
+def test_native_multi_head_attn_mid(dtype, causal):
+    # upstream tests/python_ops/test_native_multi_head_attn_mid.py:27-62: [B, H, D, S] operands, [B, H, S, D] result
+    import torch_neuronx_b200 as T
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(4)
+    B, H, D, S = 1, 8, 128, 512
+    q, k, v = (torch.randn(B, H, D, S, generator=g).to(dtype) for _ in range(3))
+    T.reset_launch_counts()
+    got = T.native_multi_head_attn_mid(q.to(dev), k.to(dev), v.to(dev), use_causal_mask=causal, dropout_p=0.0,
+                                       training=False)
+    torch.cuda.synchronize()
+    assert got.shape == (B, H, S, D) and got.dtype == dtype
+    counts = T.launch_counts()
+    assert counts["prefill" if dtype == torch.bfloat16 else "generic"] == 1
+    qt, kt, vt = (t.transpose(-2, -1) for t in (q, k, v))
+    _, lse = O.sdpa_forward(qt, kt, vt, is_causal=causal, compute_dtype=torch.float32)
+    check_against_oracle(qt, kt, vt, got.cpu(), lse, is_causal=causal, tag=f"mha mid {dtype}")
+    # out variant: written in place, same storage returned
+    out = torch.empty(B, H, S, D, dtype=dtype, device=dev)
+    ptr = out.data_ptr()
+    res = T.native_multi_head_attn_mid(q.to(dev), k.to(dev), v.to(dev), use_causal_mask=causal, out=out)
+    torch.cuda.synchronize()
+    assert res.data_ptr() == ptr and torch.equal(res, got)
+    with pytest.raises(RuntimeError, match="do not support empty tensors"):
+        T.native_multi_head_attn_mid(q[:0].to(dev), k[:0].to(dev), v[:0].to(dev))

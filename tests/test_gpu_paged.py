@@ -1,0 +1,79 @@
+"""Decode against a paged key/value cache: same numbers as the dense cache it was cut
+from (the kernel arithmetic is identical, only row addresses differ), oracle parity, both
+pool layouts, ragged lengths, pages in random order."""
+
+import pytest
+import torch
+
+from oracle import sdpa_oracle as O
+from tests.util import check_against_oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _paged_copy(k, v, lens, page_size, layout, seed):
+    """Scatter a dense (B, Hkv, S, D) cache into shuffled pages; returns pools + block table."""
+    B, Hkv, S, D = k.shape
+    max_pages = (S + page_size - 1) // page_size
+    g = torch.Generator().manual_seed(seed)
+    n_pages = B * max_pages + 3
+    order = torch.randperm(n_pages, generator=g)[: B * max_pages].view(B, max_pages).to(torch.int32)
+    kp = torch.full((n_pages, page_size, Hkv, D), float("nan"), dtype=k.dtype)
+    vp = torch.full((n_pages, page_size, Hkv, D), float("nan"), dtype=k.dtype)
+    for b in range(B):
+        for pg in range((int(lens[b]) + page_size - 1) // page_size):
+            rows = slice(pg * page_size, min((pg + 1) * page_size, S))
+            n = rows.stop - rows.start
+            kp[order[b, pg], :n] = k[b, :, rows].transpose(0, 1)
+            vp[order[b, pg], :n] = v[b, :, rows].transpose(0, 1)
+    if layout == "HND":
+        kp, vp = kp.transpose(1, 2).contiguous(), vp.transpose(1, 2).contiguous()
+    return kp, vp, order
+
+
+@pytest.mark.parametrize("layout", ["NHD", "HND"])
+@pytest.mark.parametrize("page_size", [16, 128])
+@pytest.mark.parametrize("dtype,D", [(torch.bfloat16, 128), (torch.float16, 64)])
+def test_paged_decode_matches_dense_and_oracle(dtype, D, page_size, layout):
+    import torch_neuronx_b200 as T
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(5)
+    B, Hq, Hkv, S = 5, 16, 4, 1000
+    q = torch.randn(B, Hq, 1, D, generator=g).to(dtype)
+    k = torch.randn(B, Hkv, S, D, generator=g).to(dtype)
+    v = torch.randn(B, Hkv, S, D, generator=g).to(dtype)
+    lens = torch.tensor([1000, 1, 517, 0, 256], dtype=torch.int32)
+    kp, vp, table = _paged_copy(k, v, lens, page_size, layout, seed=9)
+    T.reset_launch_counts()
+    out, lse = T.paged_decode(q.to(dev), kp.to(dev), vp.to(dev), table.to(dev), lens.to(dev), layout=layout,
+                              need_lse=True)
+    torch.cuda.synchronize()
+    T.check_device_status()
+    counts = T.launch_counts()
+    assert counts["decode_partial"] == 1 and counts["decode_combine"] == 1 and counts["generic"] == 0
+    check_against_oracle(q, k, v, out.cpu(), lse.cpu(), kv_lens=lens, tag=f"paged {layout} page={page_size}")
+    # the dense cache with the same split geometry gives the same bits
+    S_table = table.shape[1] * page_size
+    kd = torch.zeros(B, Hkv, S_table, D, dtype=dtype)
+    vd = torch.zeros(B, Hkv, S_table, D, dtype=dtype)
+    kd[:, :, :S], vd[:, :, :S] = k, v
+    dense_o, dense_l = T.sdpa_forward(q.to(dev), kd.to(dev), vd.to(dev), kv_lens=lens.to(dev))
+    torch.cuda.synchronize()
+    assert torch.equal(out, dense_o) and torch.equal(lse.nan_to_num(neginf=-1.0), dense_l.nan_to_num(neginf=-1.0))
+
+
+def test_paged_decode_rejects_what_it_cannot_serve():
+    import torch_neuronx_b200 as T
+
+    dev = torch.device("cuda", 0)
+    q = torch.zeros(2, 8, 1, 128, dtype=torch.bfloat16, device=dev)
+    pool = torch.zeros(4, 16, 2, 128, dtype=torch.bfloat16, device=dev)
+    table = torch.zeros(2, 2, dtype=torch.int32, device=dev)
+    lens = torch.tensor([5, 7], dtype=torch.int32, device=dev)
+    with pytest.raises(RuntimeError, match="float16 or bfloat16"):
+        T.paged_decode(q.float(), pool.float(), pool.float(), table, lens)
+    with pytest.raises(RuntimeError, match="block_table"):
+        T.paged_decode(q, pool, pool, table.long(), lens)
+    with pytest.raises(RuntimeError):   # page size that is not a power of two
+        T.paged_decode(q, pool[:, :12], pool[:, :12], table, lens)

@@ -16,6 +16,8 @@ from .ops import (
     fused_attention_overrideable,
     fused_attention_overrideable_backward,
     merge_partials,
+    native_multi_head_attn_mid,
+    paged_decode,
     register_aten_override,
     scaled_dot_product_attention,
     scaled_dot_product_attention_backward_kernel,
@@ -43,7 +45,7 @@ reset_launch_counts = _lib.reset_launch_counts
 __all__ = [
     "MaskStructure", "alloc_like_query", "as_units", "check_device_status", "classify_mask", "enable_sdpa_routing",
     "from_units", "fused_attention_overrideable", "fused_attention_overrideable_backward", "launch_counts",
-    "local_units", "merge_partials", "partition_units", "register_aten_override", "reset_launch_counts",
+    "local_units", "merge_partials", "native_multi_head_attn_mid", "paged_decode", "partition_units", "register_aten_override", "reset_launch_counts",
     "ring_attention", "ring_attention_backward", "ring_attention_backward_virtual", "ring_attention_virtual", "scaled_dot_product_attention",
     "scaled_dot_product_attention_backward_kernel", "scaled_dot_product_attention_kernel", "sdpa_backward",
     "sdpa_forward", "set_mask_recognition", "shard_sequence", "unshard_sequence",

@@ -19,7 +19,7 @@ import threading
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libb200_sdpa.so")
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 STATIC_SCRATCH_BYTES = 16 << 20  # B200_SDPA_STATIC_SCRATCH_BYTES
 
 # b200_sdpa_status
@@ -76,6 +76,9 @@ class Params(C.Structure):
         ("workspace", C.c_void_p),
         ("workspace_bytes", C.c_uint64),
         ("status", C.c_void_p),
+        ("block_table", C.c_void_p),
+        ("block_table_stride", C.c_int32),
+        ("page_size", C.c_int32),
     ]
 
 

@@ -50,6 +50,16 @@ int validate(const B200SdpaParams* a, Problem* p) {
   p->bias = a->bias;
   p->bias_dtype = a->bias_dtype;
   p->status = a->status;
+  p->block_table = a->block_table;
+  p->table_stride = a->block_table_stride;
+  p->page_shift = 0;
+  if (a->block_table != nullptr) {
+    const int ps = a->page_size;
+    if (ps < 1 || (ps & (ps - 1)) != 0 || a->block_table_stride < 1) return B200_SDPA_ERR_SHAPE;
+    if (a->kv_lens == nullptr) return B200_SDPA_ERR_NULL;
+    if (static_cast<int64_t>(a->S) > static_cast<int64_t>(a->block_table_stride) * ps) return B200_SDPA_ERR_SHAPE;
+    while ((1 << p->page_shift) < ps) ++p->page_shift;
+  }
   return B200_SDPA_OK;
 }
 
@@ -59,6 +69,13 @@ int choose(const B200SdpaParams* a, const Problem& p, int* path) {
   if (want != B200_SDPA_PATH_AUTO && want != B200_SDPA_PATH_GENERIC && want != B200_SDPA_PATH_PREFILL &&
       want != B200_SDPA_PATH_DECODE)
     return B200_SDPA_ERR_UNSUPPORTED;
+  if (p.block_table != nullptr) {
+    // a paged cache is only understood by the split-KV decode kernel
+    if ((want != B200_SDPA_PATH_AUTO && want != B200_SDPA_PATH_DECODE) || !decode_eligible(p, a->dtype))
+      return B200_SDPA_ERR_UNSUPPORTED;
+    *path = B200_SDPA_PATH_DECODE;
+    return B200_SDPA_OK;
+  }
   if (want == B200_SDPA_PATH_GENERIC) {
     *path = want;
     return B200_SDPA_OK;
@@ -147,6 +164,9 @@ int validate_bwd(const B200SdpaBwdParams* a, BwdProblem& bp) {
   p.bias = a->bias;
   p.bias_dtype = a->bias_dtype;
   p.status = a->status;
+  p.block_table = nullptr;
+  p.table_stride = 0;
+  p.page_shift = 0;
   if (a->force_path != B200_SDPA_PATH_AUTO && a->force_path != B200_SDPA_PATH_GENERIC &&
       a->force_path != B200_SDPA_PATH_PREFILL)
     return B200_SDPA_ERR_UNSUPPORTED;
@@ -226,8 +246,10 @@ int b200_sdpa_fwd(const B200SdpaParams* params, void* stream) {
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (path == B200_SDPA_PATH_DECODE) {
     rc = launch_decode(p, params->dtype, params->kv_chunk, params->workspace, params->workspace_bytes, st);
-    // Without scratch an automatic choice falls through to a kernel that needs none.
-    if (rc != B200_SDPA_ERR_WORKSPACE || params->force_path == B200_SDPA_PATH_DECODE) return rc;
+    // Without scratch an automatic choice falls through to a kernel that needs none
+    // (there is none for a paged cache).
+    if (rc != B200_SDPA_ERR_WORKSPACE || params->force_path == B200_SDPA_PATH_DECODE || p.block_table != nullptr)
+      return rc;
     bool unused = false;
     path = prefill_eligible(p, params->dtype, &unused) ? B200_SDPA_PATH_PREFILL : B200_SDPA_PATH_GENERIC;
   }

@@ -31,6 +31,12 @@ struct Problem {
   int bias_dtype;
   int64_t bs[4];
   int* status;
+  // Paged key/value cache (decode only): when block_table is set, k and v point at page
+  // pools, ks/vs hold (page, head, row-in-page, element) strides and key s of batch b lives
+  // in page block_table[b * table_stride + (s >> page_shift)] at row s & (page_size - 1).
+  const int* block_table;
+  int table_stride;
+  int page_shift;
 };
 
 // Backward: the forward's description (out and lse are inputs here) plus the upstream

@@ -15,6 +15,8 @@
 //     as the A operand of O += P V (V fragments by transposing ldmatrix);
 //   * the four warps' (O, m, l) are merged in shared memory and written as one
 //     partial; decode_combine_kernel merges the splits.
+// A paged cache (page pools + block table, the layout serving engines keep) is read by the
+// same kernel: only the row address of a copy changes -- one table lookup per row.
 // The group of Hq/Hkv query heads is padded to 16 rows; groups above 16 are cut
 // into blocks of 16 (grid.y).  Softmax in the exp2 domain on raw scores, fp32
 // statistics, the running maximum raised lazily (threshold 2^8) so O is rarely
@@ -92,7 +94,7 @@ template <bool BF16> __device__ __forceinline__ uint32_t pack16(float lo, float 
   return r;
 }
 
-template <int D, bool BF16>
+template <int D, bool BF16, bool PAGED>
 __global__ void __launch_bounds__(kThreads, 2) decode_mma_kernel(const Problem p, const int chunk, const int nsplit,
                                                                  float* __restrict__ part_o,
                                                                  float* __restrict__ part_ml) {
@@ -139,9 +141,13 @@ __global__ void __launch_bounds__(kThreads, 2) decode_mma_kernel(const Problem p
   }
 
   // ---- cache block loader: 64 keys of K and of V -> one ring stage
-  const char* kbase = reinterpret_cast<const char*>(p.k) + (b * p.ks[0] + hk * p.ks[1]) * 2;
-  const char* vbase = reinterpret_cast<const char*>(p.v) + (b * p.vs[0] + hk * p.vs[1]) * 2;
+  // dense cache: (batch, head, row, element) strides; paged cache: (page, head, row-in-page, element)
+  // strides and one block-table lookup per row
+  const char* kbase = reinterpret_cast<const char*>(p.k) + ((PAGED ? 0 : b * p.ks[0]) + hk * p.ks[1]) * 2;
+  const char* vbase = reinterpret_cast<const char*>(p.v) + ((PAGED ? 0 : b * p.vs[0]) + hk * p.vs[1]) * 2;
   const int64_t k_row = p.ks[2] * 2, v_row = p.vs[2] * 2;
+  const int* table = PAGED ? p.block_table + static_cast<int64_t>(b) * p.table_stride : nullptr;
+  const int page_mask = (1 << p.page_shift) - 1;
   const uint32_t smem_base = smem_addr(smem);
   auto load_block = [&](int blk) {
     const uint32_t stage = smem_base + (blk % kStages) * G::kStageBytes;
@@ -152,8 +158,18 @@ __global__ void __launch_bounds__(kThreads, 2) decode_mma_kernel(const Problem p
       const int row = c / G::kChunksPerRow, ch = c % G::kChunksPerRow;
       const bool ok = key0 + row < s1;
       const int srow = ok ? key0 + row : s0;
-      cp_async_16(stage + row * G::kRowBytes + ch * 16, kbase + srow * k_row + ch * 16, ok);
-      cp_async_16(stage + G::kTileBytes + row * G::kRowBytes + ch * 16, vbase + srow * v_row + ch * 16, ok);
+      int64_t k_off, v_off;
+      if (PAGED) {
+        const int64_t page = table[srow >> p.page_shift];
+        const int in_page = srow & page_mask;
+        k_off = (page * p.ks[0]) * 2 + in_page * k_row;
+        v_off = (page * p.vs[0]) * 2 + in_page * v_row;
+      } else {
+        k_off = srow * k_row;
+        v_off = srow * v_row;
+      }
+      cp_async_16(stage + row * G::kRowBytes + ch * 16, kbase + k_off + ch * 16, ok);
+      cp_async_16(stage + G::kTileBytes + row * G::kRowBytes + ch * 16, vbase + v_off + ch * 16, ok);
     }
   };
 
@@ -306,11 +322,11 @@ __global__ void __launch_bounds__(kThreads, 2) decode_mma_kernel(const Problem p
   }
 }
 
-template <int D, bool BF16>
+template <int D, bool BF16, bool PAGED>
 int launch_one(const Problem& p, int chunk, int nsplit, float* po, float* pml, cudaStream_t stream) {
   using G = Geo<D>;
   static_assert(kWarps * 16 * D * 4 + kWarps * 16 * 2 * 4 <= G::kSmemBytes, "merge buffer must fit in the ring");
-  auto kern = decode_mma_kernel<D, BF16>;
+  auto kern = decode_mma_kernel<D, BF16, PAGED>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G::kSmemBytes) != cudaSuccess) {
     cudaGetLastError();
     return B200_SDPA_ERR_CUDA;
@@ -335,12 +351,20 @@ bool decode_mma_eligible(const Problem& p, int dtype) {
 int launch_decode_partial_mma(const Problem& p, int dtype, int chunk, int nsplit, float* po, float* pml,
                               cudaStream_t stream) {
   const bool bf16 = dtype == B200_SDPA_BF16;
-  if (p.E == 128) {
-    return bf16 ? launch_one<128, true>(p, chunk, nsplit, po, pml, stream)
-                : launch_one<128, false>(p, chunk, nsplit, po, pml, stream);
+  if (p.block_table != nullptr) {
+    if (p.E == 128) {
+      return bf16 ? launch_one<128, true, true>(p, chunk, nsplit, po, pml, stream)
+                  : launch_one<128, false, true>(p, chunk, nsplit, po, pml, stream);
+    }
+    return bf16 ? launch_one<64, true, true>(p, chunk, nsplit, po, pml, stream)
+                : launch_one<64, false, true>(p, chunk, nsplit, po, pml, stream);
   }
-  return bf16 ? launch_one<64, true>(p, chunk, nsplit, po, pml, stream)
-              : launch_one<64, false>(p, chunk, nsplit, po, pml, stream);
+  if (p.E == 128) {
+    return bf16 ? launch_one<128, true, false>(p, chunk, nsplit, po, pml, stream)
+                : launch_one<128, false, false>(p, chunk, nsplit, po, pml, stream);
+  }
+  return bf16 ? launch_one<64, true, false>(p, chunk, nsplit, po, pml, stream)
+              : launch_one<64, false, false>(p, chunk, nsplit, po, pml, stream);
 }
 
 }  // namespace b200

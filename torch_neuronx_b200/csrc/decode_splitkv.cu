@@ -299,6 +299,7 @@ bool use_mma_partial(const Problem& p, int dtype) {
     const char* e = getenv("B200_SDPA_DECODE_SIMT");
     return e != nullptr && e[0] == '1';
   }();
+  if (p.block_table != nullptr) return true;   // a paged cache is only read by the tensor-core kernel
   return !forced_simt && decode_mma_eligible(p, dtype);
 }
 
@@ -316,6 +317,7 @@ int launch_g(const Problem& p, const DecodeGeom& gm, float* po, float* pml, cuda
 
 bool decode_eligible(const Problem& p, int dtype) {
   if (p.L != 1 || p.bias != nullptr || p.E != p.Dv) return false;
+  if (p.block_table != nullptr && !decode_mma_eligible(p, dtype)) return false;   // paged: 16-bit caches only
   if (p.E != 64 && p.E != 128) return false;
   if (p.B > 65535 || static_cast<int64_t>(p.Hkv) * ((p.group + 7) / 8) > 65535) return false;
   // is_causal with one query row only limits keys to j <= causal_shift; the host

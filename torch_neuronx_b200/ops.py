@@ -264,6 +264,96 @@ def sdpa_forward(
     return out, lse
 
 
+def paged_decode(
+    query: torch.Tensor,
+    k_pages: torch.Tensor,
+    v_pages: torch.Tensor,
+    block_table: torch.Tensor,
+    kv_lens: torch.Tensor,
+    *,
+    scale: Optional[float] = None,
+    layout: str = "NHD",
+    out: Optional[torch.Tensor] = None,
+    lse: Optional[torch.Tensor] = None,
+    need_lse: bool = False,
+    kv_chunk: int = 0,
+):
+    """One decode step against a paged key/value cache; returns ``(out, lse)``.
+
+    ``query`` is ``(B, Hq, 1, D)``; ``k_pages`` / ``v_pages`` are page pools,
+    ``(pages, page_size, Hkv, D)`` for ``layout="NHD"`` or ``(pages, Hkv, page_size, D)``
+    for ``"HND"`` (any strides with a unit inner stride); ``block_table`` is int32
+    ``(B, max_pages)`` and ``kv_lens`` int32 ``(B,)``.  Key ``s`` of sequence ``b`` is row
+    ``s % page_size`` of page ``block_table[b, s // page_size]``.  The split-KV decode
+    kernel reads the pages in place -- no gather into a dense cache.  Upstream's decode
+    runs the same op on a dense cache (``torch_mlir/ops/scaled_dot_product_attention.py:64-68``);
+    the paged layout is what a serving loop around that op keeps."""
+    lib = _lib.load()
+    if layout not in ("NHD", "HND"):
+        raise ValueError("layout must be 'NHD' or 'HND'")
+    if query.dim() != 4 or query.shape[2] != 1 or k_pages.dim() != 4 or v_pages.dim() != 4:
+        raise RuntimeError("paged_decode: query must be (B, Hq, 1, D) and the page pools 4-D")
+    if query.dtype not in (torch.float16, torch.bfloat16) or k_pages.dtype != query.dtype or v_pages.dtype != query.dtype:
+        raise RuntimeError("paged_decode: query and the page pools must share a float16 or bfloat16 dtype")
+    if not (query.is_cuda and k_pages.device == query.device and v_pages.device == query.device):
+        raise ValueError(f"Expected CUDA tensors on one device, got {query.device}, {k_pages.device}, {v_pages.device}")
+    dev = _device_index(query)
+    B, Hq, _, E = query.shape
+    hd, rd = (2, 1) if layout == "NHD" else (1, 2)
+    Hkv, page_size = k_pages.shape[hd], k_pages.shape[rd]
+    if k_pages.shape != v_pages.shape or k_pages.shape[3] != E:
+        raise RuntimeError("paged_decode: k_pages and v_pages must have the same shape and the query's head dim")
+    if Hkv == 0 or Hq % Hkv != 0:
+        raise RuntimeError("SDPA: Number of heads in key and value must divide the number of heads in query")
+    if block_table.dtype != torch.int32 or block_table.dim() != 2 or block_table.shape[0] != B or block_table.device != query.device:
+        raise RuntimeError("paged_decode: block_table must be an int32 CUDA tensor of shape (B, max_pages)")
+    if kv_lens.dtype != torch.int32 or kv_lens.shape != (B,) or kv_lens.device != query.device:
+        raise RuntimeError("kv_lens must be an int32 CUDA tensor of shape (B,) on the query's device")
+    block_table = block_table.contiguous()
+    kv_lens = kv_lens.contiguous()
+    if scale is None:
+        scale = 1.0 / math.sqrt(E)
+    if out is None:
+        out = torch.empty_like(query)
+    if lse is None and need_lse:
+        lse = torch.empty((B, Hq, 1), dtype=torch.float32, device=query.device)
+
+    p = _lib.Params()
+    p.struct_size = C.sizeof(_lib.Params)
+    p.dtype = _DTYPE_CODE[query.dtype]
+    p.device = dev
+    p.force_path = _lib.PATH_DECODE
+    p.q, p.k, p.v, p.out = query.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr()
+    p.lse = lse.data_ptr() if lse is not None else None
+    p.q_stride[:] = query.stride()
+    p.k_stride[:] = [k_pages.stride(0), k_pages.stride(hd), k_pages.stride(rd), k_pages.stride(3)]
+    p.v_stride[:] = [v_pages.stride(0), v_pages.stride(hd), v_pages.stride(rd), v_pages.stride(3)]
+    p.out_stride[:] = out.stride()
+    if lse is not None:
+        p.lse_stride[:] = lse.stride()
+    p.B, p.Hq, p.Hkv, p.L, p.E, p.Dv = B, Hq, Hkv, 1, E, E
+    p.S = block_table.shape[1] * page_size
+    p.scale = float(scale)
+    p.kv_lens = kv_lens.data_ptr()
+    p.block_table = block_table.data_ptr()
+    p.block_table_stride = block_table.shape[1]
+    p.page_size = page_size
+    p.kv_chunk = int(kv_chunk)
+    p.status = _status_word(dev).data_ptr()
+    plan = _lib.Plan()
+    plan.struct_size = C.sizeof(_lib.Plan)
+    rc = lib.b200_sdpa_query_plan(C.byref(p), C.byref(plan))
+    if rc != _lib.OK:
+        raise RuntimeError(f"b200_sdpa_query_plan: {_lib.strerror(rc)}")
+    ws = _workspace(dev, int(plan.workspace_bytes))
+    p.workspace = ws.data_ptr()
+    p.workspace_bytes = ws.numel()
+    rc = lib.b200_sdpa_decode(C.byref(p), C.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+    if rc != _lib.OK:
+        raise RuntimeError(f"b200_sdpa_decode: {_lib.strerror(rc)}")
+    return out, lse
+
+
 def sdpa_backward(
     grad_out: torch.Tensor,
     query: torch.Tensor,
@@ -554,6 +644,42 @@ def scaled_dot_product_attention_kernel(
     (``nki_kernels/scaled_dot_product_attention.py:44-86``): returns the attention
     output; with ``training=True`` the fp32 log-sum-exp is written into ``lse``."""
     return torch.ops.b200_sdpa.fwd(q, k, v, is_causal, dropout_p, scale, training, seed, lse, kv_lens=kv_lens)
+
+
+# ----------------------------------------------------------------------------
+# middle stage of native multi-head attention (inference caller of the same kernels)
+# ----------------------------------------------------------------------------
+
+
+def native_multi_head_attn_mid(query, key, value, *, use_causal_mask=False, dropout_p=0.0, training=False, out=None):
+    """The attention stage of upstream's split ``native_multi_head_attention``
+    (``python_ops/native_multi_head_attn_mid.py:66-157``,
+    ``python_ops/torch_mlir/ops/native_multi_head_attn_mid.py:58-114``): q, k and v arrive
+    in ``[B, H, D, S]`` layout, the result is ``[B, Hq, S_q, D_v]``; no log-sum-exp is
+    produced, ``training`` does not change the computation, and ``out`` (if given) is
+    written in place and returned.
+
+    The ``[B, H, D, S]`` operands are the ``[B, H, S, D]`` operands seen through a
+    transpose, which the kernels take as strides.  Half-precision inputs with a head
+    dimension the tensor-core kernels serve are first re-laid out with the head dimension
+    innermost (one streaming copy, far cheaper than leaving the call on CUDA cores)."""
+    for name, t in (("query", query), ("key", key), ("value", value)):
+        if not isinstance(t, torch.Tensor) or t.dim() != 4:
+            raise RuntimeError(f"native_multi_head_attn_mid: {name} must be a 4-D tensor [B, H, D, S]")
+    if query.numel() == 0 or key.numel() == 0 or value.numel() == 0:
+        raise RuntimeError(
+            "Attention operations do not support empty tensors. Please ensure all input tensors have non-zero elements."
+        )
+    q, k, v = query.transpose(-2, -1), key.transpose(-2, -1), value.transpose(-2, -1)
+    _validate(q, k, v, None, dropout_p, use_causal_mask, False)
+    if q.dtype in (torch.float16, torch.bfloat16) and q.shape[3] == v.shape[3] and q.shape[3] in (64, 128):
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    B, Hq, L, _ = q.shape
+    if out is not None:
+        if tuple(out.shape) != (B, Hq, L, v.shape[3]) or out.dtype != q.dtype or out.device != q.device:
+            raise RuntimeError("native_multi_head_attn_mid: out must be [B, Hq, S_q, D_v] in the input dtype on the input device")
+    result, _ = sdpa_forward(q, k, v, is_causal=bool(use_causal_mask), need_lse=False, out=out)
+    return result
 
 
 # ----------------------------------------------------------------------------
