@@ -22,15 +22,16 @@
 // forward, :94).  Roles per CTA (320 threads): warps 0-7 elementwise (two threads per TMEM
 // lane), warp 8 TMA producer, warp 9 MMA issuer.
 //
-// Both kernels work in units of 64 score columns (half an operand tile) with the two
-// score-shaped accumulators double-buffered in tensor memory, so the elementwise role
-// works on unit u+1 while the tensor cores run the accumulating products of unit u and the
-// score products of unit u+2:
-//   TMEM columns  [0,64) [64,128)  S   buffers 0/1      [128,192) [192,256)  dP  buffers 0/1
-//                 [256, ...)       the fp32 gradient accumulators (dQ, or dV and dK)
-// The MMA pipe executes in issue order, which is what makes "score products of u+2 after
-// the accumulating products of u" safe on the shared buffer.  Every wait is bounded (see
-// tc_common.cuh).
+// The dK/dV kernel works in units of 64 score columns (half an operand tile) with the two
+// score-shaped accumulators double-buffered in tensor memory, so the elementwise role works
+// on unit u+1 while the tensor cores run the accumulating products of unit u and the score
+// products of unit u+2 (the MMA pipe executes in issue order, which makes "scores of u+2
+// after the accumulating products of u" safe on the shared buffer):
+//   TMEM columns  [0,64) [64,128)  S^T buffers 0/1   [128,192) [192,256)  dP^T buffers 0/1
+//                 [256, 256+2D)    dV and dK (fp32)
+// Its tensor memory is full with that; the dQ kernel has one accumulator less and works on
+// whole 128-column tiles instead (layout and pipeline described at the kernel).
+// Every wait is bounded (see tc_common.cuh).
 #include "tc_common.cuh"
 
 namespace b200 {
@@ -59,6 +60,23 @@ template <int D> struct BCfg {
   static constexpr int kSmemBytes = kSmemTiles + kStatBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
+// Development only (-DB200_TRACE): time stamps of CTA 0.  g_btrace[kernel][role][step][event]
+#ifdef B200_TRACE
+__device__ long long g_btrace[2][3][64][4];
+#define BTRACE(kern, role, step, ev)                                                          \
+  do {                                                                                        \
+    if (blockIdx.x == 0 && (step) < 64) g_btrace[kern][role][step][ev] = clock64();           \
+  } while (0)
+__device__ long long g_cta[8192][8];
+#define CTRACE(ev)                                                                 \
+  do {                                                                             \
+    if (blockIdx.x < 8192) g_cta[blockIdx.x][ev] = clock64();                      \
+  } while (0)
+#else
+#define BTRACE(kern, role, step, ev)
+#define CTRACE(ev)
+#endif
+
 struct BSync {
   uint64_t fixed_full;
   uint64_t ring_full[kMaxStages];
@@ -74,42 +92,51 @@ struct BSync {
 
 // ------------------------------------------------------------------ prep --
 
-template <typename T>
-__global__ void bwd_prep_kernel(const BwdProblem bp, float* __restrict__ lse2, float* __restrict__ delta,
-                                const int l_pad, const int vec4) {
+// Eight lanes per row (four rows per warp) when rows can be read 16 bytes at a time,
+// otherwise one warp per row with scalar loads.
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(256) bwd_prep_kernel(const BwdProblem bp, float* __restrict__ lse2,
+                                                        float* __restrict__ delta, const int l_pad) {
   const Problem& p = bp.f;
-  const long long warp_id = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  constexpr int kLanes = VEC ? 8 : 32;             // lanes cooperating on one row
+  constexpr int kRowsPerWarp = 32 / kLanes;
+  const long long gwarp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
+  const int sub = lane % kLanes;
+  const long long row_id = gwarp * kRowsPerWarp + lane / kLanes;
   const long long total = static_cast<long long>(p.B) * p.Hq * l_pad;
-  if (warp_id >= total) return;
-  const int i = static_cast<int>(warp_id % l_pad);
-  const long long bh = warp_id / l_pad;
+  const bool in_range = row_id < total;
+  const int i = in_range ? static_cast<int>(row_id % l_pad) : 0;
+  const long long bh = in_range ? row_id / l_pad : 0;
   const int h = static_cast<int>(bh % p.Hq);
   const int b = static_cast<int>(bh / p.Hq);
   float d = 0.f, l2 = CUDART_INF_F;
-  if (i < p.L) {
+  const bool live = in_range && i < p.L;
+  if (live) {
     const T* __restrict__ go = reinterpret_cast<const T*>(bp.dout) + b * bp.dos[0] + h * bp.dos[1] + i * bp.dos[2];
     const T* __restrict__ o = reinterpret_cast<const T*>(p.out) + b * p.os[0] + h * p.os[1] + i * p.os[2];
-    if (vec4) {   // unit inner strides, rows 8-byte aligned: four elements per load
-      for (int e = lane * 4; e < p.Dv; e += 128) {
-        const uint2 a = *reinterpret_cast<const uint2*>(go + e);
-        const uint2 c = *reinterpret_cast<const uint2*>(o + e);
+    if (VEC) {
+      for (int e = sub * 8; e < p.Dv; e += 64) {
+        const uint4 a = *reinterpret_cast<const uint4*>(go + e);
+        const uint4 c = *reinterpret_cast<const uint4*>(o + e);
         const T* av = reinterpret_cast<const T*>(&a);
         const T* cv = reinterpret_cast<const T*>(&c);
 #pragma unroll
-        for (int u = 0; u < 4; ++u) d = fmaf(to_f32<T>(av[u]), to_f32<T>(cv[u]), d);
+        for (int u = 0; u < 8; ++u) d = fmaf(to_f32<T>(av[u]), to_f32<T>(cv[u]), d);
       }
     } else {
-      for (int e = lane; e < p.Dv; e += 32) d = fmaf(to_f32<T>(go[e * bp.dos[3]]), to_f32<T>(o[e * p.os[3]]), d);
+      for (int e = sub; e < p.Dv; e += 32) d = fmaf(to_f32<T>(go[e * bp.dos[3]]), to_f32<T>(o[e * p.os[3]]), d);
     }
+  }
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
+  for (int off = kLanes / 2; off > 0; off >>= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
+  if (live && sub == 0) {
     const float l = p.lse[b * p.ls[0] + h * p.ls[1] + i * p.ls[2]];
     l2 = (l == -CUDART_INF_F) ? CUDART_INF_F : l * kLog2e;
   }
-  if (lane == 0) {
-    lse2[warp_id] = l2;
-    delta[warp_id] = d;
+  if (in_range && sub == 0) {
+    lse2[row_id] = l2;
+    delta[row_id] = live ? d : 0.f;
   }
 }
 
@@ -199,6 +226,37 @@ __device__ __forceinline__ void drain_after_abort(BSync* sync, long long wait_li
 }
 
 // ------------------------------------------------------------------ dQ kernel --
+//
+// Whole 128-key tiles per step (a 128-column score product costs the tensor pipe the same
+// as a 64-column one).  The elementwise role copies S and dP of a tile into registers and
+// releases the two accumulators at once, so the score products of tile j+1 run while it
+// computes dS of tile j; dS goes to one of two operand buffers, so dQ += dS K of tile j runs
+// while tile j+1 is being computed.  K tiles live until their dQ product, V tiles only until
+// their dP product, hence separate rings (3 and 2 slots).
+//   TMEM columns: [0,128) S, [128,256) dP, [256,320) [320,384) dS operand buffers, [384, 384+D) dQ
+
+template <int D> struct ACfg {
+  static constexpr int kBoxes = D / 64;
+  static constexpr int kTileBytes = kT * D * 2;
+  static constexpr int kKSlots = 3, kVSlots = 2;
+  static constexpr int kSmemTiles = (2 + kKSlots + kVSlots) * kTileBytes;
+  static constexpr int kSmemBytes = kSmemTiles + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+struct ASync {
+  uint64_t fixed_full;
+  uint64_t k_full[3], k_empty[3];
+  uint64_t v_full[2], v_empty[2];
+  uint64_t sp_full;      // S and dP of a tile are complete
+  uint64_t f_free;       // the elementwise role holds them in registers
+  uint64_t e_ready[2];   // dS of a tile is in its operand buffer
+  uint64_t op_empty[2];  // the product reading an operand buffer has retired
+  uint64_t acc_done;
+  uint64_t staged;
+  uint64_t drain;
+  uint32_t tmem_base;
+  int abort_flag;
+};
 
 template <int D, bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -206,11 +264,19 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                  const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
                  const __grid_constant__ CUtensorMap tm_dq, const Problem p, const float* __restrict__ lse2,
                  const float* __restrict__ delta, const int l_pad, const int n_qblk, const long long wait_limit) {
-  using C = BCfg<D>;
+  using C = ACfg<D>;
   extern __shared__ uint8_t smem_raw[];
+#ifdef B200_TRACE
+  if (threadIdx.x == 0) {
+    CTRACE(0);
+    unsigned smid;
+    asm("mov.u32 %0, %smid;" : "=r"(smid));
+    if (blockIdx.x < 8192) g_cta[blockIdx.x][7] = smid;
+  }
+#endif
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t tiles = (raw_addr + 1023u) & ~1023u;
-  BSync* sync = reinterpret_cast<BSync*>(smem_raw + (tiles - raw_addr) + C::kSmemTiles + C::kStatBytes);
+  ASync* sync = reinterpret_cast<ASync*>(smem_raw + (tiles - raw_addr) + C::kSmemTiles);
   volatile int* abort_flag = &sync->abort_flag;
 
   const int tid = threadIdx.x;
@@ -236,17 +302,21 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   if (end < 0) end = 0;
   if (first < -1) first = -1;
   const int n_tiles = static_cast<int>((end + kT - 1) / kT);
-  const int n_units = static_cast<int>((end + kU - 1) / kU);   // 64-key units; the last tile may need only one
   const int min_lim = static_cast<int>(first);
 
   const uint32_t q_tile = tiles, do_tile = tiles + C::kTileBytes;
-  const uint32_t ring = tiles + 2 * C::kTileBytes;   // slot s: K at ring + 2 s tile, V right after
+  const uint32_t k_ring = tiles + 2 * C::kTileBytes;
+  const uint32_t v_ring = k_ring + C::kKSlots * C::kTileBytes;
 
   if (warp == kProducerWarp && lane == 0) {
     mbar_init(smem_u32(&sync->fixed_full), 1);
-    for (int s = 0; s < C::kStages; ++s) {
-      mbar_init(smem_u32(&sync->ring_full[s]), 1);
-      mbar_init(smem_u32(&sync->ring_empty[s]), 1);
+    for (int s = 0; s < C::kKSlots; ++s) {
+      mbar_init(smem_u32(&sync->k_full[s]), 1);
+      mbar_init(smem_u32(&sync->k_empty[s]), 1);
+    }
+    for (int s = 0; s < C::kVSlots; ++s) {
+      mbar_init(smem_u32(&sync->v_full[s]), 1);
+      mbar_init(smem_u32(&sync->v_empty[s]), 1);
     }
     mbar_fence_init();
     if (n_tiles > 0) {
@@ -259,7 +329,19 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     }
     prefetch_tmap(&tm_dq);
   }
-  if (tid == 0) init_common_barriers(sync);
+  if (tid == 0) {
+    mbar_init(smem_u32(&sync->sp_full), 1);
+    mbar_init(smem_u32(&sync->f_free), kEThreads);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&sync->e_ready[i]), kEThreads);
+      mbar_init(smem_u32(&sync->op_empty[i]), 1);
+    }
+    mbar_init(smem_u32(&sync->acc_done), 1);
+    mbar_init(smem_u32(&sync->staged), kEThreads);
+    mbar_init(smem_u32(&sync->drain), 1);
+    sync->abort_flag = 0;
+    mbar_fence_init();
+  }
   if (warp == kMmaWarp) {
     tmem_alloc(smem_u32(&sync->tmem_base), kTmemCols);
     tmem_relinquish();
@@ -268,23 +350,34 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = sync->tmem_base;
-  constexpr uint32_t kColDQ = kColAcc;
+  constexpr uint32_t kColS = 0, kColDP = 128, kColOp = 256, kColDQ = 384;
+  if (tid == 0) CTRACE(1);
 
   if (warp == kProducerWarp) {
     if (lane == 0) {
       for (int j = 0; j < n_tiles; ++j) {
-        const int stage = j % C::kStages;
-        const uint32_t round = static_cast<uint32_t>(j / C::kStages);
-        if (round > 0 && !wait_clocked(smem_u32(&sync->ring_empty[stage]), (round - 1) & 1u, abort_flag, wait_limit)) {
-          report(p.status, 11, j, stage);
+        const int ks = j % C::kKSlots, vs = j % C::kVSlots;
+        if (j >= C::kKSlots &&
+            !wait_clocked(smem_u32(&sync->k_empty[ks]), (j / C::kKSlots - 1) & 1u, abort_flag, wait_limit)) {
+          report(p.status, 11, j, ks);
           break;
         }
-        const uint32_t bar = smem_u32(&sync->ring_full[stage]);
-        const uint32_t dst = ring + stage * 2 * C::kTileBytes;
-        mbar_arrive_expect_tx(bar, 2 * C::kTileBytes);
-        for (int bx = 0; bx < C::kBoxes; ++bx) {
-          tma_load_4d(dst + bx * kBoxBytes, &tm_k, bar, bx * 64, j * kT, hk, b);
-          tma_load_4d(dst + C::kTileBytes + bx * kBoxBytes, &tm_v, bar, bx * 64, j * kT, hk, b);
+        {
+          const uint32_t bar = smem_u32(&sync->k_full[ks]);
+          mbar_arrive_expect_tx(bar, C::kTileBytes);
+          for (int bx = 0; bx < C::kBoxes; ++bx)
+            tma_load_4d(k_ring + ks * C::kTileBytes + bx * kBoxBytes, &tm_k, bar, bx * 64, j * kT, hk, b);
+        }
+        if (j >= C::kVSlots &&
+            !wait_clocked(smem_u32(&sync->v_empty[vs]), (j / C::kVSlots - 1) & 1u, abort_flag, wait_limit)) {
+          report(p.status, 11, j, 8 + vs);
+          break;
+        }
+        {
+          const uint32_t bar = smem_u32(&sync->v_full[vs]);
+          mbar_arrive_expect_tx(bar, C::kTileBytes);
+          for (int bx = 0; bx < C::kBoxes; ++bx)
+            tma_load_4d(v_ring + vs * C::kTileBytes + bx * kBoxBytes, &tm_v, bar, bx * 64, j * kT, hk, b);
         }
       }
       if (*abort_flag != 0) {
@@ -293,59 +386,86 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     }
     __syncwarp();
   } else if (warp == kMmaWarp) {
-    constexpr uint32_t idesc_score = make_idesc(BF16, false, kT, kU);
+    constexpr uint32_t idesc_score = make_idesc(BF16, false, kT, kT);
     constexpr uint32_t idesc_acc = make_idesc(BF16, true, kT, D);
-    bool alive = n_units > 0;
+    bool alive = n_tiles > 0;
     if (alive) {
       alive = wait_clocked(smem_u32(&sync->fixed_full), 0, abort_flag, wait_limit);
       if (!alive && lane == 0) report(p.status, 12, -1, 0);
     }
-    // S_u = Q K_u^T and dP_u = dO V_u^T into buffer u & 1 (waits for the key tile when the unit opens it)
-    auto issue_scores = [&](int u) -> bool {
-      const int j = u >> 1, hh = u & 1, buf = u & 1;
-      const int stage = j % C::kStages;
-      if (hh == 0) {
-        const uint32_t round = static_cast<uint32_t>(j / C::kStages);
-        if (!wait_clocked(smem_u32(&sync->ring_full[stage]), round & 1u, abort_flag, wait_limit)) {
-          if (lane == 0) report(p.status, 12, j, stage);
-          return false;
-        }
-        tc_fence_after_sync();
+    // S_j = Q K_j^T, dP_j = dO V_j^T over whole tiles
+    auto issue_scores = [&](int j) -> bool {
+      const int ks = j % C::kKSlots, vs = j % C::kVSlots;
+      if (!wait_clocked(smem_u32(&sync->k_full[ks]), (j / C::kKSlots) & 1u, abort_flag, wait_limit) ||
+          !wait_clocked(smem_u32(&sync->v_full[vs]), (j / C::kVSlots) & 1u, abort_flag, wait_limit)) {
+        if (lane == 0) report(p.status, 12, j, ks);
+        return false;
       }
-      const uint32_t k_tile = ring + stage * 2 * C::kTileBytes, v_tile = k_tile + C::kTileBytes;
-      issue_ss<D>(tmem_base + kColS + buf * kU, q_tile, k_tile, hh, idesc_score);
-      issue_ss<D>(tmem_base + kColDP + buf * kU, do_tile, v_tile, hh, idesc_score);
-      if (elect_one()) mma_commit(smem_u32(&sync->sp_full[buf]));
+      tc_fence_after_sync();
+      const uint64_t qd = kmajor_desc(q_tile), kd = kmajor_desc(k_ring + ks * C::kTileBytes);
+      const uint64_t od = kmajor_desc(do_tile), vd = kmajor_desc(v_ring + vs * C::kTileBytes);
+      if (elect_one()) {
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          mma_ss(tmem_base + kColS, qd + kmajor_step(kk), kd + kmajor_step(kk), idesc_score, kk > 0 ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          mma_ss(tmem_base + kColDP, od + kmajor_step(kk), vd + kmajor_step(kk), idesc_score, kk > 0 ? 1u : 0u);
+        mma_commit(smem_u32(&sync->sp_full));
+        mma_commit(smem_u32(&sync->v_empty[vs]));   // V_j has no reader after dP_j
+      }
       return true;
     };
     if (alive) alive = issue_scores(0);
-    if (alive && n_units > 1) alive = issue_scores(1);
-    for (int u = 0; u < n_units && alive; ++u) {
-      const int j = u >> 1, hh = u & 1, buf = u & 1;
-      const int stage = j % C::kStages;
-      alive = wait_clocked(smem_u32(&sync->e_ready[buf]), (u >> 1) & 1, abort_flag, wait_limit);
+    for (int j = 0; j < n_tiles && alive; ++j) {
+      const int buf = j & 1, ks = j % C::kKSlots;
+      // S_j and dP_j are in registers: the next tile's score products may overwrite them
+      alive = wait_clocked(smem_u32(&sync->f_free), j & 1, abort_flag, wait_limit);
       if (!alive) {
-        if (lane == 0) report(p.status, 13, u, 0);
+        if (lane == 0) report(p.status, 13, j, 1);
         break;
       }
       tc_fence_after_sync();
-      const uint32_t k_tile = ring + stage * 2 * C::kTileBytes;
-      issue_ts(tmem_base + kColDQ, tmem_base + kColDP + buf * kU, k_tile, hh, idesc_acc, u > 0);   // dQ += dS_u K_u
-      if (elect_one()) {
-        if (hh == 1 || u + 1 == n_units) mma_commit(smem_u32(&sync->ring_empty[stage]));
-        if (u + 1 == n_units) mma_commit(smem_u32(&sync->acc_done));
+      if (lane == 0) BTRACE(0, 2, j, 0);
+      if (j + 1 < n_tiles) {
+        alive = issue_scores(j + 1);
+        if (!alive) break;
       }
-      if (u + 2 < n_units) alive = issue_scores(u + 2);
+      if (lane == 0) BTRACE(0, 2, j, 1);
+      alive = wait_clocked(smem_u32(&sync->e_ready[buf]), (j >> 1) & 1, abort_flag, wait_limit);
+      if (!alive) {
+        if (lane == 0) report(p.status, 13, j, 0);
+        break;
+      }
+      tc_fence_after_sync();
+      if (lane == 0) BTRACE(0, 2, j, 2);
+      const uint64_t bd = mnmajor_desc(k_ring + ks * C::kTileBytes);
+      if (elect_one()) {
+#pragma unroll
+        for (int kk = 0; kk < kT / 16; ++kk)   // dQ += dS_j K_j
+          mma_ts(tmem_base + kColDQ, tmem_base + kColOp + buf * 64 + static_cast<uint32_t>(kk * 8), bd + mnmajor_step(kk),
+                 idesc_acc, (kk > 0 || j > 0) ? 1u : 0u);
+        mma_commit(smem_u32(&sync->op_empty[buf]));
+        mma_commit(smem_u32(&sync->k_empty[ks]));
+        if (j + 1 == n_tiles) mma_commit(smem_u32(&sync->acc_done));
+      }
+      if (lane == 0) BTRACE(0, 2, j, 3);
     }
-    if (*abort_flag != 0) drain_after_abort(sync, wait_limit);
+    if (*abort_flag != 0) {
+      if (elect_one()) mma_commit(smem_u32(&sync->drain));
+      const long long t0 = clock64();
+      while (!mbar_try_wait(smem_u32(&sync->drain), 0) && clock64() - t0 < wait_limit) {
+      }
+    }
     __syncwarp();
   } else {
     // -------------------------------------------------------- elementwise role
     const int r = tid & (kT - 1);              // query row inside the tile = TMEM lane
-    const int half = tid >> 7;                 // which 32 of the unit's 64 score columns
+    const int half = tid >> 7;                 // which 64 of the tile's 128 score columns
     const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t s_addr = tmem_base + lane_off + kColS + half * 32;
-    const uint32_t dp_addr = tmem_base + lane_off + kColDP + half * 32;
+    const uint32_t s_addr = tmem_base + lane_off + kColS + half * 64;
+    const uint32_t dp_addr = tmem_base + lane_off + kColDP + half * 64;
+    const uint32_t op_addr = tmem_base + lane_off + kColOp + half * 32;
     const uint32_t dq_addr = tmem_base + lane_off + kColDQ;
     const int row_g = row0 + r;
     int lim = kv_limit;
@@ -358,25 +478,34 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const float dl = delta[stat_idx];
     const float sl2 = p.scale * kLog2e;
     bool alive = true;
-    for (int u = 0; u < n_units; ++u) {
-      const int buf = u & 1;
-      bool ok = wait_clocked(smem_u32(&sync->sp_full[buf]), (u >> 1) & 1, abort_flag, wait_limit);
+    for (int j = 0; j < n_tiles; ++j) {
+      const int buf = j & 1;
+      bool ok = wait_clocked(smem_u32(&sync->sp_full), j & 1, abort_flag, wait_limit);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
-        if (lane == 0) report(p.status, 14, u, warp);
+        if (lane == 0) report(p.status, 14, j, warp);
         alive = false;
         break;
       }
       tc_fence_after_sync();
-      const int col0 = u * kU + half * 32;
-      const bool need_mask = u * kU + kU > min_lim;
-      uint32_t sv[32], dv[32];
-      tmem_ld_32x32(s_addr + buf * kU, sv);
-      tmem_ld_32x32(dp_addr + buf * kU, dv);
+      if (tid == 0) BTRACE(0, 0, j, 0);
+      if (tid == 128) BTRACE(0, 1, j, 0);
+      if (tid == 0 && j == 0) CTRACE(2);
+      uint32_t sv[64], dv[64];
+      tmem_ld_32x32(s_addr, reinterpret_cast<uint32_t(&)[32]>(sv[0]));
+      tmem_ld_32x32(s_addr + 32, reinterpret_cast<uint32_t(&)[32]>(sv[32]));
+      tmem_ld_32x32(dp_addr, reinterpret_cast<uint32_t(&)[32]>(dv[0]));
+      tmem_ld_32x32(dp_addr + 32, reinterpret_cast<uint32_t(&)[32]>(dv[32]));
       tmem_ld_wait();
-      uint32_t pk[16];
+      tc_fence_before_sync();
+      mbar_arrive(smem_u32(&sync->f_free));
+      if (tid == 0) BTRACE(0, 0, j, 1);
+      if (tid == 128) BTRACE(0, 1, j, 1);
+      const int col0 = j * kT + half * 64;
+      const bool need_mask = j * kT + kT > min_lim;
+      uint32_t pk[32];
 #pragma unroll
-      for (int i = 0; i < 32; i += 2) {
+      for (int i = 0; i < 64; i += 2) {
         float p0 = ex2(fmaf(__uint_as_float(sv[i]), sl2, neg_l2));
         float p1 = ex2(fmaf(__uint_as_float(sv[i + 1]), sl2, neg_l2));
         if (need_mask) {
@@ -385,12 +514,26 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         }
         pk[i >> 1] = pack2<BF16>(p0 * (__uint_as_float(dv[i]) - dl), p1 * (__uint_as_float(dv[i + 1]) - dl));
       }
-      // 16 packed columns land on dP columns this thread has just read (and that the other
-      // column half never touches)
-      tmem_st_32x16(dp_addr + buf * kU, pk);
+      if (tid == 0) BTRACE(0, 0, j, 2);
+      if (tid == 128) BTRACE(0, 1, j, 2);
+      if (j >= 2) {   // the product that read this operand buffer two tiles ago must have retired
+        ok = wait_clocked(smem_u32(&sync->op_empty[buf]), ((j >> 1) - 1) & 1, abort_flag, wait_limit);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          if (lane == 0) report(p.status, 16, j, warp);
+          alive = false;
+          break;
+        }
+        tc_fence_after_sync();
+      }
+      tmem_st_32x16(op_addr + buf * 64, reinterpret_cast<uint32_t(&)[16]>(pk[0]));
+      tmem_st_32x16(op_addr + buf * 64 + 16, reinterpret_cast<uint32_t(&)[16]>(pk[16]));
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(smem_u32(&sync->e_ready[buf]));
+      if (tid == 0) BTRACE(0, 0, j, 3);
+      if (tid == 128) BTRACE(0, 1, j, 3);
+      if (tid == 0 && j + 1 == n_tiles) CTRACE(3);
     }
     if (alive && n_tiles > 0) {
       bool ok = wait_clocked(smem_u32(&sync->acc_done), 0, abort_flag, wait_limit);
@@ -407,9 +550,11 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       fence_proxy_async_smem();
       mbar_arrive(smem_u32(&sync->staged));
       if (tid == 0 && wait_clocked(smem_u32(&sync->staged), 0, abort_flag, wait_limit)) {
+        CTRACE(4);
         for (int bx = 0; bx < C::kBoxes; ++bx) tma_store_4d(&tm_dq, q_tile + bx * kBoxBytes, bx * 64, row0, h, b);
         tma_store_commit();
         tma_store_wait_all();
+        CTRACE(5);
       }
     }
   }
@@ -419,6 +564,7 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   if (warp == kMmaWarp) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
+    if (lane == 0) CTRACE(6);
   }
 }
 
@@ -696,24 +842,28 @@ int launch_tc(const BwdProblem& bp, float* lse2, float* delta, cudaStream_t stre
     return B200_SDPA_ERR_CUDA;
   auto kq = bwd_dq_tc_kernel<D, BF16>;
   auto kkv = bwd_dkv_tc_kernel<D, BF16>;
-  if (cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess ||
+  if (cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, ACfg<D>::kSmemBytes) != cudaSuccess ||
       cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess) {
     cudaGetLastError();
     return B200_SDPA_ERR_CUDA;
   }
   const int l_pad = padded_rows(p);
   {
-    const long long warps = static_cast<long long>(p.B) * p.Hq * l_pad;
+    const long long rows = static_cast<long long>(p.B) * p.Hq * l_pad;
+    auto rows_aligned = [](const void* base, const int64_t* st) {
+      return st[3] == 1 && reinterpret_cast<uintptr_t>(base) % 16 == 0 && st[0] % 8 == 0 && st[1] % 8 == 0 && st[2] % 8 == 0;
+    };
+    const bool vec = p.Dv % 8 == 0 && rows_aligned(bp.dout, bp.dos) && rows_aligned(p.out, p.os);
+    const long long warps = vec ? (rows + 3) / 4 : rows;
     const long long blocks = (warps * 32 + 255) / 256;
     if (blocks > 0x7fffffffLL) return B200_SDPA_ERR_UNSUPPORTED;
-    auto rows_aligned = [](const void* base, const int64_t* st) {
-      return st[3] == 1 && reinterpret_cast<uintptr_t>(base) % 8 == 0 && st[0] % 4 == 0 && st[1] % 4 == 0 && st[2] % 4 == 0;
-    };
-    const int vec4 = (p.Dv % 4 == 0 && rows_aligned(bp.dout, bp.dos) && rows_aligned(p.out, p.os)) ? 1 : 0;
+    const unsigned grid = static_cast<unsigned>(blocks);
     if (BF16) {
-      bwd_prep_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(bp, lse2, delta, l_pad, vec4);
+      if (vec) bwd_prep_kernel<__nv_bfloat16, true><<<grid, 256, 0, stream>>>(bp, lse2, delta, l_pad);
+      else bwd_prep_kernel<__nv_bfloat16, false><<<grid, 256, 0, stream>>>(bp, lse2, delta, l_pad);
     } else {
-      bwd_prep_kernel<__half><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(bp, lse2, delta, l_pad, vec4);
+      if (vec) bwd_prep_kernel<__half, true><<<grid, 256, 0, stream>>>(bp, lse2, delta, l_pad);
+      else bwd_prep_kernel<__half, false><<<grid, 256, 0, stream>>>(bp, lse2, delta, l_pad);
     }
     if (cudaGetLastError() != cudaSuccess) return B200_SDPA_ERR_CUDA;
     count_launch(KID_BWD_PREP);
@@ -723,7 +873,7 @@ int launch_tc(const BwdProblem& bp, float* lse2, float* delta, cudaStream_t stre
   const long long grid_kv = static_cast<long long>(n_kblk) * p.Hkv * p.B;
   if (grid_q > 0x7fffffffLL || grid_kv > 0x7fffffffLL) return B200_SDPA_ERR_UNSUPPORTED;
   const long long limit = wait_limit_cycles();
-  kq<<<static_cast<unsigned>(grid_q), kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, tdq, p, lse2, delta, l_pad,
+  kq<<<static_cast<unsigned>(grid_q), kThreads, ACfg<D>::kSmemBytes, stream>>>(tq, tk, tv, tdo, tdq, p, lse2, delta, l_pad,
                                                                         n_qblk, limit);
   if (cudaGetLastError() != cudaSuccess) return B200_SDPA_ERR_CUDA;
   count_launch(KID_BWD_DQ);
@@ -735,6 +885,15 @@ int launch_tc(const BwdProblem& bp, float* lse2, float* delta, cudaStream_t stre
 }
 
 }  // namespace
+
+#ifdef B200_TRACE
+extern "C" int b200_debug_read_cta(long long* host) {
+  return cudaMemcpyFromSymbol(host, g_cta, sizeof(long long) * 8192 * 8) != cudaSuccess;
+}
+extern "C" int b200_debug_read_btrace(long long* host) {
+  return cudaMemcpyFromSymbol(host, g_btrace, sizeof(long long) * 2 * 3 * 64 * 4) != cudaSuccess;
+}
+#endif
 
 bool bwd_tc_eligible(const BwdProblem& bp, int dtype, bool* alignment_only_failure) {
   const Problem& p = bp.f;
