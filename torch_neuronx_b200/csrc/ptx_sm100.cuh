@@ -1,5 +1,5 @@
-// Inline-PTX wrappers for the Blackwell (sm_100a) features the prefill kernel
-// uses: mbarriers with bounded waits, TMA tensor copies (plain, single-CTA
+// Inline-PTX wrappers for the Blackwell (sm_100a) features the tcgen05 kernels
+// use: mbarriers (the bounded waits built on them live in tc_common.cuh), TMA tensor copies (plain, single-CTA
 // form only), tensor memory (TMEM) allocation and access, tcgen05 MMA issue
 // and commit, and the UMMA shared-memory / instruction descriptors.
 #pragma once
@@ -43,23 +43,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait.  `abort_flag` is a CTA-wide word in shared memory: once any
-// role gives up it is set, and every other wait returns false on its next
-// poll, so the whole CTA drains instead of hanging.  Returns true when the
-// barrier phase completed.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          uint32_t max_polls) {
-  for (uint32_t i = 0; i < max_polls; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 63u) == 63u) {
-      if (*abort_flag != 0) return false;
-      __nanosleep(i > 4096u ? 256u : 20u);
-    }
-  }
-  *abort_flag = 1;
-  return false;
-}
-
 // -------------------------------------------------------------------- fences --
 
 __device__ __forceinline__ void fence_proxy_async_smem() {
@@ -70,9 +53,6 @@ __device__ __forceinline__ void tc_fence_before_sync() {
 }
 __device__ __forceinline__ void tc_fence_after_sync() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t threads) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
 // ----------------------------------------------------------------------- TMA --
