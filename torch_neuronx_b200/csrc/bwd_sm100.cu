@@ -553,7 +553,7 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         CTRACE(4);
         for (int bx = 0; bx < C::kBoxes; ++bx) tma_store_4d(&tm_dq, q_tile + bx * kBoxBytes, bx * 64, row0, h, b);
         tma_store_commit();
-        tma_store_wait_all();
+        tma_store_wait_read();
         CTRACE(5);
       }
     }
@@ -812,7 +812,7 @@ bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           tma_store_4d(&tm_dv, ring + C::kTileBytes + bx * kBoxBytes, bx * 64, j0, hk, b);
         }
         tma_store_commit();
-        tma_store_wait_all();
+        tma_store_wait_read();
       }
     }
   }

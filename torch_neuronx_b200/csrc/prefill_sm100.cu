@@ -76,8 +76,15 @@ __device__ long long g_trace[6][64][4];
   do {                                                                               \
     if (blockIdx.x == 0 && (step) < 64) g_trace[role][step][ev] = clock64();         \
   } while (0)
+// per-CTA life-cycle stamps: [start, set-up done, first S (tile 0), last P (tile 0), staged, stored, end, smid]
+__device__ long long g_fcta[8192][8];
+#define CTRACE(ev)                                                                 \
+  do {                                                                             \
+    if (blockIdx.x < 8192) g_fcta[blockIdx.x][ev] = clock64();                     \
+  } while (0)
 #else
 #define TRACE(role, step, ev)
+#define CTRACE(ev)
 #endif
 
 #ifdef B200_PHASE_TIMING
@@ -136,6 +143,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
   if (tid == 0) TRACE(0, 63, 0);
+#ifdef B200_TRACE
+  if (tid == 0) {
+    CTRACE(0);
+    unsigned smid;
+    asm("mov.u32 %0, %smid;" : "=r"(smid));
+    if (blockIdx.x < 8192) g_fcta[blockIdx.x][7] = smid;
+  }
+#endif
 
   // Work item: longest (latest) query blocks first, heads of one kv group adjacent.
   // Two layouts of the CTA's two 128-row tiles:
@@ -217,6 +232,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   tc_fence_after_sync();
   const uint32_t tmem_base = sync->tmem_base;
   if (tid == 0) TRACE(0, 63, 1);
+  if (tid == 0) CTRACE(1);
 
   if (warp == kProducerWarp) {
     // ------------------------------------------------------------ TMA producer
@@ -413,6 +429,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
         tc_fence_after_sync();
         if (r == 0) TRACE(t, j, 0);
+        if (tid == 0 && j == 0) CTRACE(2);
         if (r == 96) TRACE(4 + t, j, 0);
         PHASE_ADD(0, r == 0);                       // 0: waiting for S
         const int col0 = j * kBlockN;
@@ -520,6 +537,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
       // ------------------------------------------------------------- epilogue
       if (r == 0) TRACE(t, 62, 0);
+      if (tid == 0) CTRACE(3);
       if (alive && tg.n_tiles > 0) {
         bool ok = wait_clocked(smem_u32(&sync->o_done[t]), 0, abort_flag, wait_limit);
         ok = __all_sync(0xffffffffu, ok);
@@ -559,11 +577,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         // others at a barrier.
         fence_proxy_async_smem();
         mbar_arrive(smem_u32(&sync->o_staged[t]));
+        if (tid == 0) CTRACE(4);
         if (r == 0 && wait_clocked(smem_u32(&sync->o_staged[t]), 0, abort_flag, wait_limit)) {
           for (int bx = 0; bx < C::kBoxes; ++bx) tma_store_4d(&tm_o, q_smem[t] + bx * kBoxBytes, bx * 64, tg.row0, head_of_tile[t], b);
           tma_store_commit();
-          tma_store_wait_all();
+          tma_store_wait_read();
         }
+        if (tid == 0) CTRACE(5);
         PHASE_ADD(10, r == 0);                      // 10: epilogue (wait O, scale, stage, store)
         if (p.lse != nullptr && row_g < p.L) {
           // one rounding at the magnitude of the maximum: m*scale + ln(l)
@@ -577,6 +597,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   tc_fence_before_sync();
   __syncthreads();
   if (tid == 0) TRACE(0, 63, 3);
+  if (tid == 0) CTRACE(6);
   if (warp == kMmaWarp) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
@@ -625,6 +646,9 @@ int launch_variant(const Problem& p, cudaStream_t stream) {
 }  // namespace
 
 #ifdef B200_TRACE
+extern "C" int b200_debug_read_fcta(long long* host) {
+  return cudaMemcpyFromSymbol(host, g_fcta, sizeof(long long) * 8192 * 8) != cudaSuccess;
+}
 extern "C" int b200_debug_read_trace(long long* host) {
   return cudaMemcpyFromSymbol(host, g_trace, sizeof(long long) * 6 * 64 * 4) != cudaSuccess;
 }
