@@ -481,6 +481,17 @@ def run_ours(args, rank, local_rank, world):
                          "frac": btf / peaks["bf16_tflops"], "executed_over_counted": 1.4, "traffic": None,
                          "peak_kind": f"bf16_tflops of {peaks['source']}"},
         }
+        # ---------------- forward + backward back to back (what one attention layer costs in training) ----------------
+        def tstep():
+            step()
+            bstep()
+
+        tms = time_steps_flushed(tstep, max(5, min(args.steps, 20)), flush)
+        extra["train_step_config3"] = {
+            "workload": "forward + backward of configuration 3, one call each",
+            "value": 3.5 * flops / (tms * 1e-3) / 1e12, "unit": "TFLOP/s (3.5 x forward FLOPs)", "ms": tms,
+            "l2": "flushed before every timed call",
+        }
         del bgo, bgq, bgk, bgv
         # ---------------- fp32 parity configuration: latency only ----------------
         g = torch.Generator().manual_seed(0)

@@ -219,3 +219,35 @@ def test_native_multi_head_attn_mid(dtype, causal):
     assert res.data_ptr() == ptr and torch.equal(res, got)
     with pytest.raises(RuntimeError, match="do not support empty tensors"):
         T.native_multi_head_attn_mid(q[:0].to(dev), k[:0].to(dev), v[:0].to(dev))
+
+
+@pytest.mark.gpu
+def test_traced_training_step_runs_the_same_kernels():
+    """``torch.compile`` with the ``aot_eager`` backend: Dynamo + AOTAutograd trace forward and backward
+    through the ATen ops (meta kernels for shapes, the derivative formula for the backward graph) and the
+    compiled graph then launches the same CUDA kernels."""
+    import torch_neuronx_b200 as T
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(13)
+    q, k, v = (torch.randn(2, 4, 256, 64, generator=g).to(torch.bfloat16).to(dev).requires_grad_() for _ in range(3))
+
+    def step(q, k, v):
+        out = torch.ops.aten._scaled_dot_product_fused_attention_overrideable(q, k, v, None, 0.0, True)[0]
+        return out.float().square().mean()
+
+    eager = step(q, k, v)
+    eager.backward()
+    want = [t.grad.clone() for t in (q, k, v)]
+    for t in (q, k, v):
+        t.grad = None
+    T.reset_launch_counts()
+    compiled = torch.compile(step, backend="aot_eager", fullgraph=True)
+    loss = compiled(q, k, v)
+    loss.backward()
+    torch.cuda.synchronize()
+    counts = T.launch_counts()
+    assert counts["prefill"] == 1 and counts["bwd_dq"] == 1 and counts["bwd_dkv"] == 1
+    assert torch.equal(loss, eager)
+    for t, w in zip((q, k, v), want):
+        assert torch.equal(t.grad, w)
