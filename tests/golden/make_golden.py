@@ -2,7 +2,7 @@
 
 Run where the upstream checkout is available::
 
-    python tests/golden/make_golden.py [/path/to/torch-neuronx-checkout]
+    python tests/golden/make_golden.py /path/to/torch-neuronx-checkout
 
 The script loads the single upstream file ``torch_neuronx/_sdpa_math.py`` by
 path (it imports nothing but torch; the package itself needs a Trainium
@@ -85,7 +85,9 @@ def input_checksum(*tensors):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("TORCH_NEURONX_SRC", "")
+    if not root:
+        raise SystemExit("usage: make_golden.py /path/to/torch-neuronx-checkout (or set TORCH_NEURONX_SRC)")
     mod = load_upstream(root)
     cases = {}
 

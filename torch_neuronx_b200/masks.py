@@ -13,7 +13,7 @@ so a sliding-window or key-offset mask can never be mistaken for a causal one.  
 boolean masks are examined; an additive float mask is left alone because reading a
 "large negative" sentinel back depends on the float width (``:9-12``).
 
-One comparison costs a device-to-host read of two flags.  The verdict is cached per
+One comparison costs a device-to-host read of three flags.  The outcome is cached per
 mask tensor (identity + version counter), so a mask built once and reused across
 layers and steps is examined once.
 """
