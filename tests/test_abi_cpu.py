@@ -154,3 +154,71 @@ def test_backward_entry_rejects_bad_blocks():
     assert lib.b200_sdpa_bwd(C.byref(p), None) == _lib.ERR_SHAPE
     p.Hkv = 2
     assert lib.b200_sdpa_bwd(C.byref(p), None) == _lib.ERR_NULL  # no pointers given
+
+
+def _bwd_params(B=2, Hq=8, Hkv=2, L=300, S=300, D=128, dtype=_lib.BF16, **kw):
+    p = _lib.BwdParams()
+    p.struct_size = C.sizeof(_lib.BwdParams)
+    p.dtype, p.device = dtype, -1
+    fake = 0x7F0000000000  # never dereferenced by the planner
+    names = ("grad_out", "q", "k", "v", "out", "lse", "grad_q", "grad_k", "grad_v")
+    for i, n in enumerate(names):
+        setattr(p, n, fake + (i << 30))
+    p.B, p.Hq, p.Hkv, p.L, p.S, p.E, p.Dv = B, Hq, Hkv, L, S, D, D
+    qs = [Hq * L * D, L * D, D, 1]
+    ks = [Hkv * S * D, S * D, D, 1]
+    for n in ("grad_out_stride", "q_stride", "out_stride", "grad_q_stride"):
+        getattr(p, n)[:] = qs
+    for n in ("k_stride", "v_stride", "grad_k_stride", "grad_v_stride"):
+        getattr(p, n)[:] = ks
+    p.lse_stride[:] = [Hq * L, L, 1]
+    p.scale = 0.1
+    for k_, v_ in kw.items():
+        setattr(p, k_, v_)
+    return p
+
+
+def _bwd_plan(p):
+    plan = _lib.Plan()
+    plan.struct_size = C.sizeof(_lib.Plan)
+    return _lib.load().b200_sdpa_bwd_query_plan(C.byref(p), C.byref(plan)), plan
+
+
+def test_backward_planner():
+    rc, plan = _bwd_plan(_bwd_params())
+    assert rc == 0 and plan.path == _lib.PATH_PREFILL and plan.launches == 3 and plan.threads == 320
+    assert plan.workspace_bytes == 2 * 4 * 2 * 8 * 384            # two fp32 rows statistics, L padded to 128
+    assert plan.grid_x == 3 * 8 * 2 and plan.grid_y == 3 * 2 * 2  # query tiles x Hq x B, key tiles x Hkv x B
+    rc, plan = _bwd_plan(_bwd_params(dtype=_lib.F32, D=64))
+    assert rc == 0 and plan.path == _lib.PATH_GENERIC and plan.workspace_bytes == 0 and plan.launches == 2
+    rc, plan = _bwd_plan(_bwd_params(D=96))          # head dim the tensor-core kernels are not built for
+    assert rc == 0 and plan.path == _lib.PATH_GENERIC
+    rc, plan = _bwd_plan(_bwd_params(force_path=_lib.PATH_GENERIC))
+    assert rc == 0 and plan.path == _lib.PATH_GENERIC
+    p = _bwd_params(force_path=_lib.PATH_PREFILL)
+    p.grad_k = 0x7F0000000002                         # misaligned gradient buffer
+    assert _bwd_plan(p)[0] == _lib.ERR_ALIGNMENT
+    assert _bwd_plan(_bwd_params(force_path=_lib.PATH_PREFILL, dtype=_lib.F32))[0] == _lib.ERR_UNSUPPORTED
+    assert _bwd_plan(_bwd_params(force_path=_lib.PATH_DECODE))[0] == _lib.ERR_UNSUPPORTED
+    assert _bwd_plan(_bwd_params(D=300))[0] == _lib.ERR_UNSUPPORTED   # beyond the CUDA-core kernels too
+
+
+def test_paged_cache_planning():
+    def paged(**kw):
+        p = _params(B=4, Hq=32, Hkv=8, L=1, S=64 * 16, E=128, Dv=128)
+        p.k_stride[:] = [16 * 8 * 128, 128, 8 * 128, 1]   # (page, head, row, element) of a (pages, 16, 8, 128) pool
+        p.v_stride[:] = [16 * 8 * 128, 128, 8 * 128, 1]
+        p.block_table, p.block_table_stride, p.page_size = 0x7F0000400000, 64, 16
+        p.kv_lens = 0x7F0000500000
+        for k_, v_ in kw.items():
+            setattr(p, k_, v_)
+        return p
+
+    rc, plan = _plan(paged())
+    assert rc == 0 and plan.path == _lib.PATH_DECODE and plan.launches == 2 and plan.workspace_bytes > 0
+    assert _plan(paged(page_size=12))[0] == _lib.ERR_SHAPE          # not a power of two
+    assert _plan(paged(kv_lens=None))[0] == _lib.ERR_NULL           # lengths are required with a block table
+    assert _plan(paged(S=64 * 16 + 1))[0] == _lib.ERR_SHAPE         # more context than the table can address
+    assert _plan(paged(L=2))[0] == _lib.ERR_UNSUPPORTED             # only the decode kernel reads pages
+    assert _plan(paged(dtype=_lib.F32))[0] == _lib.ERR_UNSUPPORTED
+    assert _plan(paged(force_path=_lib.PATH_GENERIC))[0] == _lib.ERR_UNSUPPORTED
