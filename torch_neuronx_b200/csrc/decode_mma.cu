@@ -103,10 +103,12 @@ __global__ void __launch_bounds__(kThreads, 2) decode_mma_kernel(const Problem p
   constexpr int NB = D / 8;    // n-blocks of the second product
   extern __shared__ __align__(16) uint8_t smem[];
 
-  const int split = blockIdx.x;
-  const int hk = blockIdx.y % p.Hkv;
-  const int gsub = blockIdx.y / p.Hkv;
-  const int b = blockIdx.z;
+  // the split index is the slowest grid dimension: the CTAs that run last are the last chunks of the
+  // longest sequences (partial, or empty for shorter ones), which keeps the tail of the launch short
+  const int split = blockIdx.z;
+  const int hk = blockIdx.x % p.Hkv;
+  const int gsub = blockIdx.x / p.Hkv;
+  const int b = blockIdx.y;
   const int n_keys = valid_keys(p, b);
   const int s0 = split * chunk;
   if (s0 >= n_keys && split != 0) return;  // split 0 still writes an (empty) partial
@@ -332,7 +334,7 @@ int launch_one(const Problem& p, int chunk, int nsplit, float* po, float* pml, c
     return B200_SDPA_ERR_CUDA;
   }
   const int nsub = (p.group + 15) / 16;
-  dim3 grid(nsplit, p.Hkv * nsub, p.B);
+  dim3 grid(p.Hkv * nsub, p.B, nsplit);
   kern<<<grid, kThreads, G::kSmemBytes, stream>>>(p, chunk, nsplit, po, pml);
   if (cudaGetLastError() != cudaSuccess) return B200_SDPA_ERR_CUDA;
   count_launch(KID_DECODE);

@@ -86,10 +86,10 @@ __global__ void __launch_bounds__(kThreads) decode_partial_kernel(const Problem 
   __shared__ float sm_acc[NSTATE][G][D];
   __shared__ float sm_ml[NSTATE][G][2];
 
-  const int split = blockIdx.x;
-  const int hk = blockIdx.y % p.Hkv;
-  const int gsub = blockIdx.y / p.Hkv;  // sub-block of the query-head group when group > G
-  const int b = blockIdx.z;
+  const int split = blockIdx.z;          // slowest: the launch ends on the last (short or empty) chunks
+  const int hk = blockIdx.x % p.Hkv;
+  const int gsub = blockIdx.x / p.Hkv;   // sub-block of the query-head group when group > G
+  const int b = blockIdx.y;
   const int n_keys = valid_keys(p, b);
   const int s0 = split * chunk;
   if (s0 >= n_keys && !(split == 0)) return;  // split 0 still writes an empty partial
@@ -285,7 +285,7 @@ int launch_combine(const Problem& p, const DecodeGeom& gm, float* po, float* pml
 
 template <typename T, int D, int G>
 int launch_pg(const Problem& p, const DecodeGeom& gm, float* po, float* pml, cudaStream_t stream) {
-  dim3 grid(gm.nsplit, p.Hkv * gm.nsub, p.B);
+  dim3 grid(p.Hkv * gm.nsub, p.B, gm.nsplit);
   decode_partial_kernel<T, D, G><<<grid, kThreads, 0, stream>>>(p, gm.chunk, gm.nsplit, po, pml);
   if (cudaGetLastError() != cudaSuccess) return B200_SDPA_ERR_CUDA;
   count_launch(KID_DECODE);
@@ -335,12 +335,13 @@ bool decode_eligible(const Problem& p, int dtype) {
 int plan_decode(const Problem& p, int dtype, int kv_chunk, B200SdpaPlan* plan) {
   if (!decode_eligible(p, dtype)) return B200_SDPA_ERR_UNSUPPORTED;
   const DecodeGeom gm = geometry(p, kv_chunk);
+  if (gm.nsplit > 65535) return B200_SDPA_ERR_UNSUPPORTED;   // grid.z
   plan->path = B200_SDPA_PATH_DECODE;
   plan->block_m = 1;
   plan->block_n = gm.chunk;
-  plan->grid_x = gm.nsplit;
-  plan->grid_y = p.Hkv * gm.nsub;
-  plan->grid_z = p.B;
+  plan->grid_x = p.Hkv * gm.nsub;
+  plan->grid_y = p.B;
+  plan->grid_z = gm.nsplit;
   plan->threads = kThreads;
   plan->smem_bytes = 0;
   plan->kv_splits = gm.nsplit;
@@ -353,6 +354,7 @@ int launch_decode(const Problem& p, int dtype, int kv_chunk, void* workspace, ui
                   cudaStream_t stream) {
   if (!decode_eligible(p, dtype)) return B200_SDPA_ERR_UNSUPPORTED;
   const DecodeGeom gm = geometry(p, kv_chunk);
+  if (gm.nsplit > 65535) return B200_SDPA_ERR_UNSUPPORTED;   // grid.z
   if (workspace == nullptr || workspace_bytes < gm.ws_bytes) return B200_SDPA_ERR_WORKSPACE;
   float* po = reinterpret_cast<float*>(workspace);
   float* pml = po + static_cast<uint64_t>(p.B) * p.Hq * gm.nsplit * p.Dv;
