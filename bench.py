@@ -566,7 +566,26 @@ def run_ring(T, dist, dev, rank, world, peaks):
     flops = 4.0 * D * Hq * (S * (S + 1) // 2)
     tf = flops / (t.item() * 1e-3) / 1e12
     block_bytes = 2 * n_local * Hkv * D * 2
+    # ring backward of the same sequence: K/V blocks travel as in the forward, their fp32 gradient
+    # accumulators follow one step behind; one warm-up call, one timed call
+    out, lse = step()
+    go = torch.randn(q.shape, generator=g, device=dev, dtype=torch.bfloat16)
+
+    def bstep():
+        return T.ring_attention_backward(go, q, k, v, out, lse, is_causal=True, scale=scale, layout="zigzag")
+
+    bstep()
+    torch.cuda.synchronize()
+    T.check_device_status()
+    dist.barrier()
+    bms = time_steps(bstep, 1)
+    bt = torch.tensor([bms], dtype=torch.float64, device=dev)
+    dist.all_reduce(bt, op=dist.ReduceOp.MAX)
+    btf = 2.5 * flops / (bt.item() * 1e-3) / 1e12
+    del out, lse, go
     return {
+        "backward": {"value": btf, "unit": "TFLOP/s (2.5 x forward FLOPs)", "per_gpu_tflops": btf / world,
+                     "ms": bt.item(), "accumulator_bytes_per_step_per_gpu": 2 * block_bytes},
         "workload": f"long-context causal GQA prefill bf16 q[1,64,131072,128] kv[1,8,131072,128] over {world} GPUs "
                     "(configuration 5), zigzag ring, K/V rotated un-expanded over NCCL send/recv",
         "value": tf, "unit": "TFLOP/s", "per_gpu_tflops": tf / world, "ms": t.item(), "iters": iters,
