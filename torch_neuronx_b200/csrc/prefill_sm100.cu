@@ -10,7 +10,9 @@
 //   warp  9     MMA issuer: S_t = Q_t K(j)^T and O_t += P_t V(j), one thread
 // TMEM columns: [0,128) S0, [128,256) S1, [256,256+D) O0, [256+D,256+2D) O1;
 // the probabilities P_t (16-bit, two per column) overwrite the first 64 columns
-// of S_t and are fed to the second product straight from TMEM.
+// of S_t and are fed to the second product straight from TMEM.  With D = 64 there
+// are 128 columns to spare: P_t then has columns of its own and the next score
+// product does not wait for P V (Cfg::kSplitP).
 //
 // Online softmax in the exp2 domain on raw scores: p = 2^(s*c - m*c) with
 // c = scale*log2(e); the running maximum m is only raised when it grows by more
@@ -52,6 +54,10 @@ template <int D> struct Cfg {
   static constexpr int kStages = (D == 128) ? 4 : 8;         // K/V ring slots
   static constexpr int kSmemTiles = (kTilesPerCta + kStages) * kTileBytes;
   static constexpr int kSmemBytes = kSmemTiles + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  // With D = 64 the two O accumulators leave 128 tensor-memory columns free: P_t gets columns of its
+  // own ([384,448) / [448,512)) instead of overwriting S_t, so Q_t K(j+1)^T no longer has to wait for
+  // P_t(j) V(j) -- it is issued as soon as the softmax warps have copied S_t(j) into registers.
+  static constexpr bool kSplitP = (D == 64);
 };
 
 struct Sync {
@@ -60,6 +66,8 @@ struct Sync {
   uint64_t kv_empty[8];
   uint64_t s_full[2];
   uint64_t p_ready[2][2];  // [tile][half of P]
+  uint64_t s_free[2];      // (D = 64) the softmax warps hold S_t(j) in registers
+  uint64_t pv_done[2];     // (D = 64) P_t(j) V(j) has retired
   uint64_t o_done[2];
   uint64_t o_staged[2];
   uint64_t drain;
@@ -217,6 +225,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     mbar_init(smem_u32(&sync->p_ready[t][1]), kBlockM);
     mbar_init(smem_u32(&sync->o_done[t]), 1);
     mbar_init(smem_u32(&sync->o_staged[t]), kBlockM);
+    mbar_init(smem_u32(&sync->s_free[t]), kBlockM);
+    mbar_init(smem_u32(&sync->pv_done[t]), 1);
     if (t == 0) {
       mbar_init(smem_u32(&sync->drain), 1);
       sync->abort_flag = 0;
@@ -293,7 +303,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         constexpr int t = decltype(tile_const)::value;
         const uint64_t vd = kv_desc_v + static_cast<uint64_t>(stage * (C::kTileBytes >> 4) + half * 4 * (2048 >> 4));
         const uint32_t d_addr = tmem_base + static_cast<uint32_t>(256 + t * D);
-        const uint32_t a_addr = tmem_base + static_cast<uint32_t>(t * 128 + half * 32);
+        const uint32_t a_addr = tmem_base + static_cast<uint32_t>(C::kSplitP ? 384 + t * 64 + half * 32 : t * 128 + half * 32);
         const uint32_t acc0 = (accumulate || half > 0) ? 1u : 0u;
         if (elect_one()) {
 #pragma unroll
@@ -347,6 +357,23 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         auto serve = [&](auto tile_const) {
           constexpr int t = decltype(tile_const)::value;
           const int nt = t == 0 ? tg0.n_tiles : tg1.n_tiles;
+          if (C::kSplitP) {
+            // next scores first: S_t(j) only has to be out of tensor memory, not consumed
+            if (t == 0 && has_next) {
+              alive = wait_full(item_kn);
+              if (!alive) return;
+            }
+            if (j + 1 < nt) {
+              alive = wait_clocked(smem_u32(&sync->s_free[t]), j & 1, abort_flag, wait_limit);
+              if (!alive) {
+                if (lane == 0) report(p.status, 9, j, t);
+                return;
+              }
+              tc_fence_after_sync();
+              issue_qk(tile_const, stage_addr(item_kn));
+              commit(smem_u32(&sync->s_full[t]));
+            }
+          }
           if (j < nt) {
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
@@ -364,16 +391,23 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             }
             if (lane == 0) TRACE(2 + t, j, 2);
           }
-          if (t == 0 && has_next) {
-            alive = wait_full(item_kn);
-            if (!alive) return;
-            tc_fence_after_sync();
-          }
-          if (j + 1 < nt) {
-            issue_qk(tile_const, stage_addr(item_kn));
-            commit(smem_u32(&sync->s_full[t]));
-          } else if (j < nt) {
-            commit(smem_u32(&sync->o_done[t]));
+          if (C::kSplitP) {
+            if (j < nt) {
+              commit(smem_u32(&sync->pv_done[t]));
+              if (j + 1 >= nt) commit(smem_u32(&sync->o_done[t]));
+            }
+          } else {
+            if (t == 0 && has_next) {
+              alive = wait_full(item_kn);
+              if (!alive) return;
+              tc_fence_after_sync();
+            }
+            if (j + 1 < nt) {
+              issue_qk(tile_const, stage_addr(item_kn));
+              commit(smem_u32(&sync->s_full[t]));
+            } else if (j < nt) {
+              commit(smem_u32(&sync->o_done[t]));
+            }
           }
           if (lane == 0) TRACE(2 + t, j, 3);
           PHASE_ADD(18 + 2 * t, lane == 0);         // 18 / 20: issue P V + (wait K) + Q K^T
@@ -406,6 +440,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     const uint32_t s_addr = tmem_base + lane_off + static_cast<uint32_t>(t) * 128u;
     const uint32_t o_addr = tmem_base + lane_off + 256u + static_cast<uint32_t>(t) * D;
+    const uint32_t p_addr = C::kSplitP ? tmem_base + lane_off + 384u + static_cast<uint32_t>(t) * 64u : s_addr;
     const int row_g = tg.row0 + r;
     int lim = kv_limit;                      // keys [0, lim) are visible to this row
     if (p.causal) {
@@ -454,6 +489,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           mxb = max3(mxb, __uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3]));
         }
         tmem_ld_wait();
+        if (C::kSplitP) {
+          tc_fence_before_sync();
+          mbar_arrive(smem_u32(&sync->s_free[t]));
+        }
         PHASE_ADD(1, r == 0);                       // 1: S TMEM -> registers (+ first half max)
         if (need_mask) {
 #pragma unroll
@@ -474,6 +513,17 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           m_run = m_new;
         }
         if (j > 0 && __any_sync(0xffffffffu, grow)) {
+          if (C::kSplitP) {
+            // here S(j) can be ready before P V of the previous tile has retired: wait for it
+            bool pv_ok = wait_clocked(smem_u32(&sync->pv_done[t]), (j - 1) & 1, abort_flag, wait_limit);
+            pv_ok = __all_sync(0xffffffffu, pv_ok);
+            if (!pv_ok) {
+              if (lane == 0) report(p.status, 10, j, t);
+              alive = false;
+              break;
+            }
+            tc_fence_after_sync();
+          }
           // raise the reference maximum: O_t *= alpha (PV(j-1) has retired: its
           // completion is ordered before s_full(j))
 #pragma unroll
@@ -505,7 +555,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             sum2[(i >> 1) & 1] = f2_add(sum2[(i >> 1) & 1], f2_pack(p0, p1));
             pk[i >> 1] = pack2<BF16>(p0, p1);
           }
-          tmem_st_32x16(s_addr + c * 16, pk);
+          tmem_st_32x16(p_addr + c * 16, pk);
           if (c == 1) {
             // first 64 keys of P are in TMEM: let P V start on them while the rest is computed
             tmem_st_wait();
