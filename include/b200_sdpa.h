@@ -33,7 +33,7 @@
 extern "C" {
 #endif
 
-#define B200_SDPA_ABI_VERSION 2
+#define B200_SDPA_ABI_VERSION 3
 
 typedef enum b200_sdpa_status {
   B200_SDPA_OK = 0,
@@ -133,6 +133,21 @@ typedef struct B200SdpaParams {
   const int32_t* block_table;   /* (B, block_table_stride) page numbers               */
   int32_t block_table_stride;
   int32_t page_size;            /* rows per page, a power of two                      */
+
+  /* Decode with append (L == 1, f16/bf16): the key/value row of the token being decoded,
+   * (B, Hkv, D) with unit inner stride and (batch, head) element strides that are
+   * multiples of 8.  Batch b attends keys [0, kv_lens[b]] -- the new row is key
+   * kv_lens[b] -- and the kernel that reads the row also writes it into the cache
+   * (dense or paged) at that position, so no separate append pass is needed.  A
+   * sequence whose cache is full (kv_lens[b] >= S) appends nothing.  kv_lens is
+   * required; kv_lens_out, if given, receives min(kv_lens[b] + 1, S) and must not alias
+   * kv_lens.  Both NULL = plain decode.  Upstream appends to the cache with separate
+   * ops before calling the attention op.                                              */
+  const void* k_new;
+  const void* v_new;
+  int64_t k_new_stride[2];
+  int64_t v_new_stride[2];
+  int32_t* kv_lens_out;
 } B200SdpaParams;
 
 /* What the library would do (or did) for a parameter block. */

@@ -222,3 +222,26 @@ def test_paged_cache_planning():
     assert _plan(paged(L=2))[0] == _lib.ERR_UNSUPPORTED             # only the decode kernel reads pages
     assert _plan(paged(dtype=_lib.F32))[0] == _lib.ERR_UNSUPPORTED
     assert _plan(paged(force_path=_lib.PATH_GENERIC))[0] == _lib.ERR_UNSUPPORTED
+
+
+def test_append_planning():
+    def dec(**kw):
+        p = _params(B=4, Hq=32, Hkv=8, L=1, S=2048, E=128, Dv=128)
+        p.kv_lens = 0x7F0000500000
+        p.k_new, p.v_new = 0x7F0000600000, 0x7F0000700000
+        p.k_new_stride[:] = [8 * 128, 128]
+        p.v_new_stride[:] = [8 * 128, 128]
+        for k_, v_ in kw.items():
+            setattr(p, k_, v_)
+        return p
+
+    rc, plan = _plan(dec())
+    assert rc == 0 and plan.path == _lib.PATH_DECODE
+    assert _plan(dec(v_new=None))[0] == _lib.ERR_NULL                     # the two rows go together
+    assert _plan(dec(kv_lens=None))[0] == _lib.ERR_NULL                   # the position comes from kv_lens
+    assert _plan(dec(kv_lens_out=0x7F0000500000))[0] == _lib.ERR_UNSUPPORTED   # must not alias kv_lens
+    assert _plan(dec(L=2))[0] == _lib.ERR_UNSUPPORTED                     # decode only
+    assert _plan(dec(dtype=_lib.F32))[0] == _lib.ERR_UNSUPPORTED
+    p = dec()
+    p.k_new_stride[:] = [8 * 128 + 4, 128]                                # rows not 16-byte aligned
+    assert _plan(p)[0] == _lib.ERR_UNSUPPORTED

@@ -77,3 +77,62 @@ def test_paged_decode_rejects_what_it_cannot_serve():
         T.paged_decode(q, pool, pool, table.long(), lens)
     with pytest.raises(RuntimeError):   # page size that is not a power of two
         T.paged_decode(q, pool[:, :12], pool[:, :12], table, lens)
+
+
+@pytest.mark.parametrize("paged", [False, True])
+def test_decode_with_fused_append(paged):
+    """A short generation loop: every step attends to the cache plus the new token's row and the kernel
+    itself writes that row into the cache.  Outputs must match the oracle on the grown cache, and after
+    the loop the cache must hold exactly the rows that were appended."""
+    import torch_neuronx_b200 as T
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(17)
+    B, Hq, Hkv, D, S, page = 4, 16, 4, 128, 320, 16
+    lens = torch.tensor([0, 63, 200, 318], dtype=torch.int32)
+    k_full = torch.randn(B, Hkv, S, D, generator=g).to(torch.bfloat16)   # the rows the sequence will have
+    v_full = torch.randn(B, Hkv, S, D, generator=g).to(torch.bfloat16)
+    k_cache, v_cache = k_full.clone(), v_full.clone()
+    for b in range(B):                                                   # not yet appended: poison
+        k_cache[b, :, int(lens[b]):] = float("nan")
+        v_cache[b, :, int(lens[b]):] = float("nan")
+    if paged:
+        max_pages = S // page
+        table = torch.randperm(B * max_pages, generator=g).view(B, max_pages).to(torch.int32)
+        kp = torch.empty(B * max_pages, page, Hkv, D, dtype=torch.bfloat16)
+        vp = torch.empty_like(kp)
+        for b in range(B):
+            for pg in range(max_pages):
+                kp[table[b, pg]] = k_cache[b, :, pg * page:(pg + 1) * page].transpose(0, 1)
+                vp[table[b, pg]] = v_cache[b, :, pg * page:(pg + 1) * page].transpose(0, 1)
+        kc, vc, tb = kp.to(dev), vp.to(dev), table.to(dev)
+    else:
+        kc, vc = k_cache.to(dev), v_cache.to(dev)
+    cur = lens.clone().to(dev)
+    for step in range(3):
+        q = torch.randn(B, Hq, 1, D, generator=g).to(torch.bfloat16)
+        pos = cur.cpu().long().clamp(max=S - 1)
+        k_new = torch.stack([k_full[b, :, pos[b]] for b in range(B)])   # (B, Hkv, D)
+        v_new = torch.stack([v_full[b, :, pos[b]] for b in range(B)])
+        if paged:
+            out, lse, new = T.paged_decode(q.to(dev), kc, vc, tb, cur, need_lse=True, k_new=k_new.to(dev),
+                                           v_new=v_new.to(dev))
+        else:
+            out, lse, new = T.decode_append(q.to(dev), k_new.to(dev), v_new.to(dev), kc, vc, cur, need_lse=True)
+        torch.cuda.synchronize()
+        T.check_device_status()
+        want_lens = (cur.cpu() + 1).clamp(max=S)
+        assert torch.equal(new.cpu(), want_lens)
+        check_against_oracle(q, k_full, v_full, out.cpu(), lse.cpu(), kv_lens=want_lens, tag=f"append step {step}")
+        cur = new
+    final = cur.cpu()
+    assert final.tolist() == [3, 66, 203, 320]      # the last sequence filled its cache after two steps
+    if paged:
+        dense_k = torch.stack([torch.cat([kc[tb[b, pg]].transpose(0, 1) for pg in range(S // page)], dim=1)
+                               for b in range(B)]).cpu()
+    else:
+        dense_k = kc.cpu()
+    for b in range(B):
+        n = int(final[b])
+        assert torch.equal(dense_k[b, :, :n], k_full[b, :, :n])          # appended rows are in the cache
+        assert torch.isnan(dense_k[b, :, n:].float()).all()               # and nothing beyond them was touched

@@ -12,6 +12,7 @@ from . import _lib
 from .ops import (
     alloc_like_query,
     check_device_status,
+    decode_append,
     enable_sdpa_routing,
     fused_attention_overrideable,
     fused_attention_overrideable_backward,
@@ -43,7 +44,7 @@ launch_counts = _lib.launch_counts
 reset_launch_counts = _lib.reset_launch_counts
 
 __all__ = [
-    "MaskStructure", "alloc_like_query", "as_units", "check_device_status", "classify_mask", "enable_sdpa_routing",
+    "MaskStructure", "alloc_like_query", "as_units", "check_device_status", "classify_mask", "decode_append", "enable_sdpa_routing",
     "from_units", "fused_attention_overrideable", "fused_attention_overrideable_backward", "launch_counts",
     "local_units", "merge_partials", "native_multi_head_attn_mid", "paged_decode", "partition_units", "register_aten_override", "reset_launch_counts",
     "ring_attention", "ring_attention_backward", "ring_attention_backward_virtual", "ring_attention_virtual", "scaled_dot_product_attention",

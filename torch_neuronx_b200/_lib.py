@@ -19,7 +19,7 @@ import threading
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libb200_sdpa.so")
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 STATIC_SCRATCH_BYTES = 16 << 20  # B200_SDPA_STATIC_SCRATCH_BYTES
 
 # b200_sdpa_status
@@ -79,6 +79,11 @@ class Params(C.Structure):
         ("block_table", C.c_void_p),
         ("block_table_stride", C.c_int32),
         ("page_size", C.c_int32),
+        ("k_new", C.c_void_p),
+        ("v_new", C.c_void_p),
+        ("k_new_stride", C.c_int64 * 2),
+        ("v_new_stride", C.c_int64 * 2),
+        ("kv_lens_out", C.c_void_p),
     ]
 
 

@@ -53,6 +53,18 @@ int validate(const B200SdpaParams* a, Problem* p) {
   p->block_table = a->block_table;
   p->table_stride = a->block_table_stride;
   p->page_shift = 0;
+  p->k_new = a->k_new;
+  p->v_new = a->v_new;
+  p->lens_out = a->kv_lens_out;
+  for (int i = 0; i < 2; ++i) {
+    p->kns[i] = a->k_new_stride[i];
+    p->vns[i] = a->v_new_stride[i];
+  }
+  if ((a->k_new == nullptr) != (a->v_new == nullptr)) return B200_SDPA_ERR_NULL;
+  if (a->k_new != nullptr) {
+    if (a->kv_lens == nullptr) return B200_SDPA_ERR_NULL;
+    if (a->kv_lens_out != nullptr && a->kv_lens_out == a->kv_lens) return B200_SDPA_ERR_UNSUPPORTED;
+  }
   if (a->block_table != nullptr) {
     const int ps = a->page_size;
     if (ps < 1 || (ps & (ps - 1)) != 0 || a->block_table_stride < 1) return B200_SDPA_ERR_SHAPE;
@@ -69,8 +81,8 @@ int choose(const B200SdpaParams* a, const Problem& p, int* path) {
   if (want != B200_SDPA_PATH_AUTO && want != B200_SDPA_PATH_GENERIC && want != B200_SDPA_PATH_PREFILL &&
       want != B200_SDPA_PATH_DECODE)
     return B200_SDPA_ERR_UNSUPPORTED;
-  if (p.block_table != nullptr) {
-    // a paged cache is only understood by the split-KV decode kernel
+  if (p.block_table != nullptr || p.k_new != nullptr) {
+    // a paged cache and the append of a new row are only understood by the split-KV decode kernel
     if ((want != B200_SDPA_PATH_AUTO && want != B200_SDPA_PATH_DECODE) || !decode_eligible(p, a->dtype))
       return B200_SDPA_ERR_UNSUPPORTED;
     *path = B200_SDPA_PATH_DECODE;
@@ -167,6 +179,9 @@ int validate_bwd(const B200SdpaBwdParams* a, BwdProblem& bp) {
   p.block_table = nullptr;
   p.table_stride = 0;
   p.page_shift = 0;
+  p.k_new = nullptr;
+  p.v_new = nullptr;
+  p.lens_out = nullptr;
   if (a->force_path != B200_SDPA_PATH_AUTO && a->force_path != B200_SDPA_PATH_GENERIC &&
       a->force_path != B200_SDPA_PATH_PREFILL)
     return B200_SDPA_ERR_UNSUPPORTED;
@@ -248,7 +263,8 @@ int b200_sdpa_fwd(const B200SdpaParams* params, void* stream) {
     rc = launch_decode(p, params->dtype, params->kv_chunk, params->workspace, params->workspace_bytes, st);
     // Without scratch an automatic choice falls through to a kernel that needs none
     // (there is none for a paged cache).
-    if (rc != B200_SDPA_ERR_WORKSPACE || params->force_path == B200_SDPA_PATH_DECODE || p.block_table != nullptr)
+    if (rc != B200_SDPA_ERR_WORKSPACE || params->force_path == B200_SDPA_PATH_DECODE || p.block_table != nullptr ||
+        p.k_new != nullptr)
       return rc;
     bool unused = false;
     path = prefill_eligible(p, params->dtype, &unused) ? B200_SDPA_PATH_PREFILL : B200_SDPA_PATH_GENERIC;

@@ -37,6 +37,14 @@ struct Problem {
   const int* block_table;
   int table_stride;
   int page_shift;
+  // Decode with append: the key/value row of the token being decoded arrives separately
+  // ((B, Hkv, D), unit inner stride); it is attended to as key kv_lens[b] and written into the
+  // cache at that position by the CTA that reads it.  lens_out (if set, not aliasing kv_lens)
+  // receives the new lengths.
+  const void* k_new;
+  const void* v_new;
+  int64_t kns[2], vns[2];
+  int* lens_out;
 };
 
 // Backward: the forward's description (out and lse are inputs here) plus the upstream
@@ -117,6 +125,7 @@ __device__ __forceinline__ int valid_keys(const Problem& p, int b) {
   if (p.kv_lens != nullptr) {
     int len = p.kv_lens[b];
     len = len < 0 ? 0 : len;
+    if (p.k_new != nullptr) ++len;   // the appended row counts
     n = len < n ? len : n;
   }
   return n;

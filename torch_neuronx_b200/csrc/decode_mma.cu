@@ -94,7 +94,7 @@ template <bool BF16> __device__ __forceinline__ uint32_t pack16(float lo, float 
   return r;
 }
 
-template <int D, bool BF16, bool PAGED>
+template <int D, bool BF16, bool PAGED, bool APPEND>
 __global__ void __launch_bounds__(kThreads, 2) decode_mma_kernel(const Problem p, const int chunk, const int nsplit,
                                                                  float* __restrict__ part_o,
                                                                  float* __restrict__ part_ml) {
@@ -150,6 +150,18 @@ __global__ void __launch_bounds__(kThreads, 2) decode_mma_kernel(const Problem p
   const int64_t k_row = p.ks[2] * 2, v_row = p.vs[2] * 2;
   const int* table = PAGED ? p.block_table + static_cast<int64_t>(b) * p.table_stride : nullptr;
   const int page_mask = (1 << p.page_shift) - 1;
+  // append: the row at position `pos` (the sequence's old length) comes from k_new / v_new and is
+  // written into the cache by the thread that copies it (a full cache appends nothing)
+  int pos = -1;
+  const char* knew = nullptr;
+  const char* vnew = nullptr;
+  if (APPEND) {
+    int len = p.kv_lens[b];
+    len = len < 0 ? 0 : len;
+    pos = len < p.S ? len : -1;
+    knew = reinterpret_cast<const char*>(p.k_new) + (b * p.kns[0] + hk * p.kns[1]) * 2;
+    vnew = reinterpret_cast<const char*>(p.v_new) + (b * p.vns[0] + hk * p.vns[1]) * 2;
+  }
   const uint32_t smem_base = smem_addr(smem);
   auto load_block = [&](int blk) {
     const uint32_t stage = smem_base + (blk % kStages) * G::kStageBytes;
@@ -170,8 +182,18 @@ __global__ void __launch_bounds__(kThreads, 2) decode_mma_kernel(const Problem p
         k_off = srow * k_row;
         v_off = srow * v_row;
       }
-      cp_async_16(stage + row * G::kRowBytes + ch * 16, kbase + k_off + ch * 16, ok);
-      cp_async_16(stage + G::kTileBytes + row * G::kRowBytes + ch * 16, vbase + v_off + ch * 16, ok);
+      const char* ksrc = kbase + k_off + ch * 16;
+      const char* vsrc = vbase + v_off + ch * 16;
+      if (APPEND && ok && srow == pos) {
+        const uint4 kq = *reinterpret_cast<const uint4*>(knew + ch * 16);
+        const uint4 vq = *reinterpret_cast<const uint4*>(vnew + ch * 16);
+        *reinterpret_cast<uint4*>(const_cast<char*>(ksrc)) = kq;
+        *reinterpret_cast<uint4*>(const_cast<char*>(vsrc)) = vq;
+        ksrc = knew + ch * 16;
+        vsrc = vnew + ch * 16;
+      }
+      cp_async_16(stage + row * G::kRowBytes + ch * 16, ksrc, ok);
+      cp_async_16(stage + G::kTileBytes + row * G::kRowBytes + ch * 16, vsrc, ok);
     }
   };
 
@@ -324,11 +346,11 @@ __global__ void __launch_bounds__(kThreads, 2) decode_mma_kernel(const Problem p
   }
 }
 
-template <int D, bool BF16, bool PAGED>
+template <int D, bool BF16, bool PAGED, bool APPEND>
 int launch_one(const Problem& p, int chunk, int nsplit, float* po, float* pml, cudaStream_t stream) {
   using G = Geo<D>;
   static_assert(kWarps * 16 * D * 4 + kWarps * 16 * 2 * 4 <= G::kSmemBytes, "merge buffer must fit in the ring");
-  auto kern = decode_mma_kernel<D, BF16, PAGED>;
+  auto kern = decode_mma_kernel<D, BF16, PAGED, APPEND>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G::kSmemBytes) != cudaSuccess) {
     cudaGetLastError();
     return B200_SDPA_ERR_CUDA;
@@ -353,20 +375,28 @@ bool decode_mma_eligible(const Problem& p, int dtype) {
 int launch_decode_partial_mma(const Problem& p, int dtype, int chunk, int nsplit, float* po, float* pml,
                               cudaStream_t stream) {
   const bool bf16 = dtype == B200_SDPA_BF16;
-  if (p.block_table != nullptr) {
-    if (p.E == 128) {
-      return bf16 ? launch_one<128, true, true>(p, chunk, nsplit, po, pml, stream)
-                  : launch_one<128, false, true>(p, chunk, nsplit, po, pml, stream);
-    }
-    return bf16 ? launch_one<64, true, true>(p, chunk, nsplit, po, pml, stream)
-                : launch_one<64, false, true>(p, chunk, nsplit, po, pml, stream);
-  }
-  if (p.E == 128) {
-    return bf16 ? launch_one<128, true, false>(p, chunk, nsplit, po, pml, stream)
-                : launch_one<128, false, false>(p, chunk, nsplit, po, pml, stream);
-  }
-  return bf16 ? launch_one<64, true, false>(p, chunk, nsplit, po, pml, stream)
-              : launch_one<64, false, false>(p, chunk, nsplit, po, pml, stream);
+  const bool d128 = p.E == 128, paged = p.block_table != nullptr, append = p.k_new != nullptr;
+#define B200_DECODE_CASE(DD, BB, PP, AA)                                                               \
+  if (d128 == (DD == 128) && bf16 == BB && paged == PP && append == AA)                                \
+    return launch_one<DD, BB, PP, AA>(p, chunk, nsplit, po, pml, stream);
+  B200_DECODE_CASE(128, true, false, false)
+  B200_DECODE_CASE(128, false, false, false)
+  B200_DECODE_CASE(64, true, false, false)
+  B200_DECODE_CASE(64, false, false, false)
+  B200_DECODE_CASE(128, true, true, false)
+  B200_DECODE_CASE(128, false, true, false)
+  B200_DECODE_CASE(64, true, true, false)
+  B200_DECODE_CASE(64, false, true, false)
+  B200_DECODE_CASE(128, true, false, true)
+  B200_DECODE_CASE(128, false, false, true)
+  B200_DECODE_CASE(64, true, false, true)
+  B200_DECODE_CASE(64, false, false, true)
+  B200_DECODE_CASE(128, true, true, true)
+  B200_DECODE_CASE(128, false, true, true)
+  B200_DECODE_CASE(64, true, true, true)
+  B200_DECODE_CASE(64, false, true, true)
+#undef B200_DECODE_CASE
+  return B200_SDPA_ERR_UNSUPPORTED;
 }
 
 }  // namespace b200

@@ -225,6 +225,7 @@ __global__ void __launch_bounds__(D) decode_combine_kernel(const Problem p, cons
   const int b = blockIdx.x / p.Hq;
   const int d = threadIdx.x;
   const int n_keys = valid_keys(p, b);
+  if (p.lens_out != nullptr && h == 0 && d == 0) p.lens_out[b] = n_keys;   // lengths after the append
   int used = (n_keys + chunk - 1) / chunk;
   used = used < 1 ? 1 : (used > nsplit ? nsplit : used);
   const int64_t slot0 = (static_cast<int64_t>(b) * p.Hq + h) * nsplit;
@@ -299,7 +300,7 @@ bool use_mma_partial(const Problem& p, int dtype) {
     const char* e = getenv("B200_SDPA_DECODE_SIMT");
     return e != nullptr && e[0] == '1';
   }();
-  if (p.block_table != nullptr) return true;   // a paged cache is only read by the tensor-core kernel
+  if (p.block_table != nullptr || p.k_new != nullptr) return true;   // only the tensor-core kernel serves these
   return !forced_simt && decode_mma_eligible(p, dtype);
 }
 
@@ -317,7 +318,12 @@ int launch_g(const Problem& p, const DecodeGeom& gm, float* po, float* pml, cuda
 
 bool decode_eligible(const Problem& p, int dtype) {
   if (p.L != 1 || p.bias != nullptr || p.E != p.Dv) return false;
-  if (p.block_table != nullptr && !decode_mma_eligible(p, dtype)) return false;   // paged: 16-bit caches only
+  // a paged cache or an appended row: 16-bit caches only (the tensor-core partial kernel)
+  if ((p.block_table != nullptr || p.k_new != nullptr) && !decode_mma_eligible(p, dtype)) return false;
+  if (p.k_new != nullptr) {
+    if (p.kns[0] % 8 || p.kns[1] % 8 || p.vns[0] % 8 || p.vns[1] % 8) return false;
+    if (reinterpret_cast<uintptr_t>(p.k_new) % 16 || reinterpret_cast<uintptr_t>(p.v_new) % 16) return false;
+  }
   if (p.E != 64 && p.E != 128) return false;
   if (p.B > 65535 || static_cast<int64_t>(p.Hkv) * ((p.group + 7) / 8) > 65535) return false;
   // is_causal with one query row only limits keys to j <= causal_shift; the host

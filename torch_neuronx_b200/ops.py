@@ -277,8 +277,13 @@ def paged_decode(
     lse: Optional[torch.Tensor] = None,
     need_lse: bool = False,
     kv_chunk: int = 0,
+    k_new: Optional[torch.Tensor] = None,
+    v_new: Optional[torch.Tensor] = None,
 ):
-    """One decode step against a paged key/value cache; returns ``(out, lse)``.
+    """One decode step against a paged key/value cache; returns ``(out, lse)`` -- or, with
+    ``k_new`` / ``v_new`` (``(B, Hkv, D)``, the rows of the token being decoded),
+    ``(out, lse, new_lens)``: the new row is attended to as key ``kv_lens[b]`` and written
+    into its page by the kernel that reads it (see :func:`decode_append`).
 
     ``query`` is ``(B, Hq, 1, D)``; ``k_pages`` / ``v_pages`` are page pools,
     ``(pages, page_size, Hkv, D)`` for ``layout="NHD"`` or ``(pages, Hkv, page_size, D)``
@@ -338,6 +343,7 @@ def paged_decode(
     p.block_table = block_table.data_ptr()
     p.block_table_stride = block_table.shape[1]
     p.page_size = page_size
+    new_lens = _attach_new_rows(p, k_new, v_new, query, Hkv, kv_lens)
     p.kv_chunk = int(kv_chunk)
     p.status = _status_word(dev).data_ptr()
     plan = _lib.Plan()
@@ -351,7 +357,94 @@ def paged_decode(
     rc = lib.b200_sdpa_decode(C.byref(p), C.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
     if rc != _lib.OK:
         raise RuntimeError(f"b200_sdpa_decode: {_lib.strerror(rc)}")
-    return out, lse
+    return (out, lse) if new_lens is None else (out, lse, new_lens)
+
+
+def _attach_new_rows(p, k_new, v_new, query, Hkv, kv_lens):
+    """Fill the append fields of a parameter block; returns the tensor that will receive the new lengths."""
+    if k_new is None and v_new is None:
+        return None
+    if k_new is None or v_new is None:
+        raise RuntimeError("decode append: k_new and v_new go together")
+    B, _, _, E = query.shape
+    for name, t in (("k_new", k_new), ("v_new", v_new)):
+        if tuple(t.shape) != (B, Hkv, E) or t.dtype != query.dtype or t.device != query.device or t.stride(2) != 1:
+            raise RuntimeError(f"decode append: {name} must be (B, Hkv, D) in the query dtype with unit inner stride")
+    p.k_new, p.v_new = k_new.data_ptr(), v_new.data_ptr()
+    p.k_new_stride[:] = k_new.stride()[:2]
+    p.v_new_stride[:] = v_new.stride()[:2]
+    new_lens = torch.empty_like(kv_lens)
+    p.kv_lens_out = new_lens.data_ptr()
+    return new_lens
+
+
+def decode_append(
+    query: torch.Tensor,
+    k_new: torch.Tensor,
+    v_new: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    kv_lens: torch.Tensor,
+    *,
+    scale: Optional[float] = None,
+    need_lse: bool = False,
+    kv_chunk: int = 0,
+):
+    """One decode step of a generation loop against a dense ``(B, Hkv, S, D)`` cache, with the
+    cache append fused into the attention kernel: batch ``b`` attends keys ``[0, kv_lens[b]]``
+    where key ``kv_lens[b]`` is the new row ``k_new[b]`` / ``v_new[b]`` (``(B, Hkv, D)``), and
+    the CTA that reads that row also writes it into ``k_cache`` / ``v_cache`` at that position.
+    Returns ``(out, lse, new_lens)`` with ``new_lens = min(kv_lens + 1, S)`` in a fresh tensor.
+    A sequence whose cache is full appends nothing.  (Upstream's loop appends with separate ops
+    before the attention op: ``tests/blocks/block_def/llama.py:110-119`` is the caller shape.)"""
+    lib = _lib.load()
+    if query.dim() != 4 or query.shape[2] != 1 or k_cache.dim() != 4 or v_cache.shape != k_cache.shape:
+        raise RuntimeError("decode_append: query must be (B, Hq, 1, D) and the caches (B, Hkv, S, D)")
+    if query.dtype not in (torch.float16, torch.bfloat16) or k_cache.dtype != query.dtype or v_cache.dtype != query.dtype:
+        raise RuntimeError("decode_append: query and caches must share a float16 or bfloat16 dtype")
+    dev = _device_index(query)
+    B, Hq, _, E = query.shape
+    Hkv, S = k_cache.shape[1], k_cache.shape[2]
+    if Hkv == 0 or Hq % Hkv != 0:
+        raise RuntimeError("SDPA: Number of heads in key and value must divide the number of heads in query")
+    if kv_lens.dtype != torch.int32 or kv_lens.shape != (B,) or kv_lens.device != query.device:
+        raise RuntimeError("kv_lens must be an int32 CUDA tensor of shape (B,) on the query's device")
+    kv_lens = kv_lens.contiguous()
+    if scale is None:
+        scale = 1.0 / math.sqrt(E)
+    out = torch.empty_like(query)
+    lse = torch.empty((B, Hq, 1), dtype=torch.float32, device=query.device) if need_lse else None
+    p = _lib.Params()
+    p.struct_size = C.sizeof(_lib.Params)
+    p.dtype = _DTYPE_CODE[query.dtype]
+    p.device = dev
+    p.force_path = _lib.PATH_DECODE
+    p.q, p.k, p.v, p.out = query.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr()
+    p.lse = lse.data_ptr() if lse is not None else None
+    p.q_stride[:] = query.stride()
+    p.k_stride[:] = k_cache.stride()
+    p.v_stride[:] = v_cache.stride()
+    p.out_stride[:] = out.stride()
+    if lse is not None:
+        p.lse_stride[:] = lse.stride()
+    p.B, p.Hq, p.Hkv, p.L, p.S, p.E, p.Dv = B, Hq, Hkv, 1, S, E, E
+    p.scale = float(scale)
+    p.kv_lens = kv_lens.data_ptr()
+    new_lens = _attach_new_rows(p, k_new, v_new, query, Hkv, kv_lens)
+    p.kv_chunk = int(kv_chunk)
+    p.status = _status_word(dev).data_ptr()
+    plan = _lib.Plan()
+    plan.struct_size = C.sizeof(_lib.Plan)
+    rc = lib.b200_sdpa_query_plan(C.byref(p), C.byref(plan))
+    if rc != _lib.OK:
+        raise RuntimeError(f"b200_sdpa_query_plan: {_lib.strerror(rc)}")
+    ws = _workspace(dev, int(plan.workspace_bytes))
+    p.workspace = ws.data_ptr()
+    p.workspace_bytes = ws.numel()
+    rc = lib.b200_sdpa_decode(C.byref(p), C.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+    if rc != _lib.OK:
+        raise RuntimeError(f"b200_sdpa_decode: {_lib.strerror(rc)}")
+    return out, lse, new_lens
 
 
 def sdpa_backward(
