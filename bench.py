@@ -434,7 +434,18 @@ def run_ours(args, rank, local_rank, world):
                          "frac": gbs / peaks["hbm_gbs"], "traffic": 1.018 * io_bytes, "bytes_per_launch": io_bytes,
                          "peak_kind": f"hbm_gbs of {peaks['source']}"},
         }
-        del dk, dv
+        # the same call replayed from a CUDA graph (how a serving loop issues its decode steps)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            dstep()
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            dstep()
+        gms = time_steps_flushed(graph.replay, max(5, min(args.steps, 20)), flush)
+        extra["decode"]["cuda_graph_replay"] = {"ms": gms, "value": io_bytes / (gms * 1e-3) / 1e9, "unit": "GB/s"}
+        del graph, dk, dv
         # ---------------- GPT-2-small-shaped prefill: configuration 2 ----------------
         gq, gk, gv = c2_inputs(dev)
         gout = torch.empty_like(gq)
