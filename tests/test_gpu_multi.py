@@ -117,6 +117,25 @@ def _train_worker(rank, world, port, out_dir):
             for got, want in zip((qd.grad, kd.grad, vd.grad), ref_g[:3]):
                 errs.append((got.to_local().cpu() - T.shard_sequence(want, rank, world, layout)).abs().max().item())
             res[layout] = errs
+        # head- and batch-sharded DTensors need no exchange: DTensor's ordinary dispatch runs the op on the
+        # local shards with the placements registered in torch_neuronx_b200.dtensor
+        qb = torch.randn(2, 8, 128, 64, generator=g)
+        kb = torch.randn(2, 2, 128, 64, generator=g)
+        vb = torch.randn(2, 2, 128, 64, generator=g)
+        gob = torch.randn(2, 8, 128, 64, generator=g)
+        rb_o, rb_l = O.sdpa_forward(qb, kb, vb, is_causal=True)
+        rb_g = O.sdpa_backward(gob, qb, kb, vb, rb_o, rb_l, is_causal=True)
+        for dim in (0, 1):
+            parts = [t.chunk(world, dim=dim)[rank].contiguous().to(dev) for t in (qb, kb, vb, gob)]
+            qd, kd, vd = (DTensor.from_local(t, mesh, [Shard(dim)]).requires_grad_() for t in parts[:3])
+            outd = torch.ops.aten._scaled_dot_product_fused_attention_overrideable(qd, kd, vd, None, 0.0, True)[0]
+            outd.backward(DTensor.from_local(parts[3], mesh, [Shard(dim)]))
+            torch.cuda.synchronize()
+            errs = [(outd.to_local().detach().cpu() - rb_o.chunk(world, dim=dim)[rank]).abs().max().item()]
+            for got, want in zip((qd.grad, kd.grad, vd.grad), rb_g[:3]):
+                errs.append((got.to_local().cpu() - want.chunk(world, dim=dim)[rank]).abs().max().item())
+            assert outd.placements == (Shard(dim),)
+            res[f"shard{dim}"] = errs
         torch.save(res, os.path.join(out_dir, f"r{rank}.pt"))
     finally:
         dist.destroy_process_group()
