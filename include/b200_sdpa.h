@@ -33,7 +33,7 @@
 extern "C" {
 #endif
 
-#define B200_SDPA_ABI_VERSION 3
+#define B200_SDPA_ABI_VERSION 4
 
 typedef enum b200_sdpa_status {
   B200_SDPA_OK = 0,
@@ -148,6 +148,18 @@ typedef struct B200SdpaParams {
   int64_t k_new_stride[2];
   int64_t v_new_stride[2];
   int32_t* kv_lens_out;
+
+  /* Rotary position embedding fused into the append step (needs k_new): q and k_new are
+   * rotated by the angles of position kv_lens[b] -- in fp32, rounded to the storage dtype
+   * once -- before they are used, and k_new is written to the cache rotated.  rope_cos /
+   * rope_sin are fp32 (positions, >= E/2 columns) with rope_stride floats between
+   * positions; rope_interleaved = 0 pairs element i with i + E/2 (the "rotate half"
+   * convention), 1 pairs 2i with 2i + 1.  NULL = no rotation.  Upstream applies the
+   * embedding with separate ops before the attention op.                              */
+  const float* rope_cos;
+  const float* rope_sin;
+  int32_t rope_stride;
+  int32_t rope_interleaved;
 } B200SdpaParams;
 
 /* What the library would do (or did) for a parameter block. */

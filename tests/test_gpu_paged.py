@@ -136,3 +136,53 @@ def test_decode_with_fused_append(paged):
         n = int(final[b])
         assert torch.equal(dense_k[b, :, :n], k_full[b, :, :n])          # appended rows are in the cache
         assert torch.isnan(dense_k[b, :, n:].float()).all()               # and nothing beyond them was touched
+
+
+def _rope(x, cos, sin, interleaved):
+    """fp32 rotary embedding of the last dimension; cos/sin are (..., D/2) broadcastable."""
+    x = x.float()
+    if interleaved:
+        a, b = x[..., 0::2], x[..., 1::2]
+        out = torch.stack([a * cos - b * sin, b * cos + a * sin], dim=-1).flatten(-2)
+    else:
+        h = x.shape[-1] // 2
+        a, b = x[..., :h], x[..., h:]
+        out = torch.cat([a * cos - b * sin, b * cos + a * sin], dim=-1)
+    return out
+
+
+@pytest.mark.parametrize("interleaved", [False, True])
+@pytest.mark.parametrize("dtype,D", [(torch.bfloat16, 128), (torch.float16, 64)])
+def test_decode_append_with_fused_rotary_embedding(dtype, D, interleaved):
+    import torch_neuronx_b200 as T
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(31)
+    B, Hq, Hkv, S = 3, 8, 2, 200
+    lens = torch.tensor([0, 77, 150], dtype=torch.int32)
+    inv_freq = 1.0 / (10000.0 ** (torch.arange(0, D, 2).float() / D))
+    ang = torch.arange(S).float()[:, None] * inv_freq[None, :]
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()                 # (S, D/2) fp32
+    q = torch.randn(B, Hq, 1, D, generator=g).to(dtype)
+    k_cache = torch.randn(B, Hkv, S, D, generator=g).to(dtype)                 # already rotated rows, as a cache holds
+    v_cache = torch.randn(B, Hkv, S, D, generator=g).to(dtype)
+    k_new = torch.randn(B, Hkv, D, generator=g).to(dtype)
+    v_new = torch.randn(B, Hkv, D, generator=g).to(dtype)
+    kc, vc = k_cache.to(dev), v_cache.to(dev)
+    out, lse, new = T.decode_append(q.to(dev), k_new.to(dev), v_new.to(dev), kc, vc, lens.to(dev), need_lse=True,
+                                    rope_cos=cos.to(dev), rope_sin=sin.to(dev), rope_interleaved=interleaved)
+    torch.cuda.synchronize()
+    T.check_device_status()
+    # reference: rotate in fp32, round once, append, attend
+    pos = lens.long()
+    q_rot = _rope(q, cos[pos][:, None, None, :], sin[pos][:, None, None, :], interleaved).to(dtype)
+    k_rot = _rope(k_new, cos[pos][:, None, :], sin[pos][:, None, :], interleaved).to(dtype)
+    k_ref, v_ref = k_cache.clone(), v_cache.clone()
+    for b in range(B):
+        k_ref[b, :, pos[b]] = k_rot[b]
+        v_ref[b, :, pos[b]] = v_new[b]
+    check_against_oracle(q_rot, k_ref, v_ref, out.cpu(), lse.cpu(), kv_lens=lens + 1, tag=f"rope interleaved={interleaved}")
+    assert new.cpu().tolist() == (lens + 1).tolist()
+    for b in range(B):
+        assert torch.equal(kc[b, :, pos[b]].cpu(), k_rot[b])                    # the cache holds the rotated key
+        assert torch.equal(vc[b, :, pos[b]].cpu(), v_new[b])

@@ -19,7 +19,7 @@ import threading
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libb200_sdpa.so")
 
-ABI_VERSION = 3
+ABI_VERSION = 4
 STATIC_SCRATCH_BYTES = 16 << 20  # B200_SDPA_STATIC_SCRATCH_BYTES
 
 # b200_sdpa_status
@@ -84,6 +84,10 @@ class Params(C.Structure):
         ("k_new_stride", C.c_int64 * 2),
         ("v_new_stride", C.c_int64 * 2),
         ("kv_lens_out", C.c_void_p),
+        ("rope_cos", C.c_void_p),
+        ("rope_sin", C.c_void_p),
+        ("rope_stride", C.c_int32),
+        ("rope_interleaved", C.c_int32),
     ]
 
 

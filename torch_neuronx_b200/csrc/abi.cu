@@ -60,6 +60,12 @@ int validate(const B200SdpaParams* a, Problem* p) {
     p->kns[i] = a->k_new_stride[i];
     p->vns[i] = a->v_new_stride[i];
   }
+  p->rope_cos = a->rope_cos;
+  p->rope_sin = a->rope_sin;
+  p->rope_stride = a->rope_stride;
+  p->rope_interleaved = a->rope_interleaved != 0;
+  if ((a->rope_cos == nullptr) != (a->rope_sin == nullptr)) return B200_SDPA_ERR_NULL;
+  if (a->rope_cos != nullptr && (a->k_new == nullptr || a->rope_stride < a->E / 2)) return B200_SDPA_ERR_UNSUPPORTED;
   if ((a->k_new == nullptr) != (a->v_new == nullptr)) return B200_SDPA_ERR_NULL;
   if (a->k_new != nullptr) {
     if (a->kv_lens == nullptr) return B200_SDPA_ERR_NULL;
@@ -182,6 +188,8 @@ int validate_bwd(const B200SdpaBwdParams* a, BwdProblem& bp) {
   p.k_new = nullptr;
   p.v_new = nullptr;
   p.lens_out = nullptr;
+  p.rope_cos = nullptr;
+  p.rope_sin = nullptr;
   if (a->force_path != B200_SDPA_PATH_AUTO && a->force_path != B200_SDPA_PATH_GENERIC &&
       a->force_path != B200_SDPA_PATH_PREFILL)
     return B200_SDPA_ERR_UNSUPPORTED;

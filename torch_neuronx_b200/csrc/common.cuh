@@ -45,6 +45,12 @@ struct Problem {
   const void* v_new;
   int64_t kns[2], vns[2];
   int* lens_out;
+  // Rotary position embedding fused into the append step: q and k_new are rotated by the angles of
+  // position kv_lens[b] before use (and k_new is stored rotated); cos/sin are fp32 (positions, D/2).
+  const float* rope_cos;
+  const float* rope_sin;
+  int rope_stride;       // floats between positions
+  int rope_interleaved;  // 0: pairs (i, i + D/2); 1: pairs (2i, 2i + 1)
 };
 
 // Backward: the forward's description (out and lse are inputs here) plus the upstream

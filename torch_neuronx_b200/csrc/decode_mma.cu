@@ -94,7 +94,28 @@ template <bool BF16> __device__ __forceinline__ uint32_t pack16(float lo, float 
   return r;
 }
 
-template <int D, bool BF16, bool PAGED, bool APPEND>
+template <bool BF16> __device__ __forceinline__ float half_to_f32(uint16_t x) {
+  if (BF16) return __uint_as_float(static_cast<uint32_t>(x) << 16);
+  return __half2float(__ushort_as_half(x));
+}
+template <bool BF16> __device__ __forceinline__ uint16_t f32_to_half(float x) {
+  if (BF16) return __bfloat16_as_ushort(__float2bfloat16_rn(x));
+  return __half_as_ushort(__float2half_rn(x));
+}
+// Rotary embedding of element `col` of a row: the partner element and the angle index.
+template <int D> __device__ __forceinline__ void rope_partner(int col, bool interleaved, int* partner, int* angle, float* sign) {
+  if (interleaved) {
+    *partner = col ^ 1;
+    *angle = col >> 1;
+    *sign = (col & 1) ? 1.f : -1.f;
+  } else {
+    *partner = col < D / 2 ? col + D / 2 : col - D / 2;
+    *angle = col < D / 2 ? col : col - D / 2;
+    *sign = col < D / 2 ? -1.f : 1.f;
+  }
+}
+
+template <int D, bool BF16, bool PAGED, bool APPEND, bool ROPE>
 __global__ void __launch_bounds__(kThreads, 2) decode_mma_kernel(const Problem p, const int chunk, const int nsplit,
                                                                  float* __restrict__ part_o,
                                                                  float* __restrict__ part_ml) {
@@ -135,7 +156,26 @@ __global__ void __launch_bounds__(kThreads, 2) decode_mma_kernel(const Problem p
         uint32_t v = 0;
         if (row < n_heads) {
           const int64_t o = base + (h0 + row) * p.qs[1] + col * p.qs[3];
-          v = static_cast<uint32_t>(q16[o]) | (static_cast<uint32_t>(q16[o + p.qs[3]]) << 16);
+          if (ROPE) {
+            // out[c] = x[c] cos + sign x[partner] sin at this step's position, in fp32, rounded once
+            int len = p.kv_lens[b];
+            len = len < 0 ? 0 : len;
+            const float* cs = p.rope_cos + static_cast<int64_t>(len) * p.rope_stride;
+            const float* sn = p.rope_sin + static_cast<int64_t>(len) * p.rope_stride;
+            uint16_t outv[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              int partner, angle;
+              float sign;
+              rope_partner<D>(col + e, p.rope_interleaved != 0, &partner, &angle, &sign);
+              const float x = half_to_f32<BF16>(q16[o + e * p.qs[3]]);
+              const float y = half_to_f32<BF16>(q16[o + (partner - col) * p.qs[3]]);
+              outv[e] = f32_to_half<BF16>(fmaf(sign * y, sn[angle], x * cs[angle]));
+            }
+            v = static_cast<uint32_t>(outv[0]) | (static_cast<uint32_t>(outv[1]) << 16);
+          } else {
+            v = static_cast<uint32_t>(q16[o]) | (static_cast<uint32_t>(q16[o + p.qs[3]]) << 16);
+          }
         }
         qf[ks][r] = v;
       }
@@ -184,15 +224,41 @@ __global__ void __launch_bounds__(kThreads, 2) decode_mma_kernel(const Problem p
       }
       const char* ksrc = kbase + k_off + ch * 16;
       const char* vsrc = vbase + v_off + ch * 16;
+      bool k_by_copy = true;
       if (APPEND && ok && srow == pos) {
-        const uint4 kq = *reinterpret_cast<const uint4*>(knew + ch * 16);
+        uint4 kq = *reinterpret_cast<const uint4*>(knew + ch * 16);
         const uint4 vq = *reinterpret_cast<const uint4*>(vnew + ch * 16);
+        if (ROPE) {
+          // rotate the eight elements of this chunk (their partners sit in this chunk or in one other)
+          const float* cs = p.rope_cos + static_cast<int64_t>(pos) * p.rope_stride;
+          const float* sn = p.rope_sin + static_cast<int64_t>(pos) * p.rope_stride;
+          const uint16_t* row16 = reinterpret_cast<const uint16_t*>(knew);
+          uint16_t* kv16 = reinterpret_cast<uint16_t*>(&kq);
+          uint16_t rot[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            int partner, angle;
+            float sign;
+            rope_partner<D>(ch * 8 + e, p.rope_interleaved != 0, &partner, &angle, &sign);
+            const float x = half_to_f32<BF16>(kv16[e]);
+            const float y = half_to_f32<BF16>(row16[partner]);
+            rot[e] = f32_to_half<BF16>(fmaf(sign * y, sn[angle], x * cs[angle]));
+          }
+#pragma unroll
+          for (int e = 0; e < 8; ++e) kv16[e] = rot[e];
+          // the rotated chunk goes to shared memory by a plain store (visible after the block barrier
+          // that follows the copy wait) instead of an asynchronous copy from k_new
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage + row * G::kRowBytes + ch * 16), "r"(kq.x),
+                       "r"(kq.y), "r"(kq.z), "r"(kq.w)
+                       : "memory");
+          k_by_copy = false;
+        }
         *reinterpret_cast<uint4*>(const_cast<char*>(ksrc)) = kq;
         *reinterpret_cast<uint4*>(const_cast<char*>(vsrc)) = vq;
         ksrc = knew + ch * 16;
         vsrc = vnew + ch * 16;
       }
-      cp_async_16(stage + row * G::kRowBytes + ch * 16, ksrc, ok);
+      if (k_by_copy) cp_async_16(stage + row * G::kRowBytes + ch * 16, ksrc, ok);
       cp_async_16(stage + G::kTileBytes + row * G::kRowBytes + ch * 16, vsrc, ok);
     }
   };
@@ -346,11 +412,11 @@ __global__ void __launch_bounds__(kThreads, 2) decode_mma_kernel(const Problem p
   }
 }
 
-template <int D, bool BF16, bool PAGED, bool APPEND>
+template <int D, bool BF16, bool PAGED, bool APPEND, bool ROPE>
 int launch_one(const Problem& p, int chunk, int nsplit, float* po, float* pml, cudaStream_t stream) {
   using G = Geo<D>;
   static_assert(kWarps * 16 * D * 4 + kWarps * 16 * 2 * 4 <= G::kSmemBytes, "merge buffer must fit in the ring");
-  auto kern = decode_mma_kernel<D, BF16, PAGED, APPEND>;
+  auto kern = decode_mma_kernel<D, BF16, PAGED, APPEND, ROPE>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G::kSmemBytes) != cudaSuccess) {
     cudaGetLastError();
     return B200_SDPA_ERR_CUDA;
@@ -376,9 +442,24 @@ int launch_decode_partial_mma(const Problem& p, int dtype, int chunk, int nsplit
                               cudaStream_t stream) {
   const bool bf16 = dtype == B200_SDPA_BF16;
   const bool d128 = p.E == 128, paged = p.block_table != nullptr, append = p.k_new != nullptr;
+  const bool rope = p.rope_cos != nullptr;
+  if (rope) {
+#define B200_DECODE_ROPE_CASE(DD, BB, PP)                                                              \
+  if (d128 == (DD == 128) && bf16 == BB && paged == PP) return launch_one<DD, BB, PP, true, true>(p, chunk, nsplit, po, pml, stream);
+    B200_DECODE_ROPE_CASE(128, true, false)
+    B200_DECODE_ROPE_CASE(128, false, false)
+    B200_DECODE_ROPE_CASE(64, true, false)
+    B200_DECODE_ROPE_CASE(64, false, false)
+    B200_DECODE_ROPE_CASE(128, true, true)
+    B200_DECODE_ROPE_CASE(128, false, true)
+    B200_DECODE_ROPE_CASE(64, true, true)
+    B200_DECODE_ROPE_CASE(64, false, true)
+#undef B200_DECODE_ROPE_CASE
+    return B200_SDPA_ERR_UNSUPPORTED;
+  }
 #define B200_DECODE_CASE(DD, BB, PP, AA)                                                               \
   if (d128 == (DD == 128) && bf16 == BB && paged == PP && append == AA)                                \
-    return launch_one<DD, BB, PP, AA>(p, chunk, nsplit, po, pml, stream);
+    return launch_one<DD, BB, PP, AA, false>(p, chunk, nsplit, po, pml, stream);
   B200_DECODE_CASE(128, true, false, false)
   B200_DECODE_CASE(128, false, false, false)
   B200_DECODE_CASE(64, true, false, false)

@@ -279,6 +279,9 @@ def paged_decode(
     kv_chunk: int = 0,
     k_new: Optional[torch.Tensor] = None,
     v_new: Optional[torch.Tensor] = None,
+    rope_cos: Optional[torch.Tensor] = None,
+    rope_sin: Optional[torch.Tensor] = None,
+    rope_interleaved: bool = False,
 ):
     """One decode step against a paged key/value cache; returns ``(out, lse)`` -- or, with
     ``k_new`` / ``v_new`` (``(B, Hkv, D)``, the rows of the token being decoded),
@@ -343,7 +346,8 @@ def paged_decode(
     p.block_table = block_table.data_ptr()
     p.block_table_stride = block_table.shape[1]
     p.page_size = page_size
-    new_lens = _attach_new_rows(p, k_new, v_new, query, Hkv, kv_lens)
+    rope = (rope_cos, rope_sin, rope_interleaved) if rope_cos is not None else None
+    new_lens = _attach_new_rows(p, k_new, v_new, query, Hkv, kv_lens, rope)
     p.kv_chunk = int(kv_chunk)
     p.status = _status_word(dev).data_ptr()
     plan = _lib.Plan()
@@ -360,9 +364,12 @@ def paged_decode(
     return (out, lse) if new_lens is None else (out, lse, new_lens)
 
 
-def _attach_new_rows(p, k_new, v_new, query, Hkv, kv_lens):
-    """Fill the append fields of a parameter block; returns the tensor that will receive the new lengths."""
+def _attach_new_rows(p, k_new, v_new, query, Hkv, kv_lens, rope=None):
+    """Fill the append (and rotary) fields of a parameter block; returns the tensor that will receive the
+    new lengths.  ``rope`` = ``(cos, sin, interleaved)`` with fp32 ``(positions, >= D/2)`` tables."""
     if k_new is None and v_new is None:
+        if rope is not None:
+            raise RuntimeError("decode append: the rotary embedding is applied together with an appended row")
         return None
     if k_new is None or v_new is None:
         raise RuntimeError("decode append: k_new and v_new go together")
@@ -373,6 +380,16 @@ def _attach_new_rows(p, k_new, v_new, query, Hkv, kv_lens):
     p.k_new, p.v_new = k_new.data_ptr(), v_new.data_ptr()
     p.k_new_stride[:] = k_new.stride()[:2]
     p.v_new_stride[:] = v_new.stride()[:2]
+    if rope is not None:
+        cos, sin, interleaved = rope
+        for name, t in (("rope_cos", cos), ("rope_sin", sin)):
+            if t.dtype != torch.float32 or t.dim() != 2 or t.shape[1] < E // 2 or t.stride(1) != 1 or t.device != query.device:
+                raise RuntimeError(f"decode append: {name} must be an fp32 (positions, >= D/2) CUDA tensor with unit inner stride")
+        if cos.stride(0) != sin.stride(0):
+            raise RuntimeError("decode append: rope_cos and rope_sin must have the same row stride")
+        p.rope_cos, p.rope_sin = cos.data_ptr(), sin.data_ptr()
+        p.rope_stride = cos.stride(0)
+        p.rope_interleaved = 1 if interleaved else 0
     new_lens = torch.empty_like(kv_lens)
     p.kv_lens_out = new_lens.data_ptr()
     return new_lens
@@ -389,13 +406,19 @@ def decode_append(
     scale: Optional[float] = None,
     need_lse: bool = False,
     kv_chunk: int = 0,
+    rope_cos: Optional[torch.Tensor] = None,
+    rope_sin: Optional[torch.Tensor] = None,
+    rope_interleaved: bool = False,
 ):
     """One decode step of a generation loop against a dense ``(B, Hkv, S, D)`` cache, with the
     cache append fused into the attention kernel: batch ``b`` attends keys ``[0, kv_lens[b]]``
     where key ``kv_lens[b]`` is the new row ``k_new[b]`` / ``v_new[b]`` (``(B, Hkv, D)``), and
     the CTA that reads that row also writes it into ``k_cache`` / ``v_cache`` at that position.
     Returns ``(out, lse, new_lens)`` with ``new_lens = min(kv_lens + 1, S)`` in a fresh tensor.
-    A sequence whose cache is full appends nothing.  (Upstream's loop appends with separate ops
+    A sequence whose cache is full appends nothing.  With ``rope_cos`` / ``rope_sin`` (fp32
+    ``(positions, >= D/2)``) the rotary embedding of position ``kv_lens[b]`` is applied to the query
+    and to the new key inside the same kernel (fp32 arithmetic, one rounding; ``rope_interleaved``
+    selects the (2i, 2i+1) pairing instead of (i, i + D/2)) and the key is cached rotated.  (Upstream's loop appends with separate ops
     before the attention op: ``tests/blocks/block_def/llama.py:110-119`` is the caller shape.)"""
     lib = _lib.load()
     if query.dim() != 4 or query.shape[2] != 1 or k_cache.dim() != 4 or v_cache.shape != k_cache.shape:
@@ -430,7 +453,8 @@ def decode_append(
     p.B, p.Hq, p.Hkv, p.L, p.S, p.E, p.Dv = B, Hq, Hkv, 1, S, E, E
     p.scale = float(scale)
     p.kv_lens = kv_lens.data_ptr()
-    new_lens = _attach_new_rows(p, k_new, v_new, query, Hkv, kv_lens)
+    rope = (rope_cos, rope_sin, rope_interleaved) if rope_cos is not None else None
+    new_lens = _attach_new_rows(p, k_new, v_new, query, Hkv, kv_lens, rope)
     p.kv_chunk = int(kv_chunk)
     p.status = _status_word(dev).data_ptr()
     plan = _lib.Plan()
