@@ -348,6 +348,12 @@ def paged_decode(
     p.page_size = page_size
     rope = (rope_cos, rope_sin, rope_interleaved) if rope_cos is not None else None
     new_lens = _attach_new_rows(p, k_new, v_new, query, Hkv, kv_lens, rope)
+    _launch_decode(lib, p, dev, kv_chunk)
+    return (out, lse) if new_lens is None else (out, lse, new_lens)
+
+
+def _launch_decode(lib, p, dev: int, kv_chunk: int) -> None:
+    """Plan, attach the scratch and enqueue a decode parameter block on the current stream."""
     p.kv_chunk = int(kv_chunk)
     p.status = _status_word(dev).data_ptr()
     plan = _lib.Plan()
@@ -361,7 +367,6 @@ def paged_decode(
     rc = lib.b200_sdpa_decode(C.byref(p), C.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
     if rc != _lib.OK:
         raise RuntimeError(f"b200_sdpa_decode: {_lib.strerror(rc)}")
-    return (out, lse) if new_lens is None else (out, lse, new_lens)
 
 
 def _attach_new_rows(p, k_new, v_new, query, Hkv, kv_lens, rope=None):
@@ -455,19 +460,7 @@ def decode_append(
     p.kv_lens = kv_lens.data_ptr()
     rope = (rope_cos, rope_sin, rope_interleaved) if rope_cos is not None else None
     new_lens = _attach_new_rows(p, k_new, v_new, query, Hkv, kv_lens, rope)
-    p.kv_chunk = int(kv_chunk)
-    p.status = _status_word(dev).data_ptr()
-    plan = _lib.Plan()
-    plan.struct_size = C.sizeof(_lib.Plan)
-    rc = lib.b200_sdpa_query_plan(C.byref(p), C.byref(plan))
-    if rc != _lib.OK:
-        raise RuntimeError(f"b200_sdpa_query_plan: {_lib.strerror(rc)}")
-    ws = _workspace(dev, int(plan.workspace_bytes))
-    p.workspace = ws.data_ptr()
-    p.workspace_bytes = ws.numel()
-    rc = lib.b200_sdpa_decode(C.byref(p), C.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
-    if rc != _lib.OK:
-        raise RuntimeError(f"b200_sdpa_decode: {_lib.strerror(rc)}")
+    _launch_decode(lib, p, dev, kv_chunk)
     return out, lse, new_lens
 
 
