@@ -209,3 +209,25 @@ def test_merge_kernel_matches_oracle():
     torch.testing.assert_close(acc_l.cpu()[live], ref_l[live], rtol=1e-5, atol=1e-5)
     torch.testing.assert_close(acc.cpu(), ref_o, rtol=1e-5, atol=1e-5)
     torch.testing.assert_close(fin.cpu().float(), ref_o, rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("shape", [(1, 4, 2, 300, 300), (2, 8, 8, 130, 517), (1, 24, 24, 1024, 1024), (2, 4, 1, 1, 200)])
+def test_unequal_head_dims_run_on_tensor_cores(shape, causal, dtype):
+    # upstream tests/python_ops/test_scaled_dot_product_attention.py:46-97,117-180: qk head dim 192, v head dim 128
+    import torch_neuronx_b200 as T
+
+    B, Hq, Hkv, L, S = shape
+    g = torch.Generator().manual_seed(L + S + (1 if causal else 0))
+    q = torch.randn(B, Hq, L, 192, generator=g).to(dtype)
+    k = torch.randn(B, Hkv, S, 192, generator=g).to(dtype)
+    v = torch.randn(B, Hkv, S, 128, generator=g).to(dtype)
+    lens = torch.randint(1, S + 1, (B,), generator=g).to(torch.int32) if B > 1 else None
+    T.reset_launch_counts()
+    out, lse = run_cuda(q, k, v, is_causal=causal, kv_lens=lens)
+    assert out.shape == (B, Hq, L, 128)
+    counts = T.launch_counts()
+    assert counts["prefill"] == 1 and counts["generic"] == 0, counts
+    check_against_oracle(q, k, v, out, lse, is_causal=causal, kv_lens=lens, tag=f"192/128 {shape} causal={causal}")

@@ -95,6 +95,10 @@ int launch_decode_static(const Problem& p, int dtype, int kv_chunk, cudaStream_t
 int launch_prefill(const Problem& p, int dtype, cudaStream_t stream);
 int plan_prefill(const Problem& p, int dtype, B200SdpaPlan* plan);
 bool prefill_eligible(const Problem& p, int dtype, bool* alignment_only_failure);
+// unequal head dimensions (E = 192, Dv = 128): prefill_wide_sm100.cu
+bool prefill_wide_eligible(const Problem& p, int dtype, bool* alignment_only_failure);
+int plan_prefill_wide(const Problem& p, int dtype, B200SdpaPlan* plan);
+int launch_prefill_wide(const Problem& p, int dtype, cudaStream_t stream);
 
 int launch_merge(const B200SdpaMergeParams& m, cudaStream_t stream);
 
