@@ -63,8 +63,8 @@ typedef enum b200_sdpa_path {
   B200_SDPA_PATH_GENERIC = 1,  /* CUDA-core fp32-accumulate flash kernel: any dtype,
                                   any strides, additive bias, head dim <= 512        */
   B200_SDPA_PATH_PREFILL = 2,  /* TMA + tcgen05/TMEM warp-specialised kernels:
-                                  f16/bf16, E == Dv in {64,128} or E = 192 with
-                                  Dv = 128, unit inner stride                        */
+                                  f16/bf16, E == Dv in {64,128,256} or E = 192
+                                  with Dv = 128, unit inner stride                   */
   B200_SDPA_PATH_DECODE = 3    /* split-KV flash-decoding kernel + combine, L == 1  */
 } b200_sdpa_path;
 

@@ -231,3 +231,20 @@ def test_unequal_head_dims_run_on_tensor_cores(shape, causal, dtype):
     counts = T.launch_counts()
     assert counts["prefill"] == 1 and counts["generic"] == 0, counts
     check_against_oracle(q, k, v, out, lse, is_causal=causal, kv_lens=lens, tag=f"192/128 {shape} causal={causal}")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("shape", [(1, 4, 2, 300, 300), (2, 2, 2, 130, 517), (1, 8, 8, 1024, 1024)])
+def test_head_dim_256_runs_on_tensor_cores(shape, causal, dtype):
+    import torch_neuronx_b200 as T
+
+    B, Hq, Hkv, L, S = shape
+    q, k, v = make_qkv(L + S, B, Hq, Hkv, L, S, 256, dtype)
+    lens = torch.tensor([S, max(1, S // 3)][:B], dtype=torch.int32) if B > 1 else None
+    T.reset_launch_counts()
+    out, lse = run_cuda(q, k, v, is_causal=causal, kv_lens=lens)
+    counts = T.launch_counts()
+    assert counts["prefill"] == 1 and counts["generic"] == 0, counts
+    check_against_oracle(q, k, v, out, lse, is_causal=causal, kv_lens=lens, tag=f"D=256 {shape} causal={causal}")

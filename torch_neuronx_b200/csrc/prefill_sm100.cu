@@ -716,7 +716,7 @@ extern "C" int b200_debug_read_phases(unsigned long long* host32, int reset) {
 #endif
 
 bool prefill_eligible(const Problem& p, int dtype, bool* alignment_only_failure) {
-  if (p.E == 192 && p.Dv == 128) return prefill_wide_eligible(p, dtype, alignment_only_failure);
+  if (p.E > 128) return prefill_wide_eligible(p, dtype, alignment_only_failure);
   if (alignment_only_failure) *alignment_only_failure = false;
   if (dtype != B200_SDPA_F16 && dtype != B200_SDPA_BF16) return false;
   if (p.E != p.Dv || (p.E != 64 && p.E != 128)) return false;
@@ -730,7 +730,7 @@ bool prefill_eligible(const Problem& p, int dtype, bool* alignment_only_failure)
 }
 
 int plan_prefill(const Problem& p, int dtype, B200SdpaPlan* plan) {
-  if (p.E == 192 && p.Dv == 128) return plan_prefill_wide(p, dtype, plan);
+  if (p.E > 128) return plan_prefill_wide(p, dtype, plan);
   if (!prefill_eligible(p, dtype, nullptr)) return B200_SDPA_ERR_UNSUPPORTED;
   const int pair_heads = pair_heads_mode(p);
   const int rows = pair_heads ? kBlockM : kRowsPerCta;
@@ -751,7 +751,7 @@ int plan_prefill(const Problem& p, int dtype, B200SdpaPlan* plan) {
 }
 
 int launch_prefill(const Problem& p, int dtype, cudaStream_t stream) {
-  if (p.E == 192 && p.Dv == 128) return launch_prefill_wide(p, dtype, stream);
+  if (p.E > 128) return launch_prefill_wide(p, dtype, stream);
   if (!prefill_eligible(p, dtype, nullptr)) return B200_SDPA_ERR_UNSUPPORTED;
   const bool bf16 = dtype == B200_SDPA_BF16;
   if (p.E == 128) return bf16 ? launch_variant<128, true>(p, stream) : launch_variant<128, false>(p, stream);

@@ -1,10 +1,11 @@
-// Prefill kernel for unequal head dimensions (query/key dimension E = 192, value dimension
-// Dv = 128: the shape of multi-head-latent-attention models, which upstream tests as
-// tests/python_ops/test_scaled_dot_product_attention.py:46-97,117-180).
+// Prefill kernel for head dimensions beyond 128: query/key dimension E = 192 with value
+// dimension Dv = 128 (the shape of multi-head-latent-attention models, which upstream tests as
+// tests/python_ops/test_scaled_dot_product_attention.py:46-97,117-180), and E = Dv = 256.
 //
 // Same arithmetic, operand layouts and barrier discipline as prefill_sm100.cu.  The 48 KB Q
 // and K tiles leave no room for two query tiles per CTA, so one CTA owns one 128-row tile:
-// Q (48 KB) + two K slots (48 KB each) + two V slots (32 KB each) = 208 KB of shared memory.
+// Q (48 KB) + two K slots (48 KB each) + two V slots (32 KB each) = 208 KB of shared memory
+// (at 256: Q, one K slot and one V slot of 64 KB each).
 // Roles (192 threads): warps 0-3 softmax (one thread per query row = TMEM lane), warp 4 TMA
 // producer, warp 5 MMA issuer.  TMEM columns: [0,128) S (P overwrites its first 64 columns as
 // 16-bit pairs), [128,128+Dv) O.
@@ -22,7 +23,6 @@ constexpr int kN = 128;   // keys per tile
 constexpr int kThreads = 192;
 constexpr int kProducerWarp = 4;
 constexpr int kMmaWarp = 5;
-constexpr uint32_t kTmemCols = 256;
 constexpr float kRescaleThreshold = 8.0f;   // in units of log2
 
 template <int E, int DV> struct CfgW {
@@ -30,9 +30,10 @@ template <int E, int DV> struct CfgW {
   static constexpr int kBoxesV = DV / 64;
   static constexpr int kTileQK = kN * E * 2;
   static constexpr int kTileV = kN * DV * 2;
-  static constexpr int kSlots = 2;                       // K slots and V slots
+  static constexpr int kSlots = (E <= 192) ? 2 : 1;      // K slots and V slots that fit beside Q
   static constexpr int kSmemTiles = (1 + kSlots) * kTileQK + kSlots * kTileV;
   static constexpr int kSmemBytes = kSmemTiles + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr uint32_t kTmemCols = (128 + DV <= 256) ? 256 : 512;   // S + O, a power of two
 };
 
 struct SyncW {
@@ -134,7 +135,7 @@ prefill_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     mbar_fence_init();
   }
   if (warp == kMmaWarp) {
-    tmem_alloc(smem_u32(&sync->tmem_base), kTmemCols);
+    tmem_alloc(smem_u32(&sync->tmem_base), C::kTmemCols);
     tmem_relinquish();
   }
   tc_fence_before_sync();
@@ -392,7 +393,7 @@ prefill_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   __syncthreads();
   if (warp == kMmaWarp) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, kTmemCols);
+    tmem_dealloc(tmem_base, C::kTmemCols);
   }
 }
 
@@ -422,7 +423,7 @@ int launch_wide(const Problem& p, cudaStream_t stream) {
 bool prefill_wide_eligible(const Problem& p, int dtype, bool* alignment_only_failure) {
   if (alignment_only_failure) *alignment_only_failure = false;
   if (dtype != B200_SDPA_F16 && dtype != B200_SDPA_BF16) return false;
-  if (p.E != 192 || p.Dv != 128) return false;
+  if (!((p.E == 192 && p.Dv == 128) || (p.E == 256 && p.Dv == 256))) return false;
   if (p.bias != nullptr || p.block_table != nullptr || p.k_new != nullptr) return false;
   if (!(p.scale > 0.f) || !(p.scale < 1e30f)) return false;
   if (p.L < 1 || p.S < 1) return false;
@@ -442,7 +443,7 @@ int plan_prefill_wide(const Problem& p, int dtype, B200SdpaPlan* plan) {
   plan->grid_x = static_cast<int32_t>(grid);
   plan->grid_y = plan->grid_z = 1;
   plan->threads = kThreads;
-  plan->smem_bytes = CfgW<192, 128>::kSmemBytes;
+  plan->smem_bytes = p.E == 192 ? CfgW<192, 128>::kSmemBytes : CfgW<256, 256>::kSmemBytes;
   plan->kv_splits = 1;
   plan->launches = 1;
   plan->workspace_bytes = 0;
@@ -451,7 +452,9 @@ int plan_prefill_wide(const Problem& p, int dtype, B200SdpaPlan* plan) {
 
 int launch_prefill_wide(const Problem& p, int dtype, cudaStream_t stream) {
   if (!prefill_wide_eligible(p, dtype, nullptr)) return B200_SDPA_ERR_UNSUPPORTED;
-  return dtype == B200_SDPA_BF16 ? launch_wide<192, 128, true>(p, stream) : launch_wide<192, 128, false>(p, stream);
+  const bool bf16 = dtype == B200_SDPA_BF16;
+  if (p.E == 192) return bf16 ? launch_wide<192, 128, true>(p, stream) : launch_wide<192, 128, false>(p, stream);
+  return bf16 ? launch_wide<256, 256, true>(p, stream) : launch_wide<256, 256, false>(p, stream);
 }
 
 }  // namespace b200
