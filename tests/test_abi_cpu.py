@@ -77,6 +77,20 @@ def test_planner_picks_the_expected_kernel():
     assert rc == 0 and plan.path == _lib.PATH_GENERIC
     rc, plan = _plan(_params(scale=-1.0))
     assert rc == 0 and plan.path == _lib.PATH_GENERIC
+    # head dims beyond 128: the one-tile-per-CTA tensor-core kernel
+    p = _params(E=192, Dv=128)
+    p.q_stride[:] = [8 * 256 * 192, 256 * 192, 192, 1]
+    p.k_stride[:] = [2 * 256 * 192, 256 * 192, 192, 1]
+    rc, plan = _plan(p)
+    assert rc == 0 and plan.path == _lib.PATH_PREFILL and plan.block_m == 128 and plan.threads == 192
+    assert plan.grid_x == 2 * 8 * 1 and plan.smem_bytes > 200 * 1024
+    p = _params(E=256, Dv=256)
+    for st, h in ((p.q_stride, 8), (p.k_stride, 2), (p.v_stride, 2), (p.out_stride, 8)):
+        st[:] = [h * 256 * 256, 256 * 256, 256, 1]
+    rc, plan = _plan(p)
+    assert rc == 0 and plan.path == _lib.PATH_PREFILL and plan.threads == 192
+    rc, plan = _plan(_params(E=192, Dv=192))   # not a shape the wide kernel is built for
+    assert rc == 0 and plan.path == _lib.PATH_GENERIC
 
 
 def test_planner_rejects_bad_blocks():
