@@ -262,6 +262,15 @@ def run_profile_case(args):
         out = torch.empty_like(q)
         lse = torch.empty(8, 12, 1024, dtype=torch.float32, device=dev)
         fn = lambda: T.sdpa_forward(q, k, v, is_causal=True, scale=0.125, out=out, lse=lse)  # noqa: E731
+    elif args.profile == "wide":
+        # multi-head-latent-attention shape: q/k head dim 192, v head dim 128 (335 MB of operands)
+        g = torch.Generator(device=dev).manual_seed(5)
+        q = torch.randn(4, 32, 4096, 192, generator=g, device=dev, dtype=torch.bfloat16)
+        k = torch.randn(4, 32, 4096, 192, generator=g, device=dev, dtype=torch.bfloat16)
+        v = torch.randn(4, 32, 4096, 128, generator=g, device=dev, dtype=torch.bfloat16)
+        out = torch.empty(4, 32, 4096, 128, device=dev, dtype=torch.bfloat16)
+        lse = torch.empty(4, 32, 4096, dtype=torch.float32, device=dev)
+        fn = lambda: T.sdpa_forward(q, k, v, is_causal=True, out=out, lse=lse)  # noqa: E731
     elif args.profile == "bwd":
         # the headline batch cut to one sequence (84 MB of operands, still around L2 size) keeps captures short
         q, k, v, lens = c3_inputs(2, device=dev)
@@ -613,7 +622,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--profile", default=None, choices=["prefill", "decode", "gpt2", "bwd"],
+    ap.add_argument("--profile", default=None, choices=["prefill", "decode", "gpt2", "bwd", "wide"],
                     help="bare kernel loop on one GPU for profiler captures")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the decode / GPT-2 / fp32 extras")

@@ -263,7 +263,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
                  const __grid_constant__ CUtensorMap tm_dq, const Problem p, const float* __restrict__ lse2,
-                 const float* __restrict__ delta, const int l_pad, const int n_qblk, const long long wait_limit) {
+                 const float* __restrict__ delta, const int l_pad, const int n_qblk, const int streams_per_wave,
+                 const long long wait_limit) {
   using C = ACfg<D>;
   extern __shared__ uint8_t smem_raw[];
 #ifdef B200_TRACE
@@ -282,13 +283,21 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
 
-  // latest query blocks (most key tiles under a causal mask) first
-  const int per_blk = p.Hq * p.B;
-  const int qblk = n_qblk - 1 - static_cast<int>(blockIdx.x / per_blk);
-  const int rem = static_cast<int>(blockIdx.x % per_blk);
-  const int h = rem % p.Hq;
-  const int b = rem / p.Hq;
-  const int hk = h / p.group;
+  // Latest query blocks (most key tiles under a causal mask) first, within waves of
+  // `streams_per_wave` (batch, kv head) key/value streams that fit in L2 together.
+  const int n_streams = p.Hkv * p.B;
+  const int full_wave_ctas = n_qblk * streams_per_wave * p.group;
+  const int wave = static_cast<int>(blockIdx.x / full_wave_ctas);
+  const int in_wave = static_cast<int>(blockIdx.x - static_cast<unsigned>(wave) * full_wave_ctas);
+  const int first_stream = wave * streams_per_wave;
+  const int wave_streams = (n_streams - first_stream) < streams_per_wave ? (n_streams - first_stream) : streams_per_wave;
+  const int per_blk = wave_streams * p.group;
+  const int qblk = n_qblk - 1 - in_wave / per_blk;
+  const int rem = in_wave % per_blk;
+  const int kv_stream = first_stream + rem / p.group;
+  const int hk = kv_stream % p.Hkv;
+  const int b = kv_stream / p.Hkv;
+  const int h = hk * p.group + rem % p.group;
   const int row0 = qblk * kT;
   const int kv_limit = valid_keys(p, b);
   long long end = kv_limit, first = kv_limit;
@@ -576,7 +585,7 @@ bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                   const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
                   const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv,
                   const Problem p, const float* __restrict__ lse2, const float* __restrict__ delta, const int l_pad,
-                  const int n_kblk, const long long wait_limit) {
+                  const int n_kblk, const int streams_per_wave, const long long wait_limit) {
   using C = BCfg<D>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -588,12 +597,18 @@ bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
 
-  // earliest key blocks (seen by the most query tiles under a causal mask) first
-  const int per_blk = p.Hkv * p.B;
-  const int kblk = static_cast<int>(blockIdx.x / per_blk);
-  const int rem = static_cast<int>(blockIdx.x % per_blk);
-  const int hk = rem % p.Hkv;
-  const int b = rem / p.Hkv;
+  // Earliest key blocks (seen by the most query tiles under a causal mask) first, within waves of
+  // `streams_per_wave` (batch, kv head) groups whose query-side operands fit in L2 together.
+  const int n_streams = p.Hkv * p.B;
+  const int full_wave_ctas = n_kblk * streams_per_wave;
+  const int wave = static_cast<int>(blockIdx.x / full_wave_ctas);
+  const int in_wave = static_cast<int>(blockIdx.x - static_cast<unsigned>(wave) * full_wave_ctas);
+  const int first_stream = wave * streams_per_wave;
+  const int wave_streams = (n_streams - first_stream) < streams_per_wave ? (n_streams - first_stream) : streams_per_wave;
+  const int kblk = in_wave / wave_streams;
+  const int kv_stream = first_stream + in_wave % wave_streams;
+  const int hk = kv_stream % p.Hkv;
+  const int b = kv_stream / p.Hkv;
   const int j0 = kblk * kT;
   const int n_keys = valid_keys(p, b);
   const int n_qt = (p.L + kT - 1) / kT;
@@ -873,12 +888,16 @@ int launch_tc(const BwdProblem& bp, float* lse2, float* delta, cudaStream_t stre
   const long long grid_kv = static_cast<long long>(n_kblk) * p.Hkv * p.B;
   if (grid_q > 0x7fffffffLL || grid_kv > 0x7fffffffLL) return B200_SDPA_ERR_UNSUPPORTED;
   const long long limit = wait_limit_cycles();
+  const long long n_streams = static_cast<long long>(p.Hkv) * p.B;
+  // the dQ kernel streams keys and values; the dK/dV kernel the queries, dO and row statistics of a group
+  const int wave_q = kv_streams_per_wave(static_cast<long long>(p.S) * 2 * D * 2, n_streams);
+  const int wave_kv = kv_streams_per_wave(static_cast<long long>(p.L) * p.group * (2 * D * 2 + 8), n_streams);
   kq<<<static_cast<unsigned>(grid_q), kThreads, ACfg<D>::kSmemBytes, stream>>>(tq, tk, tv, tdo, tdq, p, lse2, delta, l_pad,
-                                                                        n_qblk, limit);
+                                                                        n_qblk, wave_q, limit);
   if (cudaGetLastError() != cudaSuccess) return B200_SDPA_ERR_CUDA;
   count_launch(KID_BWD_DQ);
   kkv<<<static_cast<unsigned>(grid_kv), kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, tdk, tdv, p, lse2, delta,
-                                                                          l_pad, n_kblk, limit);
+                                                                          l_pad, n_kblk, wave_kv, limit);
   if (cudaGetLastError() != cudaSuccess) return B200_SDPA_ERR_CUDA;
   count_launch(KID_BWD_DKV);
   return B200_SDPA_OK;

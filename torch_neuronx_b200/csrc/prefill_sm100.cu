@@ -140,7 +140,7 @@ template <int D, bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o, const Problem p,
-               const int n_qblk, const int pair_heads, const long long wait_limit) {
+               const int n_qblk, const int pair_heads, const int streams_per_wave, const long long wait_limit) {
   using C = Cfg<D>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -166,13 +166,23 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   //   pair_heads == 1: the same 128 rows of two query heads that share a kv head
   //     (even group size) -- both tiles then see exactly the same keys, so under a
   //     causal mask neither waits for the other's extra diagonal tile.
+  // The (batch, kv head) key/value streams are taken `streams_per_wave` at a time, so that what the
+  // CTAs in flight read together fits in L2 (all streams at once when they do).
   const int heads_per_cta = pair_heads ? 2 : 1;
-  const int per_blk = (p.Hq / heads_per_cta) * p.B;
-  const int qblk = n_qblk - 1 - static_cast<int>(blockIdx.x / per_blk);
-  const int rem = static_cast<int>(blockIdx.x % per_blk);
-  const int hq0 = (rem % (p.Hq / heads_per_cta)) * heads_per_cta;
-  const int b = rem / (p.Hq / heads_per_cta);
-  const int hk = hq0 / p.group;
+  const int ctas_per_stream = p.group / heads_per_cta;            // per query block
+  const int n_streams = p.Hkv * p.B;
+  const int full_wave_ctas = n_qblk * streams_per_wave * ctas_per_stream;
+  const int wave = static_cast<int>(blockIdx.x / full_wave_ctas);
+  const int in_wave = static_cast<int>(blockIdx.x - static_cast<unsigned>(wave) * full_wave_ctas);
+  const int first_stream = wave * streams_per_wave;
+  const int wave_streams = (n_streams - first_stream) < streams_per_wave ? (n_streams - first_stream) : streams_per_wave;
+  const int per_blk = wave_streams * ctas_per_stream;
+  const int qblk = n_qblk - 1 - in_wave / per_blk;
+  const int rem = in_wave % per_blk;
+  const int stream = first_stream + rem / ctas_per_stream;
+  const int hk = stream % p.Hkv;
+  const int b = stream / p.Hkv;
+  const int hq0 = hk * p.group + (rem % ctas_per_stream) * heads_per_cta;
   const int head_of_tile[2] = {hq0, pair_heads ? hq0 + 1 : hq0};
   const int kv_limit = valid_keys(p, b);
   const int rows_per_cta = pair_heads ? kBlockM : kRowsPerCta;
@@ -686,8 +696,9 @@ int launch_variant(const Problem& p, cudaStream_t stream) {
   const int n_qblk = (p.L + rows - 1) / rows;
   const long long grid = static_cast<long long>(n_qblk) * (p.Hq / (pair_heads ? 2 : 1)) * p.B;
   if (grid <= 0 || grid > 0x7fffffffLL) return B200_SDPA_ERR_UNSUPPORTED;
+  const int per_wave = kv_streams_per_wave(static_cast<long long>(p.S) * 2 * D * 2, static_cast<long long>(p.Hkv) * p.B);
   kern<<<static_cast<unsigned>(grid), kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, to, p, n_qblk, pair_heads,
-                                                                         wait_limit_cycles());
+                                                                         per_wave, wait_limit_cycles());
   if (cudaGetLastError() != cudaSuccess) return B200_SDPA_ERR_CUDA;
   count_launch(KID_PREFILL);
   return B200_SDPA_OK;

@@ -53,7 +53,7 @@ template <int E, int DV, bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o, const Problem p,
-                const int n_qblk, const long long wait_limit) {
+                const int n_qblk, const int streams_per_wave, const long long wait_limit) {
   using C = CfgW<E, DV>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -64,13 +64,22 @@ prefill_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
 
-  // latest query blocks (most key tiles under a causal mask) first, heads of a kv group adjacent
-  const int per_blk = p.Hq * p.B;
-  const int qblk = n_qblk - 1 - static_cast<int>(blockIdx.x / per_blk);
-  const int rem = static_cast<int>(blockIdx.x % per_blk);
-  const int h = rem % p.Hq;
-  const int b = rem / p.Hq;
-  const int hk = h / p.group;
+  // Work order.  The (batch, kv head) key/value streams are taken `streams_per_wave` at a time, so that
+  // the keys and values the CTAs in flight read together fit in L2; inside such a wave: latest query
+  // blocks (most key tiles under a causal mask) first, the query heads of a kv head adjacent.
+  const int n_streams = p.Hkv * p.B;
+  const int full_wave_ctas = n_qblk * streams_per_wave * p.group;
+  const int wave = static_cast<int>(blockIdx.x / full_wave_ctas);
+  const int in_wave = static_cast<int>(blockIdx.x - static_cast<unsigned>(wave) * full_wave_ctas);
+  const int first_stream = wave * streams_per_wave;
+  const int wave_streams = (n_streams - first_stream) < streams_per_wave ? (n_streams - first_stream) : streams_per_wave;
+  const int per_blk = wave_streams * p.group;
+  const int qblk = n_qblk - 1 - in_wave / per_blk;
+  const int rem = in_wave % per_blk;
+  const int stream = first_stream + rem / p.group;
+  const int hk = stream % p.Hkv;
+  const int b = stream / p.Hkv;
+  const int h = hk * p.group + rem % p.group;
   const int row0 = qblk * kM;
   const int kv_limit = valid_keys(p, b);
   long long end = kv_limit, first = kv_limit;
@@ -412,7 +421,9 @@ int launch_wide(const Problem& p, cudaStream_t stream) {
   const int n_qblk = (p.L + kM - 1) / kM;
   const long long grid = static_cast<long long>(n_qblk) * p.Hq * p.B;
   if (grid <= 0 || grid > 0x7fffffffLL) return B200_SDPA_ERR_UNSUPPORTED;
-  kern<<<static_cast<unsigned>(grid), kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, to, p, n_qblk, wait_limit_cycles());
+  const int per_wave = kv_streams_per_wave(static_cast<long long>(p.S) * (E + DV) * 2, static_cast<long long>(p.Hkv) * p.B);
+  kern<<<static_cast<unsigned>(grid), kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, to, p, n_qblk,
+                                                                         per_wave, wait_limit_cycles());
   if (cudaGetLastError() != cudaSuccess) return B200_SDPA_ERR_CUDA;
   count_launch(KID_PREFILL);
   return B200_SDPA_OK;

@@ -139,6 +139,17 @@ inline bool strides_ok(const void* base, const int64_t* s, int rows, int heads, 
   return true;
 }
 
+// Key/value bytes that the CTAs of one wave of (batch, kv head) streams read together: about a quarter
+// of the 126 MB L2, so that a wave's streams stay resident while its query blocks sweep over them.
+#ifndef B200_WAVE_BYTES
+#define B200_WAVE_BYTES (32LL << 20)
+#endif
+inline int kv_streams_per_wave(long long stream_bytes, long long n_streams) {
+  long long per_wave = B200_WAVE_BYTES / (stream_bytes > 0 ? stream_bytes : 1);
+  per_wave = per_wave < 1 ? 1 : (per_wave > n_streams ? n_streams : per_wave);
+  return static_cast<int>(per_wave);
+}
+
 inline long long wait_limit_cycles() {
   // about two seconds at 2 GHz; B200_SDPA_WAIT_LIMIT overrides (cycles)
   static long long v = [] {
