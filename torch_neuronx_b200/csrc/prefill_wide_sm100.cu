@@ -33,15 +33,16 @@ template <int E, int DV> struct CfgW {
   static constexpr int kSlots = (E <= 192) ? 2 : 1;      // K slots and V slots that fit beside Q
   static constexpr int kSmemTiles = (1 + kSlots) * kTileQK + kSlots * kTileV;
   static constexpr int kSmemBytes = kSmemTiles + 1024 /*alignment slack*/ + 256 /*barriers*/;
-  static constexpr uint32_t kTmemCols = (128 + DV <= 256) ? 256 : 512;   // S + O, a power of two
+  static constexpr uint32_t kTmemCols = 512;   // two score buffers + O (2 * 128 + DV), a power of two
 };
 
 struct SyncW {
   uint64_t q_full;
   uint64_t k_full[2], k_empty[2];
   uint64_t v_full[2], v_empty[2];
-  uint64_t s_full;
-  uint64_t p_ready[2];   // halves of P
+  uint64_t s_full[2];       // per score buffer
+  uint64_t p_ready[2][2];   // per score buffer, halves of P
+  uint64_t pv_done;         // P V of a key tile has retired: O may be rescaled
   uint64_t o_done;
   uint64_t o_staged;
   uint64_t drain;
@@ -134,9 +135,12 @@ prefill_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     prefetch_tmap(&tm_o);
   }
   if (tid == 0) {
-    mbar_init(smem_u32(&sync->s_full), 1);
-    mbar_init(smem_u32(&sync->p_ready[0]), kM);
-    mbar_init(smem_u32(&sync->p_ready[1]), kM);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&sync->s_full[i]), 1);
+      mbar_init(smem_u32(&sync->p_ready[i][0]), kM);
+      mbar_init(smem_u32(&sync->p_ready[i][1]), kM);
+    }
+    mbar_init(smem_u32(&sync->pv_done), 1);
     mbar_init(smem_u32(&sync->o_done), 1);
     mbar_init(smem_u32(&sync->o_staged), kM);
     mbar_init(smem_u32(&sync->drain), 1);
@@ -151,7 +155,9 @@ prefill_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = sync->tmem_base;
-  constexpr uint32_t kColS = 0, kColO = 128;
+  // Scores of key tile j live in buffer j & 1, so that Q K^T of the next tile runs under the softmax
+  // of this one and P V of this one under the softmax of the next.
+  constexpr uint32_t kColS = 0, kColO = 256;
 
   if (warp == kProducerWarp) {
     // ------------------------------------------------------------ TMA producer
@@ -193,9 +199,9 @@ prefill_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 #pragma unroll
         for (int kk = 0; kk < E / 16; ++kk) {
           const uint64_t off = static_cast<uint64_t>(((kk >> 2) * kBoxBytes + (kk & 3) * 32) >> 4);
-          mma_ss(tmem_base + kColS, q_desc + off, kd + off, idesc_qk, kk > 0 ? 1u : 0u);
+          mma_ss(tmem_base + kColS + static_cast<uint32_t>((j & 1) * kN), q_desc + off, kd + off, idesc_qk, kk > 0 ? 1u : 0u);
         }
-        mma_commit(smem_u32(&sync->s_full));
+        mma_commit(smem_u32(&sync->s_full[j & 1]));
         mma_commit(smem_u32(&sync->k_empty[slot]));
       }
       return true;
@@ -207,6 +213,11 @@ prefill_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     if (alive) alive = issue_qk(0);
     for (int j = 0; j < n_tiles && alive; ++j) {
       const int slot = j % C::kSlots;
+      // the buffer of tile j + 1 held P of tile j - 1, whose P V was issued before (MMAs run in order)
+      if (j + 1 < n_tiles) {
+        alive = issue_qk(j + 1);
+        if (!alive) break;
+      }
       alive = wait_clocked(smem_u32(&sync->v_full[slot]), static_cast<uint32_t>(j / C::kSlots) & 1u, abort_flag, wait_limit);
       if (!alive) {
         if (lane == 0) report(p.status, 2, j, 8 + slot);
@@ -215,7 +226,7 @@ prefill_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       const uint64_t vd0 = smem_desc_sw128(v_smem + slot * C::kTileV, kBoxBytes, 1024);   // V tile as MN-major B operand
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        alive = wait_clocked(smem_u32(&sync->p_ready[half]), j & 1, abort_flag, wait_limit);
+        alive = wait_clocked(smem_u32(&sync->p_ready[j & 1][half]), static_cast<uint32_t>(j >> 1) & 1u, abort_flag, wait_limit);
         if (!alive) {
           if (lane == 0) report(p.status, 3, j, half);
           break;
@@ -224,16 +235,15 @@ prefill_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         if (elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            mma_ts(tmem_base + kColO, tmem_base + kColS + static_cast<uint32_t>(half * 32 + kk * 8),
+            mma_ts(tmem_base + kColO, tmem_base + kColS + static_cast<uint32_t>((j & 1) * kN + half * 32 + kk * 8),
                    vd0 + static_cast<uint64_t>((half * 4 + kk) * (2048 >> 4)), idesc_pv, (j > 0 || half > 0 || kk > 0) ? 1u : 0u);
         }
       }
       if (!alive) break;
-      if (elect_one()) mma_commit(smem_u32(&sync->v_empty[slot]));
-      if (j + 1 < n_tiles) {
-        alive = issue_qk(j + 1);
-      } else if (elect_one()) {
-        mma_commit(smem_u32(&sync->o_done));
+      if (elect_one()) {
+        mma_commit(smem_u32(&sync->v_empty[slot]));
+        mma_commit(smem_u32(&sync->pv_done));
+        if (j + 1 == n_tiles) mma_commit(smem_u32(&sync->o_done));
       }
     }
     if (*abort_flag != 0) {
@@ -247,7 +257,7 @@ prefill_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     // ------------------------------------------------------------ softmax role
     const int r = tid;                       // row inside the tile = TMEM lane
     const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
-    const uint32_t s_addr = tmem_base + lane_off + kColS;
+    const uint32_t s_base = tmem_base + lane_off + kColS;
     const uint32_t o_addr = tmem_base + lane_off + kColO;
     const int row_g = row0 + r;
     int lim = kv_limit;                      // keys [0, lim) are visible to this row
@@ -260,7 +270,8 @@ prefill_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     bool alive = true;
 
     for (int j = 0; j < n_tiles; ++j) {
-      bool ok = wait_clocked(smem_u32(&sync->s_full), j & 1, abort_flag, wait_limit);
+      const uint32_t s_addr = s_base + static_cast<uint32_t>((j & 1) * kN);
+      bool ok = wait_clocked(smem_u32(&sync->s_full[j & 1]), static_cast<uint32_t>(j >> 1) & 1u, abort_flag, wait_limit);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
         if (lane == 0) report(p.status, 4, j, warp);
@@ -307,8 +318,15 @@ prefill_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         m_run = m_new;
       }
       if (j > 0 && __any_sync(0xffffffffu, grow)) {
-        // raise the reference maximum: O *= alpha (P V of the previous tile has retired: its
-        // completion is ordered before s_full of this one)
+        // raise the reference maximum: O *= alpha, once P V of the previous tile has retired
+        ok = wait_clocked(smem_u32(&sync->pv_done), static_cast<uint32_t>(j - 1) & 1u, abort_flag, wait_limit);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          if (lane == 0) report(p.status, 5, j, warp);
+          alive = false;
+          break;
+        }
+        tc_fence_after_sync();
 #pragma unroll
         for (int c = 0; c < DV / 16; ++c) {
           uint32_t v[16];
@@ -338,7 +356,7 @@ prefill_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           // first 64 keys of P are in TMEM: let P V start on them while the rest is computed
           tmem_st_wait();
           tc_fence_before_sync();
-          mbar_arrive(smem_u32(&sync->p_ready[0]));
+          mbar_arrive(smem_u32(&sync->p_ready[j & 1][0]));
         }
       }
       float sum4[4];
@@ -347,7 +365,7 @@ prefill_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       tmem_st_wait();
       tc_fence_before_sync();
-      mbar_arrive(smem_u32(&sync->p_ready[1]));
+      mbar_arrive(smem_u32(&sync->p_ready[j & 1][1]));
     }
 
     // ------------------------------------------------------------- epilogue
