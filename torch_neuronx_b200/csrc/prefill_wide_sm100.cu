@@ -213,8 +213,10 @@ prefill_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     if (alive) alive = issue_qk(0);
     for (int j = 0; j < n_tiles && alive; ++j) {
       const int slot = j % C::kSlots;
-      // the buffer of tile j + 1 held P of tile j - 1, whose P V was issued before (MMAs run in order)
-      if (j + 1 < n_tiles) {
+      // The buffer of tile j + 1 held P of tile j - 1, whose P V was issued before (MMAs run in order).
+      // With a single K slot the next key tile lands late, and waiting for it here would hold back
+      // P V (j): then the score product follows P V instead.
+      if (C::kSlots > 1 && j + 1 < n_tiles) {
         alive = issue_qk(j + 1);
         if (!alive) break;
       }
@@ -245,6 +247,7 @@ prefill_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         mma_commit(smem_u32(&sync->pv_done));
         if (j + 1 == n_tiles) mma_commit(smem_u32(&sync->o_done));
       }
+      if (C::kSlots == 1 && j + 1 < n_tiles) alive = issue_qk(j + 1);
     }
     if (*abort_flag != 0) {
       if (elect_one()) mma_commit(smem_u32(&sync->drain));
