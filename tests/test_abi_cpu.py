@@ -265,3 +265,40 @@ def test_append_planning():
     assert _plan(dec(rope_cos=0x7F0000800000, rope_stride=64))[0] == _lib.ERR_NULL
     assert _plan(dec(k_new=None, v_new=None, **rope))[0] == _lib.ERR_UNSUPPORTED
     assert _plan(dec(rope_cos=0x7F0000800000, rope_sin=0x7F0000900000, rope_stride=32))[0] == _lib.ERR_UNSUPPORTED
+
+
+def test_bias_planning():
+    """An additive bias stays on the tcgen05 kernel when its softmax threads can read it as 16-byte
+    pieces of a row: the query's dtype, unit stride along the keys, S % 8 == 0, aligned rows."""
+    fake_bias = 0x7F4000000000
+    L = S = 512
+    full = dict(bias=fake_bias, bias_dtype=_lib.BF16)
+
+    def plan_with(stride, **kw):
+        p = _params(L=L, S=kw.pop("S", S), **{**full, **kw})
+        p.bias_stride[:] = stride
+        return _plan(p)
+
+    rc, plan = plan_with([8 * L * S, L * S, S, 1])
+    assert rc == 0 and plan.path == _lib.PATH_PREFILL
+    rc, plan = plan_with([0, 0, S, 1])                       # broadcast over batch and heads
+    assert rc == 0 and plan.path == _lib.PATH_PREFILL
+    rc, plan = plan_with([S, 0, 0, 1])                       # per batch and key
+    assert rc == 0 and plan.path == _lib.PATH_PREFILL
+    rc, plan = plan_with([8 * L * S, L * S, S, 1], E=64, Dv=64)
+    assert rc == 0 and plan.path == _lib.PATH_PREFILL
+    # everything else is served by the CUDA-core kernel
+    rc, plan = plan_with([8 * L * S, L * S, S, 1], bias_dtype=_lib.F32)
+    assert rc == 0 and plan.path == _lib.PATH_GENERIC
+    rc, plan = plan_with([8 * L * S, L * S, S, 1], bias_dtype=_lib.F16)
+    assert rc == 0 and plan.path == _lib.PATH_GENERIC       # not the query's dtype
+    rc, plan = plan_with([8 * L * 2 * S, L * 2 * S, 2 * S, 2])
+    assert rc == 0 and plan.path == _lib.PATH_GENERIC       # strided along the keys
+    rc, plan = plan_with([8 * L * 500, L * 500, 500, 1], S=500)
+    assert rc == 0 and plan.path == _lib.PATH_GENERIC       # S % 8 != 0
+    rc, plan = plan_with([8 * L * S, L * S, S + 4, 1])
+    assert rc == 0 and plan.path == _lib.PATH_GENERIC       # rows off the 16-byte grid
+    rc, plan = plan_with([8 * L * S, L * S, S, 1], bias=fake_bias + 2)
+    assert rc == 0 and plan.path == _lib.PATH_GENERIC
+    rc, plan = plan_with([8 * L * S, L * S, S, 1], E=192, Dv=128)
+    assert rc == 0 and plan.path == _lib.PATH_GENERIC       # the wide kernel takes no bias

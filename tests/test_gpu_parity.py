@@ -248,3 +248,67 @@ def test_head_dim_256_runs_on_tensor_cores(shape, causal, dtype):
     counts = T.launch_counts()
     assert counts["prefill"] == 1 and counts["generic"] == 0, counts
     check_against_oracle(q, k, v, out, lse, is_causal=causal, kv_lens=lens, tag=f"D=256 {shape} causal={causal}")
+
+
+def _make_bias(kind, B, Hq, L, S, dtype, g):
+    shape = {"full": (B, Hq, L, S), "query_key": (L, S), "batch_key": (B, 1, 1, S), "head": (1, Hq, L, S)}[kind]
+    bias = (torch.randn(shape, generator=g) * 2).to(dtype)
+    drop = torch.rand(shape, generator=g) < 0.1
+    bias = bias.masked_fill(drop, float("-inf"))
+    if kind == "full":
+        bias[0, 0, min(5, L - 1)] = float("-inf")        # a row without a visible key
+    if kind == "batch_key":
+        bias[-1, ..., S // 2:] = float("-inf")          # right padding written as a bias
+    return bias
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("kind", ["full", "query_key", "batch_key", "head"])
+@pytest.mark.parametrize("shape", [(2, 4, 2, 300, 304, 128), (1, 8, 8, 520, 1024, 64), (2, 6, 3, 129, 136, 128)])
+def test_additive_bias_runs_on_tensor_cores(shape, kind, dtype):
+    """An additive bias in the query's dtype (what the SDPA front end makes of every mask it does not
+    recognise) is read by the softmax threads of the tcgen05 kernel: full, broadcast over batch and
+    heads, over heads and queries, and over the batch; -inf entries and a dead row included."""
+    import torch_neuronx_b200 as T
+
+    B, Hq, Hkv, L, S, D = shape
+    g = torch.Generator().manual_seed(L * 7 + S + D)
+    q = torch.randn(B, Hq, L, D, generator=g).to(dtype)
+    k = torch.randn(B, Hkv, S, D, generator=g).to(dtype)
+    v = torch.randn(B, Hkv, S, D, generator=g).to(dtype)
+    bias = _make_bias(kind, B, Hq, L, S, dtype, g)
+    out, lse = run_cuda(q, k, v, attn_bias=bias)
+    assert T.ops.last_plan["path"] == "prefill"
+    check_against_oracle(q, k, v, out, lse, attn_mask=bias, tag=f"bias {kind}")
+    if kind == "full":
+        r = min(5, L - 1)
+        assert torch.all(out[0, 0, r] == 0) and lse[0, 0, r] == float("-inf")
+
+
+def test_additive_bias_with_key_lengths_and_fallbacks():
+    import torch_neuronx_b200 as T
+
+    g = torch.Generator().manual_seed(77)
+    B, Hq, Hkv, L, S, D = 2, 4, 4, 256, 512, 128
+    q = torch.randn(B, Hq, L, D, generator=g).to(torch.bfloat16)
+    k = torch.randn(B, Hkv, S, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(B, Hkv, S, D, generator=g).to(torch.bfloat16)
+    bias = torch.randn(B, Hq, L, S, generator=g).to(torch.bfloat16)
+    lens = torch.tensor([300, 512], dtype=torch.int32)
+    out, lse = run_cuda(q, k, v, attn_bias=bias, kv_lens=lens)
+    assert T.ops.last_plan["path"] == "prefill"
+    check_against_oracle(q, k, v, out, lse, attn_mask=bias, kv_lens=lens, tag="bias + lengths")
+    # what the tensor-core kernel cannot read as 16-byte pieces goes to the CUDA-core kernel:
+    # a key count that is not a multiple of 8, a bias of another dtype, a strided last dimension
+    out, lse = run_cuda(q, k[:, :, :500], v[:, :, :500], attn_bias=bias[..., :500].contiguous())
+    assert T.ops.last_plan["path"] == "generic"
+    check_against_oracle(q, k[:, :, :500], v[:, :, :500], out, lse, attn_mask=bias[..., :500], tag="S % 8")
+    out, lse = run_cuda(q, k, v, attn_bias=bias.float())
+    assert T.ops.last_plan["path"] == "generic"
+    check_against_oracle(q, k, v, out, lse, attn_mask=bias.float(), tag="fp32 bias")
+    wide = torch.randn(B, Hq, L, 2 * S, generator=g).to(torch.bfloat16)
+    strided = wide.to("cuda:0")[..., ::2]
+    out, lse = T.sdpa_forward(q.to("cuda:0"), k.to("cuda:0"), v.to("cuda:0"), attn_bias=strided)
+    torch.cuda.synchronize()
+    assert T.ops.last_plan["path"] == "generic"
+    check_against_oracle(q, k, v, out.cpu(), lse.cpu(), attn_mask=wide[..., ::2], tag="strided bias")

@@ -136,7 +136,28 @@ __device__ __forceinline__ TileGeom tile_geometry(const Problem& p, int row0, in
   return g;
 }
 
-template <int D, bool BF16>
+// Eight logits in log2 units: s * (scale * log2 e) + bias * log2 e, the bias as eight 16-bit
+// elements of the query's dtype.
+template <bool BF16>
+__device__ __forceinline__ void add_bias8(uint32_t* sv, const uint4 bias, const float sl2_in) {
+  const uint32_t w[4] = {bias.x, bias.y, bias.z, bias.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float lo, hi;
+    if (BF16) {
+      lo = __uint_as_float(w[i] << 16);
+      hi = __uint_as_float(w[i] & 0xffff0000u);
+    } else {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+      lo = f.x;
+      hi = f.y;
+    }
+    sv[2 * i] = __float_as_uint(fmaf(__uint_as_float(sv[2 * i]), sl2_in, lo * kLog2e));
+    sv[2 * i + 1] = __float_as_uint(fmaf(__uint_as_float(sv[2 * i + 1]), sl2_in, hi * kLog2e));
+  }
+}
+
+template <int D, bool BF16, bool BIAS>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o, const Problem p,
@@ -457,14 +478,34 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       const long long c = static_cast<long long>(row_g) + p.causal_shift + 1;
       lim = c < lim ? static_cast<int>(c < 0 ? 0 : c) : lim;
     }
-    const float sl2 = p.scale * kLog2e;
+    // With an additive bias the logits are brought to log2 units when they are read
+    // (s * scale * log2 e + bias * log2 e); everything after that then works with scale 1.
+    const float sl2_in = p.scale * kLog2e;
+    const float sl2 = BIAS ? 1.f : sl2_in;
     float m_run = -CUDART_INF_F, l_run = 0.f;
     bool alive = true;
+    // this row of the bias, 16-bit elements in the query's dtype, unit stride along the keys
+    const uint4* bias_row = nullptr;
+    if constexpr (BIAS) {
+      if (row_g < p.L)
+        bias_row = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.bias) + b * p.bs[0] +
+                                                  static_cast<long long>(head_of_tile[t]) * p.bs[1] +
+                                                  static_cast<long long>(row_g) * p.bs[2]);
+    }
 
     PHASE_DECL;
     if (tg.in_range) {
       for (int j = 0; j < tg.n_tiles; ++j) {
         PHASE_ADD(8 + (j == 0 ? 0 : 1), r == 0);   // 8: prologue until the first wait, 9: arrive -> next wait
+        uint4 bv[BIAS ? kBlockN / 8 : 1];
+        if constexpr (BIAS) {
+          // the bias of this key tile travels while the scores are awaited (S is a multiple of 8)
+#pragma unroll
+          for (int i = 0; i < kBlockN / 8; ++i) {
+            const int c = j * kBlockN + 8 * i;
+            bv[i] = (bias_row != nullptr && c < p.S) ? __ldg(bias_row + (c >> 3)) : make_uint4(0u, 0u, 0u, 0u);
+          }
+        }
         bool ok = wait_clocked(smem_u32(&sync->s_full[t]), j & 1, abort_flag, wait_limit);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) {
@@ -489,6 +530,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         tmem_ld_32x32(s_addr + 64, reinterpret_cast<uint32_t(&)[32]>(sv[64]));
         tmem_ld_32x32(s_addr + 96, reinterpret_cast<uint32_t(&)[32]>(sv[96]));
         float mxa = -CUDART_INF_F, mxb = -CUDART_INF_F;
+        if constexpr (BIAS) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) add_bias8<BF16>(&sv[8 * i], bv[i], sl2_in);
+        }
         if (need_mask) {
 #pragma unroll
           for (int i = 0; i < 64; ++i) sv[i] = (col0 + i < lim) ? sv[i] : 0xff800000u;  // -inf
@@ -504,6 +549,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           mbar_arrive(smem_u32(&sync->s_free[t]));
         }
         PHASE_ADD(1, r == 0);                       // 1: S TMEM -> registers (+ first half max)
+        if constexpr (BIAS) {
+#pragma unroll
+          for (int i = 8; i < 16; ++i) add_bias8<BF16>(&sv[8 * i], bv[i], sl2_in);
+        }
         if (need_mask) {
 #pragma unroll
           for (int i = 64; i < kBlockN; ++i) sv[i] = (col0 + i < lim) ? sv[i] : 0xff800000u;
@@ -522,19 +571,20 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           l_run *= alpha;
           m_run = m_new;
         }
-        if (j > 0 && __any_sync(0xffffffffu, grow)) {
-          if (C::kSplitP) {
-            // here S(j) can be ready before P V of the previous tile has retired: wait for it
-            bool pv_ok = wait_clocked(smem_u32(&sync->pv_done[t]), (j - 1) & 1, abort_flag, wait_limit);
-            pv_ok = __all_sync(0xffffffffu, pv_ok);
-            if (!pv_ok) {
-              if (lane == 0) report(p.status, 10, j, t);
-              alive = false;
-              break;
-            }
-            tc_fence_after_sync();
+        if (C::kSplitP && j > 0) {
+          // here S(j) can be ready before P V of the previous tile has retired, and that product
+          // still reads the P columns and writes O_t: wait for it before touching either
+          bool pv_ok = wait_clocked(smem_u32(&sync->pv_done[t]), (j - 1) & 1, abort_flag, wait_limit);
+          pv_ok = __all_sync(0xffffffffu, pv_ok);
+          if (!pv_ok) {
+            if (lane == 0) report(p.status, 10, j, t);
+            alive = false;
+            break;
           }
-          // raise the reference maximum: O_t *= alpha (PV(j-1) has retired: its
+          tc_fence_after_sync();
+        }
+        if (j > 0 && __any_sync(0xffffffffu, grow)) {
+          // raise the reference maximum: O_t *= alpha (PV(j-1) has retired: without the split its
           // completion is ordered before s_full(j))
 #pragma unroll
           for (int c = 0; c < D / 16; ++c) {
@@ -647,7 +697,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         PHASE_ADD(10, r == 0);                      // 10: epilogue (wait O, scale, stage, store)
         if (p.lse != nullptr && row_g < p.L) {
           // one rounding at the magnitude of the maximum: m*scale + ln(l)
-          const float lse = l_run > 0.f ? fmaf(m_run, p.scale, lg2(l_run) * kLn2) : -CUDART_INF_F;
+          const float lse = l_run > 0.f ? fmaf(m_run, BIAS ? kLn2 : p.scale, lg2(l_run) * kLn2) : -CUDART_INF_F;
           p.lse[b * p.ls[0] + head_of_tile[t] * p.ls[1] + row_g * p.ls[2]] = lse;
         }
       }
@@ -670,14 +720,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 // mask is causal (that is where the row-block layout leaves one tile idle at the end).
 int pair_heads_mode(const Problem& p) { return (p.causal && p.group % 2 == 0) ? 1 : 0; }
 
-template <int D, bool BF16>
+template <int D, bool BF16, bool BIAS>
 int launch_variant(const Problem& p, cudaStream_t stream) {
   using C = Cfg<D>;
   CUtensorMap tq, tk, tv, to;
   if (!make_map(&tq, p.q, BF16, D, p.L, p.Hq, p.B, p.qs) || !make_map(&tk, p.k, BF16, D, p.S, p.Hkv, p.B, p.ks) ||
       !make_map(&tv, p.v, BF16, D, p.S, p.Hkv, p.B, p.vs) || !make_map(&to, p.out, BF16, D, p.L, p.Hq, p.B, p.os))
     return B200_SDPA_ERR_CUDA;
-  auto kern = prefill_kernel<D, BF16>;
+  auto kern = prefill_kernel<D, BF16, BIAS>;
   static std::once_flag once;
   static cudaError_t attr_rc = cudaSuccess;
   std::call_once(once, [&] {
@@ -731,9 +781,17 @@ bool prefill_eligible(const Problem& p, int dtype, bool* alignment_only_failure)
   if (alignment_only_failure) *alignment_only_failure = false;
   if (dtype != B200_SDPA_F16 && dtype != B200_SDPA_BF16) return false;
   if (p.E != p.Dv || (p.E != 64 && p.E != 128)) return false;
-  if (p.bias != nullptr) return false;
   if (!(p.scale > 0.f) || !(p.scale < 1e30f)) return false;
   if (p.L < 1 || p.S < 1) return false;
+  if (p.bias != nullptr) {
+    // read by the softmax threads as 16-byte pieces of their row: the query's dtype, unit stride along
+    // the keys, every row start on a 16-byte boundary (broadcast dimensions have stride 0)
+    if (p.bias_dtype != dtype || p.bs[3] != 1 || p.S % 8 != 0) return false;
+    if (reinterpret_cast<uintptr_t>(p.bias) % 16 != 0 || p.bs[0] % 8 != 0 || p.bs[1] % 8 != 0 || p.bs[2] % 8 != 0) {
+      if (alignment_only_failure) *alignment_only_failure = true;
+      return false;
+    }
+  }
   const bool ok = strides_ok(p.q, p.qs, p.L, p.Hq, p.B) && strides_ok(p.k, p.ks, p.S, p.Hkv, p.B) &&
                   strides_ok(p.v, p.vs, p.S, p.Hkv, p.B) && strides_ok(p.out, p.os, p.L, p.Hq, p.B);
   if (!ok && alignment_only_failure) *alignment_only_failure = true;
@@ -765,8 +823,12 @@ int launch_prefill(const Problem& p, int dtype, cudaStream_t stream) {
   if (p.E > 128) return launch_prefill_wide(p, dtype, stream);
   if (!prefill_eligible(p, dtype, nullptr)) return B200_SDPA_ERR_UNSUPPORTED;
   const bool bf16 = dtype == B200_SDPA_BF16;
-  if (p.E == 128) return bf16 ? launch_variant<128, true>(p, stream) : launch_variant<128, false>(p, stream);
-  return bf16 ? launch_variant<64, true>(p, stream) : launch_variant<64, false>(p, stream);
+  if (p.bias != nullptr) {
+    if (p.E == 128) return bf16 ? launch_variant<128, true, true>(p, stream) : launch_variant<128, false, true>(p, stream);
+    return bf16 ? launch_variant<64, true, true>(p, stream) : launch_variant<64, false, true>(p, stream);
+  }
+  if (p.E == 128) return bf16 ? launch_variant<128, true, false>(p, stream) : launch_variant<128, false, false>(p, stream);
+  return bf16 ? launch_variant<64, true, false>(p, stream) : launch_variant<64, false, false>(p, stream);
 }
 
 }  // namespace b200
