@@ -332,8 +332,9 @@ int b200_sdpa_decode_static(const B200SdpaParams* params, void* stream);
  * Kernel family, launch geometry (grid_x: grad_q kernel, grid_y: grad_k/grad_v kernel)
  * and scratch size of a backward request, without launching.  Host-only.
  * `path` is B200_SDPA_PATH_PREFILL for the tcgen05 kernels (f16/bf16, E == Dv in
- * {64,128}, no bias, unit inner strides, 16-byte aligned bases and outer strides of
- * q, k, v, grad_out and the three gradients) and B200_SDPA_PATH_GENERIC otherwise.
+ * {64,128}, no grad_bias, a bias only under the forward's rules for that path, unit
+ * inner strides, 16-byte aligned bases and outer strides of q, k, v, grad_out and the
+ * three gradients) and B200_SDPA_PATH_GENERIC otherwise.
  */
 int b200_sdpa_bwd_query_plan(const B200SdpaBwdParams* params, B200SdpaPlan* plan);
 

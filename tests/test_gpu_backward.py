@@ -431,3 +431,41 @@ def test_tensor_core_backward_is_deterministic():
     b = _cuda_backward(go, q, k, v, is_causal=True, force_path=_lib.PATH_PREFILL, out=_cuda_backward.forward[0],
                        lse=_cuda_backward.forward[1])
     assert all(torch.equal(x, y) for x, y in zip(a[:3], b[:3]))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("kind", ["full", "query_key", "batch_key", "head"])
+@pytest.mark.parametrize("shape", [(2, 4, 2, 300, 304, 128), (1, 8, 8, 520, 1024, 64), (2, 6, 3, 129, 136, 128)])
+def test_tensor_core_backward_with_additive_bias(shape, kind, dtype):
+    """The forward's additive bias (query dtype, unit stride along the keys) is re-read by both
+    tcgen05 backward kernels: row-wise by the grad_q kernel, column-wise (lanes = keys) by the
+    grad_k / grad_v kernel; -inf entries and a dead row included."""
+    from torch_neuronx_b200 import _lib
+
+    B, Hq, Hkv, L, S, D = shape
+    g = torch.Generator().manual_seed(L * 5 + S + D)
+    q = torch.randn(B, Hq, L, D, generator=g).to(dtype)
+    k = torch.randn(B, Hkv, S, D, generator=g).to(dtype)
+    v = torch.randn(B, Hkv, S, D, generator=g).to(dtype)
+    go = torch.randn(B, Hq, L, D, generator=g).to(dtype)
+    bshape = {"full": (B, Hq, L, S), "query_key": (L, S), "batch_key": (B, 1, 1, S), "head": (1, Hq, L, S)}[kind]
+    bias = (torch.randn(bshape, generator=g) * 2).to(dtype)
+    bias = bias.masked_fill(torch.rand(bshape, generator=g) < 0.1, float("-inf"))
+    if kind == "full":
+        bias[0, 0, min(5, L - 1)] = float("-inf")
+    got = _cuda_backward(go, q, k, v, mask=bias)
+    assert _cuda_backward.path == "prefill"
+    fwd = _cuda_backward.forward
+    want = _oracle_backward(go, q, k, v, forward=fwd, attn_mask=bias)
+    ref = _cuda_backward(go, q, k, v, mask=bias, force_path=_lib.PATH_GENERIC, out=fwd[0], lse=fwd[1])
+    assert _cuda_backward.path == "generic"
+    for a, b, c, n in zip(got[:3], want[:3], ref[:3], ("dq", "dk", "dv")):
+        _close(a, b, dtype, f"tc bias {kind} {shape} {n}", dict(rtol=5e-2, atol=2e-2))
+        err = (a.float() - b.float()).abs().mean().item()
+        assert err <= 2e-3 * max(1.0, b.float().abs().mean().item() * 10), f"{n}: mean-abs {err:.3e}"
+        _close(a, c, dtype, f"tc bias vs cuda-core {kind} {shape} {n}", dict(rtol=5e-2, atol=2e-2))
+    if kind == "full":
+        assert torch.all(got[0][0, 0, min(5, L - 1)] == 0)
+    # the logit gradient is written by the CUDA-core kernels only
+    _cuda_backward(go, q, k, v, mask=bias, need_grad_bias=True)
+    assert _cuda_backward.path == "generic"

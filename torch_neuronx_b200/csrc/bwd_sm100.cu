@@ -258,7 +258,14 @@ struct ASync {
   int abort_flag;
 };
 
-template <int D, bool BF16>
+// One 16-bit bias element (the query's dtype) as fp32.
+template <bool BF16>
+__device__ __forceinline__ float bias_to_f32(const uint32_t bits16) {
+  if (BF16) return __uint_as_float(bits16 << 16);
+  return __half2float(__ushort_as_half(static_cast<unsigned short>(bits16)));
+}
+
+template <int D, bool BF16, bool BIAS>
 __global__ void __launch_bounds__(kThreads, 1)
 bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
@@ -487,8 +494,28 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const float dl = delta[stat_idx];
     const float sl2 = p.scale * kLog2e;
     bool alive = true;
+    // this row of the forward's additive bias (the query's dtype, unit stride along the keys)
+    const uint4* bias_row = nullptr;
+    if constexpr (BIAS) {
+      if (row_g < p.L)
+        bias_row = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.bias) + b * p.bs[0] +
+                                                  static_cast<long long>(h) * p.bs[1] +
+                                                  static_cast<long long>(row_g) * p.bs[2]);
+    }
     for (int j = 0; j < n_tiles; ++j) {
       const int buf = j & 1;
+      uint32_t bw[BIAS ? 32 : 1];   // this thread's 64 bias elements of the tile, fetched under the wait
+      if constexpr (BIAS) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int c = j * kT + half * 64 + 8 * i;
+          const uint4 w = (bias_row != nullptr && c < p.S) ? __ldg(bias_row + (c >> 3)) : make_uint4(0u, 0u, 0u, 0u);
+          bw[4 * i] = w.x;
+          bw[4 * i + 1] = w.y;
+          bw[4 * i + 2] = w.z;
+          bw[4 * i + 3] = w.w;
+        }
+      }
       bool ok = wait_clocked(smem_u32(&sync->sp_full), j & 1, abort_flag, wait_limit);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
@@ -515,8 +542,13 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       uint32_t pk[32];
 #pragma unroll
       for (int i = 0; i < 64; i += 2) {
-        float p0 = ex2(fmaf(__uint_as_float(sv[i]), sl2, neg_l2));
-        float p1 = ex2(fmaf(__uint_as_float(sv[i + 1]), sl2, neg_l2));
+        float off0 = neg_l2, off1 = neg_l2;
+        if constexpr (BIAS) {
+          off0 = fmaf(bias_to_f32<BF16>(bw[i >> 1] & 0xffffu), kLog2e, neg_l2);
+          off1 = fmaf(bias_to_f32<BF16>(bw[i >> 1] >> 16), kLog2e, neg_l2);
+        }
+        float p0 = ex2(fmaf(__uint_as_float(sv[i]), sl2, off0));
+        float p1 = ex2(fmaf(__uint_as_float(sv[i + 1]), sl2, off1));
         if (need_mask) {
           p0 = (col0 + i < lim) ? p0 : 0.f;
           p1 = (col0 + i + 1 < lim) ? p1 : 0.f;
@@ -579,7 +611,7 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
 // --------------------------------------------------------------- dK/dV kernel --
 
-template <int D, bool BF16>
+template <int D, bool BF16, bool BIAS>
 __global__ void __launch_bounds__(kThreads, 1)
 bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                   const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
@@ -758,6 +790,17 @@ bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     bool alive = true;
     for (int u = 0; u < n_units; ++u) {
       const int it = u >> 1, hh = u & 1, buf = u & 1;
+      const int unit_row0 = (i_first + it % per_head) * kT + hh * kU;   // first query row of the unit
+      const int qrow0 = unit_row0 + half * 32;                          // ... and of this thread's columns
+      uint32_t bq[BIAS ? 32 : 1];   // bias of this key under the thread's 32 query rows, fetched under the wait
+      if constexpr (BIAS) {
+        // neighbouring lanes are neighbouring keys: each of the 32 loads is one 64-byte piece per warp
+        const uint16_t* col = static_cast<const uint16_t*>(p.bias) + b * p.bs[0] +
+                              static_cast<long long>(hk * p.group + it / per_head) * p.bs[1] + key_g;
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          bq[i] = (key_g < p.S && qrow0 + i < p.L) ? __ldg(col + static_cast<long long>(qrow0 + i) * p.bs[2]) : 0u;
+      }
       bool ok = wait_clocked(smem_u32(&sync->sp_full[buf]), (u >> 1) & 1, abort_flag, wait_limit);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
@@ -767,8 +810,6 @@ bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       }
       tc_fence_after_sync();
       const int stage = it % C::kStages;
-      const int unit_row0 = (i_first + it % per_head) * kT + hh * kU;   // first query row of the unit
-      const int qrow0 = unit_row0 + half * 32;                          // ... and of this thread's columns
       const float4* st4 = reinterpret_cast<const float4*>(stats + stage * 2 * kT) + hh * 16 + half * 8;
       // some key of this tile hides some row of this unit
       const bool need_mask = tile_has_padding ||
@@ -788,7 +829,9 @@ bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int i = q4 * 4 + e;
-          float pe = ex2(fmaf(__uint_as_float(sv[i]), sl2, -ls[e]));
+          float off = -ls[e];
+          if constexpr (BIAS) off = fmaf(bias_to_f32<BF16>(bq[i]), kLog2e, off);
+          float pe = ex2(fmaf(__uint_as_float(sv[i]), sl2, off));
           if (need_mask) pe = (qrow0 + i >= i_min) ? pe : 0.f;
           pr[e] = pe;
           dsv[e] = pe * (__uint_as_float(dv[i]) - ds_[e]);
@@ -844,7 +887,7 @@ bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
 int padded_rows(const Problem& p) { return (p.L + kT - 1) / kT * kT; }
 
-template <int D, bool BF16>
+template <int D, bool BF16, bool BIAS>
 int launch_tc(const BwdProblem& bp, float* lse2, float* delta, cudaStream_t stream) {
   using C = BCfg<D>;
   const Problem& p = bp.f;
@@ -855,8 +898,8 @@ int launch_tc(const BwdProblem& bp, float* lse2, float* delta, cudaStream_t stre
       !make_map(&tdk, bp.dk, BF16, D, p.S, p.Hkv, p.B, bp.dks) ||
       !make_map(&tdv, bp.dv, BF16, D, p.S, p.Hkv, p.B, bp.dvs))
     return B200_SDPA_ERR_CUDA;
-  auto kq = bwd_dq_tc_kernel<D, BF16>;
-  auto kkv = bwd_dkv_tc_kernel<D, BF16>;
+  auto kq = bwd_dq_tc_kernel<D, BF16, BIAS>;
+  auto kkv = bwd_dkv_tc_kernel<D, BF16, BIAS>;
   if (cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, ACfg<D>::kSmemBytes) != cudaSuccess ||
       cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess) {
     cudaGetLastError();
@@ -919,9 +962,17 @@ bool bwd_tc_eligible(const BwdProblem& bp, int dtype, bool* alignment_only_failu
   if (alignment_only_failure) *alignment_only_failure = false;
   if (dtype != B200_SDPA_F16 && dtype != B200_SDPA_BF16) return false;
   if (p.E != p.Dv || (p.E != 64 && p.E != 128)) return false;
-  if (p.bias != nullptr || bp.dbias != nullptr) return false;
+  if (bp.dbias != nullptr) return false;   // the logit gradient is written by the CUDA-core kernels only
   if (!(p.scale > 0.f) || !(p.scale < 1e30f)) return false;
   if (p.L < 1 || p.S < 1) return false;
+  if (p.bias != nullptr) {
+    // as in the forward: the query's dtype, unit stride along the keys, rows on the 16-byte grid
+    if (p.bias_dtype != dtype || p.bs[3] != 1 || p.S % 8 != 0) return false;
+    if (reinterpret_cast<uintptr_t>(p.bias) % 16 != 0 || p.bs[0] % 8 != 0 || p.bs[1] % 8 != 0 || p.bs[2] % 8 != 0) {
+      if (alignment_only_failure) *alignment_only_failure = true;
+      return false;
+    }
+  }
   const bool ok = strides_ok(p.q, p.qs, p.L, p.Hq, p.B) && strides_ok(p.k, p.ks, p.S, p.Hkv, p.B) &&
                   strides_ok(p.v, p.vs, p.S, p.Hkv, p.B) && strides_ok(bp.dout, bp.dos, p.L, p.Hq, p.B) &&
                   strides_ok(bp.dq, bp.dqs, p.L, p.Hq, p.B) && strides_ok(bp.dk, bp.dks, p.S, p.Hkv, p.B) &&
@@ -959,8 +1010,14 @@ int launch_bwd_tc(const BwdProblem& bp, int dtype, void* workspace, uint64_t wor
   float* lse2 = reinterpret_cast<float*>(workspace);
   float* delta = lse2 + need / (2 * sizeof(float));
   const bool bf16 = dtype == B200_SDPA_BF16;
-  if (bp.f.E == 128) return bf16 ? launch_tc<128, true>(bp, lse2, delta, stream) : launch_tc<128, false>(bp, lse2, delta, stream);
-  return bf16 ? launch_tc<64, true>(bp, lse2, delta, stream) : launch_tc<64, false>(bp, lse2, delta, stream);
+  if (bp.f.bias != nullptr) {
+    if (bp.f.E == 128)
+      return bf16 ? launch_tc<128, true, true>(bp, lse2, delta, stream) : launch_tc<128, false, true>(bp, lse2, delta, stream);
+    return bf16 ? launch_tc<64, true, true>(bp, lse2, delta, stream) : launch_tc<64, false, true>(bp, lse2, delta, stream);
+  }
+  if (bp.f.E == 128)
+    return bf16 ? launch_tc<128, true, false>(bp, lse2, delta, stream) : launch_tc<128, false, false>(bp, lse2, delta, stream);
+  return bf16 ? launch_tc<64, true, false>(bp, lse2, delta, stream) : launch_tc<64, false, false>(bp, lse2, delta, stream);
 }
 
 }  // namespace b200
