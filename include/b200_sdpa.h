@@ -64,8 +64,8 @@ typedef enum b200_sdpa_path {
                                   any strides, additive bias, head dim <= 512        */
   B200_SDPA_PATH_PREFILL = 2,  /* TMA + tcgen05/TMEM warp-specialised kernels:
                                   f16/bf16, E == Dv in {64,128,256} or E = 192
-                                  with Dv = 128, unit inner stride; at 64 and 128
-                                  also an additive bias of the same dtype with unit
+                                  with Dv = 128, unit inner stride; also with an
+                                  additive bias of the same dtype that has unit
                                   stride along the keys, S % 8 == 0 and 16-byte
                                   aligned rows                                       */
   B200_SDPA_PATH_DECODE = 3    /* split-KV flash-decoding kernel + combine, L == 1  */

@@ -301,4 +301,4 @@ def test_bias_planning():
     rc, plan = plan_with([8 * L * S, L * S, S, 1], bias=fake_bias + 2)
     assert rc == 0 and plan.path == _lib.PATH_GENERIC
     rc, plan = plan_with([8 * L * S, L * S, S, 1], E=192, Dv=128)
-    assert rc == 0 and plan.path == _lib.PATH_GENERIC       # the wide kernel takes no bias
+    assert rc == 0 and plan.path == _lib.PATH_PREFILL       # the wide kernel reads it the same way

@@ -264,7 +264,8 @@ def _make_bias(kind, B, Hq, L, S, dtype, g):
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("kind", ["full", "query_key", "batch_key", "head"])
-@pytest.mark.parametrize("shape", [(2, 4, 2, 300, 304, 128), (1, 8, 8, 520, 1024, 64), (2, 6, 3, 129, 136, 128)])
+@pytest.mark.parametrize("shape", [(2, 4, 2, 300, 304, 128), (1, 8, 8, 520, 1024, 64), (2, 6, 3, 129, 136, 128),
+                                   (1, 4, 2, 300, 520, (192, 128)), (1, 2, 2, 260, 264, 256)])
 def test_additive_bias_runs_on_tensor_cores(shape, kind, dtype):
     """An additive bias in the query's dtype (what the SDPA front end makes of every mask it does not
     recognise) is read by the softmax threads of the tcgen05 kernel: full, broadcast over batch and
@@ -272,10 +273,11 @@ def test_additive_bias_runs_on_tensor_cores(shape, kind, dtype):
     import torch_neuronx_b200 as T
 
     B, Hq, Hkv, L, S, D = shape
-    g = torch.Generator().manual_seed(L * 7 + S + D)
-    q = torch.randn(B, Hq, L, D, generator=g).to(dtype)
-    k = torch.randn(B, Hkv, S, D, generator=g).to(dtype)
-    v = torch.randn(B, Hkv, S, D, generator=g).to(dtype)
+    E, Dv = D if isinstance(D, tuple) else (D, D)
+    g = torch.Generator().manual_seed(L * 7 + S + E)
+    q = torch.randn(B, Hq, L, E, generator=g).to(dtype)
+    k = torch.randn(B, Hkv, S, E, generator=g).to(dtype)
+    v = torch.randn(B, Hkv, S, Dv, generator=g).to(dtype)
     bias = _make_bias(kind, B, Hq, L, S, dtype, g)
     out, lse = run_cuda(q, k, v, attn_bias=bias)
     assert T.ops.last_plan["path"] == "prefill"

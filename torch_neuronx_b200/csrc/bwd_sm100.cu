@@ -966,12 +966,7 @@ bool bwd_tc_eligible(const BwdProblem& bp, int dtype, bool* alignment_only_failu
   if (!(p.scale > 0.f) || !(p.scale < 1e30f)) return false;
   if (p.L < 1 || p.S < 1) return false;
   if (p.bias != nullptr) {
-    // as in the forward: the query's dtype, unit stride along the keys, rows on the 16-byte grid
-    if (p.bias_dtype != dtype || p.bs[3] != 1 || p.S % 8 != 0) return false;
-    if (reinterpret_cast<uintptr_t>(p.bias) % 16 != 0 || p.bs[0] % 8 != 0 || p.bs[1] % 8 != 0 || p.bs[2] % 8 != 0) {
-      if (alignment_only_failure) *alignment_only_failure = true;
-      return false;
-    }
+    if (!bias_readable(p, dtype, alignment_only_failure)) return false;   // as in the forward
   }
   const bool ok = strides_ok(p.q, p.qs, p.L, p.Hq, p.B) && strides_ok(p.k, p.ks, p.S, p.Hkv, p.B) &&
                   strides_ok(p.v, p.vs, p.S, p.Hkv, p.B) && strides_ok(bp.dout, bp.dos, p.L, p.Hq, p.B) &&

@@ -136,27 +136,6 @@ __device__ __forceinline__ TileGeom tile_geometry(const Problem& p, int row0, in
   return g;
 }
 
-// Eight logits in log2 units: s * (scale * log2 e) + bias * log2 e, the bias as eight 16-bit
-// elements of the query's dtype.
-template <bool BF16>
-__device__ __forceinline__ void add_bias8(uint32_t* sv, const uint4 bias, const float sl2_in) {
-  const uint32_t w[4] = {bias.x, bias.y, bias.z, bias.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float lo, hi;
-    if (BF16) {
-      lo = __uint_as_float(w[i] << 16);
-      hi = __uint_as_float(w[i] & 0xffff0000u);
-    } else {
-      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
-      lo = f.x;
-      hi = f.y;
-    }
-    sv[2 * i] = __float_as_uint(fmaf(__uint_as_float(sv[2 * i]), sl2_in, lo * kLog2e));
-    sv[2 * i + 1] = __float_as_uint(fmaf(__uint_as_float(sv[2 * i + 1]), sl2_in, hi * kLog2e));
-  }
-}
-
 template <int D, bool BF16, bool BIAS>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -784,13 +763,7 @@ bool prefill_eligible(const Problem& p, int dtype, bool* alignment_only_failure)
   if (!(p.scale > 0.f) || !(p.scale < 1e30f)) return false;
   if (p.L < 1 || p.S < 1) return false;
   if (p.bias != nullptr) {
-    // read by the softmax threads as 16-byte pieces of their row: the query's dtype, unit stride along
-    // the keys, every row start on a 16-byte boundary (broadcast dimensions have stride 0)
-    if (p.bias_dtype != dtype || p.bs[3] != 1 || p.S % 8 != 0) return false;
-    if (reinterpret_cast<uintptr_t>(p.bias) % 16 != 0 || p.bs[0] % 8 != 0 || p.bs[1] % 8 != 0 || p.bs[2] % 8 != 0) {
-      if (alignment_only_failure) *alignment_only_failure = true;
-      return false;
-    }
+    if (!bias_readable(p, dtype, alignment_only_failure)) return false;
   }
   const bool ok = strides_ok(p.q, p.qs, p.L, p.Hq, p.B) && strides_ok(p.k, p.ks, p.S, p.Hkv, p.B) &&
                   strides_ok(p.v, p.vs, p.S, p.Hkv, p.B) && strides_ok(p.out, p.os, p.L, p.Hq, p.B);

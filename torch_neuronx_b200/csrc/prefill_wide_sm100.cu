@@ -50,7 +50,7 @@ struct SyncW {
   int abort_flag;
 };
 
-template <int E, int DV, bool BF16>
+template <int E, int DV, bool BF16, bool BIAS>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o, const Problem p,
@@ -268,12 +268,29 @@ prefill_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       const long long c = static_cast<long long>(row_g) + p.causal_shift + 1;
       lim = c < lim ? static_cast<int>(c < 0 ? 0 : c) : lim;
     }
-    const float sl2 = p.scale * kLog2e;
+    // with an additive bias the logits are brought to log2 units as they are read (see prefill_sm100.cu)
+    const float sl2_in = p.scale * kLog2e;
+    const float sl2 = BIAS ? 1.f : sl2_in;
     float m_run = -CUDART_INF_F, l_run = 0.f;
     bool alive = true;
+    const uint4* bias_row = nullptr;
+    if constexpr (BIAS) {
+      if (row_g < p.L)
+        bias_row = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.bias) + b * p.bs[0] +
+                                                  static_cast<long long>(h) * p.bs[1] +
+                                                  static_cast<long long>(row_g) * p.bs[2]);
+    }
 
     for (int j = 0; j < n_tiles; ++j) {
       const uint32_t s_addr = s_base + static_cast<uint32_t>((j & 1) * kN);
+      uint4 bv[BIAS ? kN / 8 : 1];
+      if constexpr (BIAS) {
+#pragma unroll
+        for (int i = 0; i < kN / 8; ++i) {
+          const int c = j * kN + 8 * i;
+          bv[i] = (bias_row != nullptr && c < p.S) ? __ldg(bias_row + (c >> 3)) : make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
       bool ok = wait_clocked(smem_u32(&sync->s_full[j & 1]), static_cast<uint32_t>(j >> 1) & 1u, abort_flag, wait_limit);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
@@ -292,6 +309,10 @@ prefill_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       tmem_ld_32x32(s_addr + 64, reinterpret_cast<uint32_t(&)[32]>(sv[64]));
       tmem_ld_32x32(s_addr + 96, reinterpret_cast<uint32_t(&)[32]>(sv[96]));
       float mxa = -CUDART_INF_F, mxb = -CUDART_INF_F;
+      if constexpr (BIAS) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) add_bias8<BF16>(&sv[8 * i], bv[i], sl2_in);
+      }
       if (need_mask) {
 #pragma unroll
         for (int i = 0; i < 64; ++i) sv[i] = (col0 + i < lim) ? sv[i] : 0xff800000u;   // -inf
@@ -302,6 +323,10 @@ prefill_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         mxb = max3(mxb, __uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3]));
       }
       tmem_ld_wait();
+      if constexpr (BIAS) {
+#pragma unroll
+        for (int i = 8; i < 16; ++i) add_bias8<BF16>(&sv[8 * i], bv[i], sl2_in);
+      }
       if (need_mask) {
 #pragma unroll
         for (int i = 64; i < kN; ++i) sv[i] = (col0 + i < lim) ? sv[i] : 0xff800000u;
@@ -413,7 +438,7 @@ prefill_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         tma_store_wait_read();
       }
       if (p.lse != nullptr && row_g < p.L) {
-        const float lse = l_run > 0.f ? fmaf(m_run, p.scale, lg2(l_run) * kLn2) : -CUDART_INF_F;
+        const float lse = l_run > 0.f ? fmaf(m_run, BIAS ? kLn2 : p.scale, lg2(l_run) * kLn2) : -CUDART_INF_F;
         p.lse[b * p.ls[0] + h * p.ls[1] + row_g * p.ls[2]] = lse;
       }
     }
@@ -427,14 +452,14 @@ prefill_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   }
 }
 
-template <int E, int DV, bool BF16>
+template <int E, int DV, bool BF16, bool BIAS>
 int launch_wide(const Problem& p, cudaStream_t stream) {
   using C = CfgW<E, DV>;
   CUtensorMap tq, tk, tv, to;
   if (!make_map(&tq, p.q, BF16, E, p.L, p.Hq, p.B, p.qs) || !make_map(&tk, p.k, BF16, E, p.S, p.Hkv, p.B, p.ks) ||
       !make_map(&tv, p.v, BF16, DV, p.S, p.Hkv, p.B, p.vs) || !make_map(&to, p.out, BF16, DV, p.L, p.Hq, p.B, p.os))
     return B200_SDPA_ERR_CUDA;
-  auto kern = prefill_wide_kernel<E, DV, BF16>;
+  auto kern = prefill_wide_kernel<E, DV, BF16, BIAS>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess) {
     cudaGetLastError();
     return B200_SDPA_ERR_CUDA;
@@ -456,7 +481,8 @@ bool prefill_wide_eligible(const Problem& p, int dtype, bool* alignment_only_fai
   if (alignment_only_failure) *alignment_only_failure = false;
   if (dtype != B200_SDPA_F16 && dtype != B200_SDPA_BF16) return false;
   if (!((p.E == 192 && p.Dv == 128) || (p.E == 256 && p.Dv == 256))) return false;
-  if (p.bias != nullptr || p.block_table != nullptr || p.k_new != nullptr) return false;
+  if (p.block_table != nullptr || p.k_new != nullptr) return false;
+  if (p.bias != nullptr && !bias_readable(p, dtype, alignment_only_failure)) return false;
   if (!(p.scale > 0.f) || !(p.scale < 1e30f)) return false;
   if (p.L < 1 || p.S < 1) return false;
   const bool ok = strides_ok(p.q, p.qs, p.L, p.Hq, p.B) && strides_ok(p.k, p.ks, p.S, p.Hkv, p.B) &&
@@ -485,8 +511,12 @@ int plan_prefill_wide(const Problem& p, int dtype, B200SdpaPlan* plan) {
 int launch_prefill_wide(const Problem& p, int dtype, cudaStream_t stream) {
   if (!prefill_wide_eligible(p, dtype, nullptr)) return B200_SDPA_ERR_UNSUPPORTED;
   const bool bf16 = dtype == B200_SDPA_BF16;
-  if (p.E == 192) return bf16 ? launch_wide<192, 128, true>(p, stream) : launch_wide<192, 128, false>(p, stream);
-  return bf16 ? launch_wide<256, 256, true>(p, stream) : launch_wide<256, 256, false>(p, stream);
+  if (p.bias != nullptr) {
+    if (p.E == 192) return bf16 ? launch_wide<192, 128, true, true>(p, stream) : launch_wide<192, 128, false, true>(p, stream);
+    return bf16 ? launch_wide<256, 256, true, true>(p, stream) : launch_wide<256, 256, false, true>(p, stream);
+  }
+  if (p.E == 192) return bf16 ? launch_wide<192, 128, true, false>(p, stream) : launch_wide<192, 128, false, false>(p, stream);
+  return bf16 ? launch_wide<256, 256, true, false>(p, stream) : launch_wide<256, 256, false, false>(p, stream);
 }
 
 }  // namespace b200

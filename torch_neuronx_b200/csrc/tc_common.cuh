@@ -139,6 +139,39 @@ inline bool strides_ok(const void* base, const int64_t* s, int rows, int heads, 
   return true;
 }
 
+// Eight logits in log2 units: s * (scale * log2 e) + bias * log2 e, the bias as eight 16-bit
+// elements of the query's dtype.
+template <bool BF16>
+__device__ __forceinline__ void add_bias8(uint32_t* sv, const uint4 bias, const float sl2_in) {
+  const uint32_t w[4] = {bias.x, bias.y, bias.z, bias.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float lo, hi;
+    if (BF16) {
+      lo = __uint_as_float(w[i] << 16);
+      hi = __uint_as_float(w[i] & 0xffff0000u);
+    } else {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+      lo = f.x;
+      hi = f.y;
+    }
+    sv[2 * i] = __float_as_uint(fmaf(__uint_as_float(sv[2 * i]), sl2_in, lo * kLog2e));
+    sv[2 * i + 1] = __float_as_uint(fmaf(__uint_as_float(sv[2 * i + 1]), sl2_in, hi * kLog2e));
+  }
+}
+
+// An additive bias the tensor-core kernels can read as 16-byte pieces of a row: the query's dtype,
+// unit stride along the keys, a key count that is a multiple of 8, every row start on a 16-byte
+// boundary (broadcast dimensions have stride 0).
+inline bool bias_readable(const Problem& p, int dtype, bool* alignment_only_failure) {
+  if (p.bias_dtype != dtype || p.bs[3] != 1 || p.S % 8 != 0) return false;
+  if (reinterpret_cast<uintptr_t>(p.bias) % 16 != 0 || p.bs[0] % 8 != 0 || p.bs[1] % 8 != 0 || p.bs[2] % 8 != 0) {
+    if (alignment_only_failure) *alignment_only_failure = true;
+    return false;
+  }
+  return true;
+}
+
 // Key/value bytes that the CTAs of one wave of (batch, kv head) streams read together: about a quarter
 // of the 126 MB L2, so that a wave's streams stay resident while its query blocks sweep over them.
 #ifndef B200_WAVE_BYTES
