@@ -502,20 +502,12 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                                                   static_cast<long long>(h) * p.bs[1] +
                                                   static_cast<long long>(row_g) * p.bs[2]);
     }
+    const bool bias_wide = BIAS && bias_rows_32b(p);
     for (int j = 0; j < n_tiles; ++j) {
       const int buf = j & 1;
-      uint32_t bw[BIAS ? 32 : 1];   // this thread's 64 bias elements of the tile, fetched under the wait
-      if constexpr (BIAS) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int c = j * kT + half * 64 + 8 * i;
-          const uint4 w = (bias_row != nullptr && c < p.S) ? __ldg(bias_row + (c >> 3)) : make_uint4(0u, 0u, 0u, 0u);
-          bw[4 * i] = w.x;
-          bw[4 * i + 1] = w.y;
-          bw[4 * i + 2] = w.z;
-          bw[4 * i + 3] = w.w;
-        }
-      }
+      uint4 bv[BIAS ? 8 : 1];   // this thread's 64 bias elements of the tile, fetched under the wait
+      if constexpr (BIAS) load_bias_row(bv, bias_row, j * kT + half * 64, p.S, bias_wide);
+      const uint32_t* bw = reinterpret_cast<const uint32_t*>(bv);
       bool ok = wait_clocked(smem_u32(&sync->sp_full), j & 1, abort_flag, wait_limit);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {

@@ -457,10 +457,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       const long long c = static_cast<long long>(row_g) + p.causal_shift + 1;
       lim = c < lim ? static_cast<int>(c < 0 ? 0 : c) : lim;
     }
-    // With an additive bias the logits are brought to log2 units when they are read
-    // (s * scale * log2 e + bias * log2 e); everything after that then works with scale 1.
-    const float sl2_in = p.scale * kLog2e;
-    const float sl2 = BIAS ? 1.f : sl2_in;
+    // With an additive bias the logits s * scale + bias are formed when the scores are read;
+    // everything after that then works on them with scale 1 (log2 e in the exponent).
+    const float sl2_in = BIAS ? p.scale : p.scale * kLog2e;
+    const float sl2 = BIAS ? kLog2e : sl2_in;
     float m_run = -CUDART_INF_F, l_run = 0.f;
     bool alive = true;
     // this row of the bias, 16-bit elements in the query's dtype, unit stride along the keys
@@ -472,18 +472,16 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                                                   static_cast<long long>(row_g) * p.bs[2]);
     }
 
+    const bool bias_wide = BIAS && bias_rows_32b(p);
+
     PHASE_DECL;
     if (tg.in_range) {
       for (int j = 0; j < tg.n_tiles; ++j) {
         PHASE_ADD(8 + (j == 0 ? 0 : 1), r == 0);   // 8: prologue until the first wait, 9: arrive -> next wait
         uint4 bv[BIAS ? kBlockN / 8 : 1];
         if constexpr (BIAS) {
-          // the bias of this key tile travels while the scores are awaited (S is a multiple of 8)
-#pragma unroll
-          for (int i = 0; i < kBlockN / 8; ++i) {
-            const int c = j * kBlockN + 8 * i;
-            bv[i] = (bias_row != nullptr && c < p.S) ? __ldg(bias_row + (c >> 3)) : make_uint4(0u, 0u, 0u, 0u);
-          }
+          // the bias of this key tile travels while the scores are awaited
+          load_bias_row(bv, bias_row, j * kBlockN, p.S, bias_wide);
         }
         bool ok = wait_clocked(smem_u32(&sync->s_full[t]), j & 1, abort_flag, wait_limit);
         ok = __all_sync(0xffffffffu, ok);
@@ -676,7 +674,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         PHASE_ADD(10, r == 0);                      // 10: epilogue (wait O, scale, stage, store)
         if (p.lse != nullptr && row_g < p.L) {
           // one rounding at the magnitude of the maximum: m*scale + ln(l)
-          const float lse = l_run > 0.f ? fmaf(m_run, BIAS ? kLn2 : p.scale, lg2(l_run) * kLn2) : -CUDART_INF_F;
+          const float lse = l_run > 0.f ? fmaf(m_run, BIAS ? 1.f : p.scale, lg2(l_run) * kLn2) : -CUDART_INF_F;
           p.lse[b * p.ls[0] + head_of_tile[t] * p.ls[1] + row_g * p.ls[2]] = lse;
         }
       }

@@ -7,8 +7,9 @@
 // Q (48 KB) + two K slots (48 KB each) + two V slots (32 KB each) = 208 KB of shared memory
 // (at 256: Q, one K slot and one V slot of 64 KB each).
 // Roles (192 threads): warps 0-3 softmax (one thread per query row = TMEM lane), warp 4 TMA
-// producer, warp 5 MMA issuer.  TMEM columns: [0,128) S (P overwrites its first 64 columns as
-// 16-bit pairs), [128,128+Dv) O.
+// producer, warp 5 MMA issuer.  TMEM columns: [0,128) and [128,256) scores of even and odd key
+// tiles (P overwrites the first 64 columns of its buffer as 16-bit pairs), [256,256+Dv) O.  With
+// two score buffers Q K^T of the next key tile runs under the softmax of this one.
 #include "tc_common.cuh"
 
 namespace b200 {
@@ -268,9 +269,9 @@ prefill_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       const long long c = static_cast<long long>(row_g) + p.causal_shift + 1;
       lim = c < lim ? static_cast<int>(c < 0 ? 0 : c) : lim;
     }
-    // with an additive bias the logits are brought to log2 units as they are read (see prefill_sm100.cu)
-    const float sl2_in = p.scale * kLog2e;
-    const float sl2 = BIAS ? 1.f : sl2_in;
+    // with an additive bias the logits s * scale + bias are formed as the scores are read (see prefill_sm100.cu)
+    const float sl2_in = BIAS ? p.scale : p.scale * kLog2e;
+    const float sl2 = BIAS ? kLog2e : sl2_in;
     float m_run = -CUDART_INF_F, l_run = 0.f;
     bool alive = true;
     const uint4* bias_row = nullptr;
@@ -281,15 +282,13 @@ prefill_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                                                   static_cast<long long>(row_g) * p.bs[2]);
     }
 
+    const bool bias_wide = BIAS && bias_rows_32b(p);
+
     for (int j = 0; j < n_tiles; ++j) {
       const uint32_t s_addr = s_base + static_cast<uint32_t>((j & 1) * kN);
       uint4 bv[BIAS ? kN / 8 : 1];
       if constexpr (BIAS) {
-#pragma unroll
-        for (int i = 0; i < kN / 8; ++i) {
-          const int c = j * kN + 8 * i;
-          bv[i] = (bias_row != nullptr && c < p.S) ? __ldg(bias_row + (c >> 3)) : make_uint4(0u, 0u, 0u, 0u);
-        }
+        load_bias_row(bv, bias_row, j * kN, p.S, bias_wide);
       }
       bool ok = wait_clocked(smem_u32(&sync->s_full[j & 1]), static_cast<uint32_t>(j >> 1) & 1u, abort_flag, wait_limit);
       ok = __all_sync(0xffffffffu, ok);
@@ -438,7 +437,7 @@ prefill_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         tma_store_wait_read();
       }
       if (p.lse != nullptr && row_g < p.L) {
-        const float lse = l_run > 0.f ? fmaf(m_run, BIAS ? kLn2 : p.scale, lg2(l_run) * kLn2) : -CUDART_INF_F;
+        const float lse = l_run > 0.f ? fmaf(m_run, BIAS ? 1.f : p.scale, lg2(l_run) * kLn2) : -CUDART_INF_F;
         p.lse[b * p.ls[0] + h * p.ls[1] + row_g * p.ls[2]] = lse;
       }
     }

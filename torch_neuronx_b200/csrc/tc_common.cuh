@@ -48,6 +48,12 @@ __device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
   return r;
 }
 
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+
 template <bool BF16> __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   uint32_t r;
   if (BF16) {
@@ -139,11 +145,46 @@ inline bool strides_ok(const void* base, const int64_t* s, int rows, int heads, 
   return true;
 }
 
-// Eight logits in log2 units: s * (scale * log2 e) + bias * log2 e, the bias as eight 16-bit
-// elements of the query's dtype.
+// One thread's 8 N bias elements (16-bit) of a key tile: N 16-byte pieces, fetched as N / 2
+// 32-byte loads when the row allows it (`wide`: the row start and the key offset on a 32-byte
+// boundary) -- every thread reads its own row, so the number of load instructions is what the
+// load/store unit feels.  Pieces at or beyond `n_cols` (a multiple of 8) read as zero.
+template <int N>
+__device__ __forceinline__ void load_bias_row(uint4 (&bv)[N], const uint4* row, const int col0, const int n_cols,
+                                              const bool wide) {
+  if (row == nullptr) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) bv[i] = make_uint4(0u, 0u, 0u, 0u);
+    return;
+  }
+  if (wide && col0 + 8 * N <= n_cols) {
+#pragma unroll
+    for (int i = 0; i < N / 2; ++i) {
+      asm volatile("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                   : "=r"(bv[2 * i].x), "=r"(bv[2 * i].y), "=r"(bv[2 * i].z), "=r"(bv[2 * i].w), "=r"(bv[2 * i + 1].x),
+                     "=r"(bv[2 * i + 1].y), "=r"(bv[2 * i + 1].z), "=r"(bv[2 * i + 1].w)
+                   : "l"(row + (col0 >> 3) + 2 * i));
+    }
+    return;
+  }
+#pragma unroll
+  for (int i = 0; i < N; ++i) {
+    const int c = col0 + 8 * i;
+    bv[i] = c < n_cols ? __ldg(row + (c >> 3)) : make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
+// Whether every row of the bias starts on a 32-byte boundary.
+__host__ __device__ inline bool bias_rows_32b(const Problem& p) {
+  return reinterpret_cast<uintptr_t>(p.bias) % 32 == 0 && p.bs[0] % 16 == 0 && p.bs[1] % 16 == 0 && p.bs[2] % 16 == 0;
+}
+
+// Eight logits s * scale + bias (natural units), the bias as eight 16-bit elements of the query's
+// dtype; one packed fma per pair of elements.
 template <bool BF16>
-__device__ __forceinline__ void add_bias8(uint32_t* sv, const uint4 bias, const float sl2_in) {
+__device__ __forceinline__ void add_bias8(uint32_t* sv, const uint4 bias, const float scale) {
   const uint32_t w[4] = {bias.x, bias.y, bias.z, bias.w};
+  const uint64_t scale2 = f2_pack(scale, scale);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     float lo, hi;
@@ -155,8 +196,11 @@ __device__ __forceinline__ void add_bias8(uint32_t* sv, const uint4 bias, const 
       lo = f.x;
       hi = f.y;
     }
-    sv[2 * i] = __float_as_uint(fmaf(__uint_as_float(sv[2 * i]), sl2_in, lo * kLog2e));
-    sv[2 * i + 1] = __float_as_uint(fmaf(__uint_as_float(sv[2 * i + 1]), sl2_in, hi * kLog2e));
+    const uint64_t t = f2_fma(f2_pack(__uint_as_float(sv[2 * i]), __uint_as_float(sv[2 * i + 1])), scale2, f2_pack(lo, hi));
+    float t0, t1;
+    f2_unpack(t, t0, t1);
+    sv[2 * i] = __float_as_uint(t0);
+    sv[2 * i + 1] = __float_as_uint(t1);
   }
 }
 
