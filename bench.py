@@ -271,6 +271,16 @@ def run_profile_case(args):
         out = torch.empty(4, 32, 4096, 128, device=dev, dtype=torch.bfloat16)
         lse = torch.empty(4, 32, 4096, dtype=torch.float32, device=dev)
         fn = lambda: T.sdpa_forward(q, k, v, is_causal=True, out=out, lse=lse)  # noqa: E731
+    elif args.profile == "bias":
+        # an additive bias shared by batch and heads (34 MB) on a 2 x 32/8 x 4096^2 problem (168 MB of operands)
+        g = torch.Generator(device=dev).manual_seed(6)
+        q = torch.randn(2, 32, 4096, 128, generator=g, device=dev, dtype=torch.bfloat16)
+        k = torch.randn(2, 8, 4096, 128, generator=g, device=dev, dtype=torch.bfloat16)
+        v = torch.randn(2, 8, 4096, 128, generator=g, device=dev, dtype=torch.bfloat16)
+        bias = torch.randn(4096, 4096, generator=g, device=dev, dtype=torch.bfloat16)
+        out = torch.empty_like(q)
+        lse = torch.empty(2, 32, 4096, dtype=torch.float32, device=dev)
+        fn = lambda: T.sdpa_forward(q, k, v, attn_bias=bias, scale=scale, out=out, lse=lse)  # noqa: E731
     elif args.profile == "bwd":
         # the headline batch cut to one sequence (84 MB of operands, still around L2 size) keeps captures short
         q, k, v, lens = c3_inputs(2, device=dev)
@@ -622,7 +632,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--profile", default=None, choices=["prefill", "decode", "gpt2", "bwd", "wide"],
+    ap.add_argument("--profile", default=None, choices=["prefill", "decode", "gpt2", "bwd", "wide", "bias"],
                     help="bare kernel loop on one GPU for profiler captures")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the decode / GPT-2 / fp32 extras")
