@@ -90,6 +90,8 @@ struct BSync {
   int abort_flag;
 };
 
+static_assert(sizeof(BSync) <= 272, "barrier block must fit its reserve (272 bytes + up to 1008 of alignment <= 1280)");
+
 // ------------------------------------------------------------------ prep --
 
 // Eight lanes per row (four rows per warp) when rows can be read 16 bytes at a time,
@@ -264,6 +266,8 @@ __device__ __forceinline__ float bias_to_f32(const uint32_t bits16) {
   if (BF16) return __uint_as_float(bits16 << 16);
   return __half2float(__ushort_as_half(static_cast<unsigned short>(bits16)));
 }
+
+static_assert(sizeof(ASync) <= 272, "barrier block must fit its reserve (272 bytes + up to 1008 of alignment <= 1280)");
 
 template <int D, bool BF16, bool BIAS>
 __global__ void __launch_bounds__(kThreads, 1)

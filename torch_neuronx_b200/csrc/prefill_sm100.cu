@@ -75,6 +75,8 @@ struct Sync {
   int abort_flag;
 };
 
+static_assert(sizeof(Sync) <= 272, "barrier block must fit its reserve (272 bytes + up to 1008 of alignment <= 1280)");
+
 // Optional phase timing (development builds only: -DB200_PHASE_TIMING).  One thread
 // per role adds the cycles it spent in each phase to a global table.
 #ifdef B200_TRACE

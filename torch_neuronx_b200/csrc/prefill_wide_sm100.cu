@@ -51,6 +51,8 @@ struct SyncW {
   int abort_flag;
 };
 
+static_assert(sizeof(SyncW) <= 272, "barrier block must fit its reserve (272 bytes + up to 1008 of alignment <= 1280)");
+
 template <int E, int DV, bool BF16, bool BIAS>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
