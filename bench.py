@@ -523,6 +523,45 @@ def run_ours(args, rank, local_rank, world):
             "l2": "flushed before every timed call",
         }
         del bgo, bgq, bgk, bgv
+        # ---------------- additive bias and the wide head dims on the tensor-core kernels ----------------
+        gen = torch.Generator(device=dev).manual_seed(7)
+        bias = torch.randn(4096, 4096, generator=gen, device=dev, dtype=torch.bfloat16)
+
+        aout, alse = torch.empty_like(out), torch.empty_like(lse)
+
+        def bias_step():
+            T.sdpa_forward(q, k, v, attn_bias=bias, scale=scale, out=aout, lse=alse)
+
+        for _ in range(3):
+            bias_step()
+        ams = time_steps_flushed(bias_step, max(5, min(args.steps, 10)), flush)
+        aflops = 4.0 * 128 * 4 * 32 * 4096 * 4096
+        extra["bias_prefill"] = {
+            "workload": "configuration 3 tensors, non-causal, with a bf16 [4096,4096] additive bias shared by batch and heads",
+            "value": aflops / (ams * 1e-3) / 1e12, "unit": "TFLOP/s", "ms": ams, "path": T.ops.last_plan.get("path"),
+            "l2": "flushed before every timed call",
+        }
+        del bias, aout, alse
+        wq = torch.randn(4, 32, 4096, 192, generator=gen, device=dev, dtype=torch.bfloat16)
+        wk = torch.randn(4, 32, 4096, 192, generator=gen, device=dev, dtype=torch.bfloat16)
+        wv = torch.randn(4, 32, 4096, 128, generator=gen, device=dev, dtype=torch.bfloat16)
+        wout = torch.empty(4, 32, 4096, 128, device=dev, dtype=torch.bfloat16)
+        wlse = torch.empty(4, 32, 4096, dtype=torch.float32, device=dev)
+
+        def wide_step():
+            T.sdpa_forward(wq, wk, wv, is_causal=True, out=wout, lse=wlse)
+
+        for _ in range(3):
+            wide_step()
+        wms = time_steps_flushed(wide_step, max(5, min(args.steps, 10)), flush)
+        wflops = 2.0 * (192 + 128) * 4 * 32 * (4096 * 4097 // 2)
+        extra["mla_shape_prefill"] = {
+            "workload": "q/k head dim 192, v head dim 128, bf16 [4,32,4096] causal, multi-head (the shape of upstream's "
+                        "multi-head-latent-attention test, at benchmark size)",
+            "value": wflops / (wms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms": wms, "path": T.ops.last_plan.get("path"),
+            "l2": "flushed before every timed call",
+        }
+        del wq, wk, wv, wout, wlse
         # ---------------- fp32 parity configuration: latency only ----------------
         g = torch.Generator().manual_seed(0)
         fq, fk, fv = (torch.randn(2, 8, 512, 64, generator=g).to(dev) for _ in range(3))
