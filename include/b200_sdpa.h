@@ -33,7 +33,7 @@
 extern "C" {
 #endif
 
-#define B200_SDPA_ABI_VERSION 4
+#define B200_SDPA_ABI_VERSION 5
 
 typedef enum b200_sdpa_status {
   B200_SDPA_OK = 0,
@@ -48,7 +48,10 @@ typedef enum b200_sdpa_status {
   B200_SDPA_ERR_CUDA = 8,         /* a CUDA runtime/driver call failed              */
   B200_SDPA_ERR_DEVICE = 9,       /* not an sm_100 device                           */
   B200_SDPA_ERR_TIMEOUT = 10,     /* (status word only) a device-side wait gave up  */
-  B200_SDPA_ERR_TOO_LARGE = 11    /* exceeds a fixed-capacity entry point's limit   */
+  B200_SDPA_ERR_TOO_LARGE = 11,   /* exceeds a fixed-capacity entry point's limit   */
+  B200_SDPA_ERR_CACHE_FULL = 12   /* (status word only) decode with append met a
+                                     sequence whose cache is full: its new row was
+                                     not stored and not attended to; [1] = batch    */
 } b200_sdpa_status;
 
 typedef enum b200_sdpa_dtype {
@@ -117,7 +120,9 @@ typedef struct B200SdpaParams {
                              cache), or NULL = all S keys                              */
 
   const void* bias;       /* optional additive bias broadcastable to (B,Hq,L,S), or
-                             NULL; forces the generic path                             */
+                             NULL.  The tensor-core kernels read it when it has the
+                             query's dtype, unit stride along the keys, S % 8 == 0 and
+                             16-byte aligned rows; any other bias runs the generic path */
   int32_t bias_dtype;     /* b200_sdpa_dtype of bias                                   */
   int32_t kv_chunk;       /* decode: keys per split, 0 = library default               */
   int64_t bias_stride[4]; /* 0 for broadcast dimensions                                */
@@ -143,7 +148,8 @@ typedef struct B200SdpaParams {
    * multiples of 8.  Batch b attends keys [0, kv_lens[b]] -- the new row is key
    * kv_lens[b] -- and the kernel that reads the row also writes it into the cache
    * (dense or paged) at that position, so no separate append pass is needed.  A
-   * sequence whose cache is full (kv_lens[b] >= S) appends nothing.  kv_lens is
+   * sequence whose cache is full (kv_lens[b] >= S) appends nothing and reports
+   * B200_SDPA_ERR_CACHE_FULL through the status word.  kv_lens is
    * required; kv_lens_out, if given, receives min(kv_lens[b] + 1, S) and must not alias
    * kv_lens.  Both NULL = plain decode.  Upstream appends to the cache with separate
    * ops before calling the attention op.                                              */
@@ -156,14 +162,19 @@ typedef struct B200SdpaParams {
   /* Rotary position embedding fused into the append step (needs k_new): q and k_new are
    * rotated by the angles of position kv_lens[b] -- in fp32, rounded to the storage dtype
    * once -- before they are used, and k_new is written to the cache rotated.  rope_cos /
-   * rope_sin are fp32 (positions, >= E/2 columns) with rope_stride floats between
+   * rope_sin are fp32 (rope_positions, >= E/2 columns) with rope_stride floats between
    * positions; rope_interleaved = 0 pairs element i with i + E/2 (the "rotate half"
-   * convention), 1 pairs 2i with 2i + 1.  NULL = no rotation.  Upstream applies the
-   * embedding with separate ops before the attention op.                              */
+   * convention), 1 pairs 2i with 2i + 1.  NULL = no rotation.  rope_positions (>= 1) is
+   * the number of rows in the tables; a length beyond the last row uses the last row's
+   * angles rather than reading past the tables, so give tables that cover the cache
+   * capacity S.  Upstream applies the embedding with separate ops before the attention
+   * op.                                                                               */
   const float* rope_cos;
   const float* rope_sin;
   int32_t rope_stride;
   int32_t rope_interleaved;
+  int32_t rope_positions;
+  int32_t reserved0;      /* keep 0                                                    */
 } B200SdpaParams;
 
 /* What the library would do (or did) for a parameter block. */

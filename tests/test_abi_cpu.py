@@ -260,11 +260,13 @@ def test_append_planning():
     p.k_new_stride[:] = [8 * 128 + 4, 128]                                # rows not 16-byte aligned
     assert _plan(p)[0] == _lib.ERR_UNSUPPORTED
     # rotary tables: both or none, only together with an appended row, at least E/2 columns
-    rope = dict(rope_cos=0x7F0000800000, rope_sin=0x7F0000900000, rope_stride=64)
+    # and a stated number of table rows
+    rope = dict(rope_cos=0x7F0000800000, rope_sin=0x7F0000900000, rope_stride=64, rope_positions=2048)
     assert _plan(dec(**rope))[0] == 0
-    assert _plan(dec(rope_cos=0x7F0000800000, rope_stride=64))[0] == _lib.ERR_NULL
+    assert _plan(dec(rope_cos=0x7F0000800000, rope_stride=64, rope_positions=2048))[0] == _lib.ERR_NULL
     assert _plan(dec(k_new=None, v_new=None, **rope))[0] == _lib.ERR_UNSUPPORTED
-    assert _plan(dec(rope_cos=0x7F0000800000, rope_sin=0x7F0000900000, rope_stride=32))[0] == _lib.ERR_UNSUPPORTED
+    assert _plan(dec(**{**rope, "rope_stride": 32}))[0] == _lib.ERR_UNSUPPORTED
+    assert _plan(dec(**{**rope, "rope_positions": 0}))[0] == _lib.ERR_SHAPE
 
 
 def test_bias_planning():

@@ -469,3 +469,34 @@ def test_tensor_core_backward_with_additive_bias(shape, kind, dtype):
     # the logit gradient is written by the CUDA-core kernels only
     _cuda_backward(go, q, k, v, mask=bias, need_grad_bias=True)
     assert _cuda_backward.path == "generic"
+
+
+def test_one_element_bias_takes_part_in_the_backward():
+    # A (1,1,1,1) bias shifts every logit and therefore lse; only None / an empty tensor mean "no bias"
+    # (upstream scaled_dot_product_fused_attention.py:178).  Gradients must match CPU autograd.
+    import torch_neuronx_b200 as T
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(11)
+    q, k, v, go = (torch.randn(2, 3, 20, 32, generator=g) for _ in range(4))
+    bias = torch.full((1, 1, 1, 1), 1.5)
+    qr, kr, vr, br = (t.clone().double().requires_grad_() for t in (q, k, v, bias))
+    torch.nn.functional.scaled_dot_product_attention(qr, kr, vr, attn_mask=br).backward(go.double())
+    qd, kd, vd, bd = (t.to(dev).requires_grad_() for t in (q, k, v, bias))
+    T.scaled_dot_product_attention(qd, kd, vd, attn_mask=bd).backward(go.to(dev))
+    torch.cuda.synchronize()
+    _close(qd.grad.cpu(), qr.grad, torch.float32, "dq with a one-element bias")
+    _close(kd.grad.cpu(), kr.grad, torch.float32, "dk with a one-element bias")
+    _close(vd.grad.cpu(), vr.grad, torch.float32, "dv with a one-element bias")
+    assert bd.grad.shape == bias.shape
+    assert abs(float(bd.grad.cpu()) - float(br.grad)) <= 1e-4   # the logit gradients sum to zero per row
+    # and with B = Hq = L = S = 1 a full-shape bias is a one-element tensor too
+    q1, k1, v1, go1 = (torch.randn(1, 1, 1, 32, generator=g) for _ in range(4))
+    b1 = torch.full((1, 1, 1, 1), -0.75)
+    qd, kd, vd, bd = (t.to(dev).requires_grad_() for t in (q1, k1, v1, b1))
+    out = T.scaled_dot_product_attention(qd, kd, vd, attn_mask=bd)
+    out.backward(go1.to(dev))
+    torch.cuda.synchronize()
+    torch.testing.assert_close(out.detach().cpu(), v1, rtol=1e-6, atol=1e-6)          # one key: out = v
+    torch.testing.assert_close(vd.grad.cpu(), go1, rtol=1e-6, atol=1e-6)
+    assert float(qd.grad.abs().max()) <= 1e-6 and float(kd.grad.abs().max()) <= 1e-6

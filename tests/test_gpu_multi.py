@@ -150,3 +150,33 @@ def test_context_parallel_training_step_on_two_gpus(tmp_path):
         res = torch.load(tmp_path / f"r{r}.pt")
         for layout, errs in res.items():
             assert errs[0] <= 1e-5 and max(errs[1:]) <= 1e-4, (r, layout, errs)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_one_process_drives_two_devices_and_keeps_its_current_device():
+    """Every kernel family on cuda:0 and then on cuda:1 from one process: the opt-in to large dynamic
+    shared memory is a per-device attribute, and a call naming another device must leave the caller's
+    current device as it found it."""
+    import torch_neuronx_b200 as T
+    from oracle import sdpa_oracle as O
+    from tests.util import make_qkv
+
+    q, k, v = make_qkv(3, 1, 8, 2, 300, 300, 128, torch.bfloat16)
+    go = torch.randn(q.shape, generator=torch.Generator().manual_seed(4)).to(torch.bfloat16)
+    ref_o, ref_l = O.sdpa_forward(q, k, v, is_causal=True, compute_dtype=torch.float32)
+    torch.cuda.set_device(0)
+    for index in (0, 1):
+        dev = torch.device("cuda", index)
+        T.reset_launch_counts()
+        out, lse = T.sdpa_forward(q.to(dev), k.to(dev), v.to(dev), is_causal=True)
+        gq, gk, gv, _ = T.sdpa_backward(go.to(dev), q.to(dev), k.to(dev), v.to(dev), out, lse, is_causal=True)
+        torch.cuda.synchronize(dev)
+        T.check_device_status()
+        assert torch.cuda.current_device() == 0, "a call on another device changed the caller's device"
+        counts = T.launch_counts()
+        assert counts["prefill"] == 1 and counts["bwd_dq"] == 1 and counts["bwd_dkv"] == 1, counts
+        assert (out.cpu().float() - ref_o).abs().max().item() <= 2e-2
+        assert (lse.cpu() - ref_l).abs().max().item() <= 1e-3
+        want = O.sdpa_backward(go, q, k, v, out.cpu(), lse.cpu(), is_causal=True, compute_dtype=torch.float32)
+        for got, ref in zip((gq, gk, gv), want[:3]):
+            torch.testing.assert_close(got.cpu().float(), ref, rtol=5e-2, atol=2e-2)

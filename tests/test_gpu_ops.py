@@ -42,6 +42,9 @@ def test_aten_op_returns_the_nine_tuple():
     assert max_q == 96 and max_k == 80
     assert cq is None or cq.numel() == 0
     assert dbg is None or dbg.numel() == 0
+    # dropout is off: the philox slots are int32 scalar zeros (upstream decompositions.py:2310-2311)
+    for slot in (seed, off):
+        assert slot.dtype == torch.int32 and slot.dim() == 0 and slot.device.type == "cuda" and int(slot) == 0
     ref_o, ref_l = O.sdpa_forward(q, k, v, scale=0.1, compute_dtype=torch.float32)
     assert (out.cpu().float() - ref_o).abs().max().item() <= HALF_MAX_ABS
     assert (lse.cpu() - ref_l).abs().max().item() <= 1e-3

@@ -120,7 +120,12 @@ def test_decode_with_fused_append(paged):
         else:
             out, lse, new = T.decode_append(q.to(dev), k_new.to(dev), v_new.to(dev), kc, vc, cur, need_lse=True)
         torch.cuda.synchronize()
-        T.check_device_status()
+        if bool((cur.cpu() >= S).any()):
+            # a sequence whose cache is full drops its new row; the status word says which one
+            with pytest.raises(RuntimeError, match=r"cache is full.*role=3 step=320 extra=320"):
+                T.check_device_status()
+        else:
+            T.check_device_status()
         want_lens = (cur.cpu() + 1).clamp(max=S)
         assert torch.equal(new.cpu(), want_lens)
         check_against_oracle(q, k_full, v_full, out.cpu(), lse.cpu(), kv_lens=want_lens, tag=f"append step {step}")
@@ -186,3 +191,56 @@ def test_decode_append_with_fused_rotary_embedding(dtype, D, interleaved):
     for b in range(B):
         assert torch.equal(kc[b, :, pos[b]].cpu(), k_rot[b])                    # the cache holds the rotated key
         assert torch.equal(vc[b, :, pos[b]].cpu(), v_new[b])
+
+
+def test_rotary_tables_must_cover_the_cache():
+    """The rotary tables are indexed by the sequence length: the host layer refuses tables shorter than
+    the cache, and through the C ABI a length beyond the tables uses their last row instead of reading
+    past them."""
+    import ctypes as C
+
+    import torch_neuronx_b200 as T
+    from torch_neuronx_b200 import _lib
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(5)
+    B, Hq, Hkv, S, D = 2, 4, 2, 64, 64
+    q = torch.randn(B, Hq, 1, D, generator=g).to(torch.bfloat16).to(dev)
+    kc = torch.randn(B, Hkv, S, D, generator=g).to(torch.bfloat16).to(dev)
+    vc = torch.randn(B, Hkv, S, D, generator=g).to(torch.bfloat16).to(dev)
+    kn = torch.randn(B, Hkv, D, generator=g).to(torch.bfloat16).to(dev)
+    vn = torch.randn(B, Hkv, D, generator=g).to(torch.bfloat16).to(dev)
+    lens = torch.tensor([10, 40], dtype=torch.int32, device=dev)
+    short = torch.randn(32, D // 2, generator=g).to(dev)           # 32 positions for a 64-row cache
+    with pytest.raises(RuntimeError, match="rotary tables hold 32 positions"):
+        T.decode_append(q, kn, vn, kc, vc, lens, rope_cos=short, rope_sin=short)
+
+    # straight through the C ABI with the short tables: sequence 1 (length 40) is rotated by row 31
+    lib = _lib.load()
+    cos, sin = short.cos().contiguous(), short.sin().contiguous()
+    out = torch.full_like(q, float("nan"))
+    new_lens = torch.empty_like(lens)
+    p = _lib.Params()
+    p.struct_size = C.sizeof(_lib.Params)
+    p.dtype, p.device, p.force_path = _lib.BF16, 0, _lib.PATH_DECODE
+    p.q, p.k, p.v, p.out = q.data_ptr(), kc.data_ptr(), vc.data_ptr(), out.data_ptr()
+    p.q_stride[:], p.k_stride[:], p.v_stride[:], p.out_stride[:] = q.stride(), kc.stride(), vc.stride(), out.stride()
+    p.B, p.Hq, p.Hkv, p.L, p.S, p.E, p.Dv = B, Hq, Hkv, 1, S, D, D
+    p.scale = D ** -0.5
+    p.kv_lens, p.kv_lens_out = lens.data_ptr(), new_lens.data_ptr()
+    p.k_new, p.v_new = kn.data_ptr(), vn.data_ptr()
+    p.k_new_stride[:], p.v_new_stride[:] = kn.stride()[:2], vn.stride()[:2]
+    p.rope_cos, p.rope_sin, p.rope_stride, p.rope_positions = cos.data_ptr(), sin.data_ptr(), cos.stride(0), 32
+    plan = _lib.Plan()
+    plan.struct_size = C.sizeof(_lib.Plan)
+    assert lib.b200_sdpa_query_plan(C.byref(p), C.byref(plan)) == _lib.OK
+    ws = torch.empty(max(int(plan.workspace_bytes), 16), dtype=torch.uint8, device=dev)
+    p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
+    assert lib.b200_sdpa_decode(C.byref(p), C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)) == _lib.OK
+    torch.cuda.synchronize()
+    rows = torch.tensor([10, 31])
+    k_rot = _rope(kn.cpu(), cos.cpu()[rows][:, None, :], sin.cpu()[rows][:, None, :], False).to(torch.bfloat16)
+    for b, pos in enumerate((10, 40)):
+        assert torch.equal(kc[b, :, pos].cpu(), k_rot[b])
+    p.rope_positions = 0
+    assert lib.b200_sdpa_query_plan(C.byref(p), C.byref(plan)) == _lib.ERR_SHAPE

@@ -19,13 +19,13 @@ import threading
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libb200_sdpa.so")
 
-ABI_VERSION = 4
+ABI_VERSION = 5
 STATIC_SCRATCH_BYTES = 16 << 20  # B200_SDPA_STATIC_SCRATCH_BYTES
 
 # b200_sdpa_status
 OK = 0
 ERR_NULL, ERR_STRUCT, ERR_DTYPE, ERR_SHAPE, ERR_UNSUPPORTED = 1, 2, 3, 4, 5
-ERR_WORKSPACE, ERR_ALIGNMENT, ERR_CUDA, ERR_DEVICE, ERR_TIMEOUT, ERR_TOO_LARGE = 6, 7, 8, 9, 10, 11
+ERR_WORKSPACE, ERR_ALIGNMENT, ERR_CUDA, ERR_DEVICE, ERR_TIMEOUT, ERR_TOO_LARGE, ERR_CACHE_FULL = 6, 7, 8, 9, 10, 11, 12
 
 # b200_sdpa_dtype
 F32, F16, BF16 = 0, 1, 2
@@ -88,6 +88,8 @@ class Params(C.Structure):
         ("rope_sin", C.c_void_p),
         ("rope_stride", C.c_int32),
         ("rope_interleaved", C.c_int32),
+        ("rope_positions", C.c_int32),
+        ("reserved0", C.c_int32),
     ]
 
 

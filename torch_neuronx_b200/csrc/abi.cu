@@ -64,6 +64,8 @@ int validate(const B200SdpaParams* a, Problem* p) {
   p->rope_sin = a->rope_sin;
   p->rope_stride = a->rope_stride;
   p->rope_interleaved = a->rope_interleaved != 0;
+  p->rope_positions = a->rope_positions;
+  if (a->rope_cos != nullptr && a->rope_positions < 1) return B200_SDPA_ERR_SHAPE;
   if ((a->rope_cos == nullptr) != (a->rope_sin == nullptr)) return B200_SDPA_ERR_NULL;
   if (a->rope_cos != nullptr && (a->k_new == nullptr || a->rope_stride < a->E / 2)) return B200_SDPA_ERR_UNSUPPORTED;
   if ((a->k_new == nullptr) != (a->v_new == nullptr)) return B200_SDPA_ERR_NULL;
@@ -120,14 +122,55 @@ int choose(const B200SdpaParams* a, const Problem& p, int* path) {
   return B200_SDPA_OK;
 }
 
-int select_device(int device) {
-  if (device < 0) return B200_SDPA_OK;
-  if (cudaSetDevice(device) != cudaSuccess) {
-    cudaGetLastError();
-    return B200_SDPA_ERR_CUDA;
+// Makes the requested device current for the duration of one entry point and puts the caller's
+// device back afterwards (a library call must not change which device the host thread is on).
+// Also the one place that checks the compute capability: every kernel here is sm_100a code.
+class DeviceScope {
+ public:
+  explicit DeviceScope(int device) {
+    int cur = -1;
+    if (cudaGetDevice(&cur) != cudaSuccess) {
+      cudaGetLastError();
+      rc_ = B200_SDPA_ERR_CUDA;
+      return;
+    }
+    int want = device < 0 ? cur : device;
+    if (want != cur) {
+      if (cudaSetDevice(want) != cudaSuccess) {
+        cudaGetLastError();
+        rc_ = B200_SDPA_ERR_CUDA;
+        return;
+      }
+      restore_ = cur;
+    }
+    rc_ = is_sm100(want) ? B200_SDPA_OK : B200_SDPA_ERR_DEVICE;
   }
-  return B200_SDPA_OK;
-}
+  ~DeviceScope() {
+    if (restore_ >= 0 && cudaSetDevice(restore_) != cudaSuccess) cudaGetLastError();
+  }
+  DeviceScope(const DeviceScope&) = delete;
+  DeviceScope& operator=(const DeviceScope&) = delete;
+  int status() const { return rc_; }
+
+ private:
+  static bool is_sm100(int dev) {
+    constexpr int kMax = 64;
+    static std::atomic<int> known[kMax];   // 0 = not asked yet, 1 = sm_100, 2 = something else
+    if (dev >= 0 && dev < kMax) {
+      const int k = known[dev].load(std::memory_order_relaxed);
+      if (k != 0) return k == 1;
+    }
+    int major = 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) {
+      cudaGetLastError();
+      return false;
+    }
+    if (dev >= 0 && dev < kMax) known[dev].store(major == 10 ? 1 : 2, std::memory_order_relaxed);
+    return major == 10;
+  }
+  int restore_ = -1;
+  int rc_ = B200_SDPA_OK;
+};
 
 int validate_bwd(const B200SdpaBwdParams* a, BwdProblem& bp) {
   if (a == nullptr) return B200_SDPA_ERR_NULL;
@@ -190,6 +233,7 @@ int validate_bwd(const B200SdpaBwdParams* a, BwdProblem& bp) {
   p.lens_out = nullptr;
   p.rope_cos = nullptr;
   p.rope_sin = nullptr;
+  p.rope_positions = 0;
   if (a->force_path != B200_SDPA_PATH_AUTO && a->force_path != B200_SDPA_PATH_GENERIC &&
       a->force_path != B200_SDPA_PATH_PREFILL)
     return B200_SDPA_ERR_UNSUPPORTED;
@@ -235,6 +279,7 @@ const char* b200_sdpa_strerror(int status) {
     case B200_SDPA_ERR_DEVICE: return "device is not sm_100";
     case B200_SDPA_ERR_TIMEOUT: return "a device-side wait gave up (kernel drained and returned)";
     case B200_SDPA_ERR_TOO_LARGE: return "request exceeds the fixed capacity of this entry point";
+    case B200_SDPA_ERR_CACHE_FULL: return "decode with append: a sequence's cache is full, its new row was dropped";
     default: return "unknown status";
   }
 }
@@ -264,8 +309,8 @@ int b200_sdpa_fwd(const B200SdpaParams* params, void* stream) {
   rc = choose(params, p, &path);
   if (rc != B200_SDPA_OK) return rc;
   if (p.S == 0) path = B200_SDPA_PATH_GENERIC;  // nothing to attend to: zeros and -inf
-  rc = select_device(params->device);
-  if (rc != B200_SDPA_OK) return rc;
+  DeviceScope scope(params->device);
+  if (scope.status() != B200_SDPA_OK) return scope.status();
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (path == B200_SDPA_PATH_DECODE) {
     rc = launch_decode(p, params->dtype, params->kv_chunk, params->workspace, params->workspace_bytes, st);
@@ -286,8 +331,8 @@ int b200_sdpa_decode(const B200SdpaParams* params, void* stream) {
   int rc = validate(params, &p);
   if (rc != B200_SDPA_OK) return rc;
   if (!decode_eligible(p, params->dtype)) return B200_SDPA_ERR_UNSUPPORTED;
-  rc = select_device(params->device);
-  if (rc != B200_SDPA_OK) return rc;
+  DeviceScope scope(params->device);
+  if (scope.status() != B200_SDPA_OK) return scope.status();
   return launch_decode(p, params->dtype, params->kv_chunk, params->workspace, params->workspace_bytes,
                        reinterpret_cast<cudaStream_t>(stream));
 }
@@ -297,8 +342,8 @@ int b200_sdpa_decode_static(const B200SdpaParams* params, void* stream) {
   int rc = validate(params, &p);
   if (rc != B200_SDPA_OK) return rc;
   if (!decode_eligible(p, params->dtype)) return B200_SDPA_ERR_UNSUPPORTED;
-  rc = select_device(params->device);
-  if (rc != B200_SDPA_OK) return rc;
+  DeviceScope scope(params->device);
+  if (scope.status() != B200_SDPA_OK) return scope.status();
   return launch_decode_static(p, params->dtype, params->kv_chunk, reinterpret_cast<cudaStream_t>(stream));
 }
 
@@ -321,8 +366,8 @@ int b200_sdpa_bwd(const B200SdpaBwdParams* a, void* stream) {
   int path = 0;
   rc = choose_bwd(a, bp, &path);
   if (rc != B200_SDPA_OK) return rc;
-  rc = select_device(a->device);
-  if (rc != B200_SDPA_OK) return rc;
+  DeviceScope scope(a->device);
+  if (scope.status() != B200_SDPA_OK) return scope.status();
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (path == B200_SDPA_PATH_PREFILL) {
     rc = launch_bwd_tc(bp, a->dtype, a->workspace, a->workspace_bytes, st);
@@ -338,8 +383,8 @@ int b200_sdpa_merge(const B200SdpaMergeParams* m, void* stream) {
   if (m->acc == nullptr || m->acc_lse == nullptr || m->part == nullptr || m->part_lse == nullptr)
     return B200_SDPA_ERR_NULL;
   if (m->B < 0 || m->Hq < 0 || m->L < 0 || m->Dv < 0) return B200_SDPA_ERR_SHAPE;
-  int rc = select_device(m->device);
-  if (rc != B200_SDPA_OK) return rc;
+  DeviceScope scope(m->device);
+  if (scope.status() != B200_SDPA_OK) return scope.status();
   return launch_merge(*m, reinterpret_cast<cudaStream_t>(stream));
 }
 

@@ -60,23 +60,6 @@ template <int D> struct BCfg {
   static constexpr int kSmemBytes = kSmemTiles + kStatBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
-// Development only (-DB200_TRACE): time stamps of CTA 0.  g_btrace[kernel][role][step][event]
-#ifdef B200_TRACE
-__device__ long long g_btrace[2][3][64][4];
-#define BTRACE(kern, role, step, ev)                                                          \
-  do {                                                                                        \
-    if (blockIdx.x == 0 && (step) < 64) g_btrace[kern][role][step][ev] = clock64();           \
-  } while (0)
-__device__ long long g_cta[8192][8];
-#define CTRACE(ev)                                                                 \
-  do {                                                                             \
-    if (blockIdx.x < 8192) g_cta[blockIdx.x][ev] = clock64();                      \
-  } while (0)
-#else
-#define BTRACE(kern, role, step, ev)
-#define CTRACE(ev)
-#endif
-
 struct BSync {
   uint64_t fixed_full;
   uint64_t ring_full[kMaxStages];
@@ -278,14 +261,6 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                  const long long wait_limit) {
   using C = ACfg<D>;
   extern __shared__ uint8_t smem_raw[];
-#ifdef B200_TRACE
-  if (threadIdx.x == 0) {
-    CTRACE(0);
-    unsigned smid;
-    asm("mov.u32 %0, %smid;" : "=r"(smid));
-    if (blockIdx.x < 8192) g_cta[blockIdx.x][7] = smid;
-  }
-#endif
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t tiles = (raw_addr + 1023u) & ~1023u;
   ASync* sync = reinterpret_cast<ASync*>(smem_raw + (tiles - raw_addr) + C::kSmemTiles);
@@ -371,7 +346,6 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   tc_fence_after_sync();
   const uint32_t tmem_base = sync->tmem_base;
   constexpr uint32_t kColS = 0, kColDP = 128, kColOp = 256, kColDQ = 384;
-  if (tid == 0) CTRACE(1);
 
   if (warp == kProducerWarp) {
     if (lane == 0) {
@@ -446,19 +420,16 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         break;
       }
       tc_fence_after_sync();
-      if (lane == 0) BTRACE(0, 2, j, 0);
       if (j + 1 < n_tiles) {
         alive = issue_scores(j + 1);
         if (!alive) break;
       }
-      if (lane == 0) BTRACE(0, 2, j, 1);
       alive = wait_clocked(smem_u32(&sync->e_ready[buf]), (j >> 1) & 1, abort_flag, wait_limit);
       if (!alive) {
         if (lane == 0) report(p.status, 13, j, 0);
         break;
       }
       tc_fence_after_sync();
-      if (lane == 0) BTRACE(0, 2, j, 2);
       const uint64_t bd = mnmajor_desc(k_ring + ks * C::kTileBytes);
       if (elect_one()) {
 #pragma unroll
@@ -469,7 +440,6 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         mma_commit(smem_u32(&sync->k_empty[ks]));
         if (j + 1 == n_tiles) mma_commit(smem_u32(&sync->acc_done));
       }
-      if (lane == 0) BTRACE(0, 2, j, 3);
     }
     if (*abort_flag != 0) {
       if (elect_one()) mma_commit(smem_u32(&sync->drain));
@@ -520,9 +490,6 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         break;
       }
       tc_fence_after_sync();
-      if (tid == 0) BTRACE(0, 0, j, 0);
-      if (tid == 128) BTRACE(0, 1, j, 0);
-      if (tid == 0 && j == 0) CTRACE(2);
       uint32_t sv[64], dv[64];
       tmem_ld_32x32(s_addr, reinterpret_cast<uint32_t(&)[32]>(sv[0]));
       tmem_ld_32x32(s_addr + 32, reinterpret_cast<uint32_t(&)[32]>(sv[32]));
@@ -531,8 +498,6 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       tmem_ld_wait();
       tc_fence_before_sync();
       mbar_arrive(smem_u32(&sync->f_free));
-      if (tid == 0) BTRACE(0, 0, j, 1);
-      if (tid == 128) BTRACE(0, 1, j, 1);
       const int col0 = j * kT + half * 64;
       const bool need_mask = j * kT + kT > min_lim;
       uint32_t pk[32];
@@ -551,8 +516,6 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         }
         pk[i >> 1] = pack2<BF16>(p0 * (__uint_as_float(dv[i]) - dl), p1 * (__uint_as_float(dv[i + 1]) - dl));
       }
-      if (tid == 0) BTRACE(0, 0, j, 2);
-      if (tid == 128) BTRACE(0, 1, j, 2);
       if (j >= 2) {   // the product that read this operand buffer two tiles ago must have retired
         ok = wait_clocked(smem_u32(&sync->op_empty[buf]), ((j >> 1) - 1) & 1, abort_flag, wait_limit);
         ok = __all_sync(0xffffffffu, ok);
@@ -568,9 +531,6 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(smem_u32(&sync->e_ready[buf]));
-      if (tid == 0) BTRACE(0, 0, j, 3);
-      if (tid == 128) BTRACE(0, 1, j, 3);
-      if (tid == 0 && j + 1 == n_tiles) CTRACE(3);
     }
     if (alive && n_tiles > 0) {
       bool ok = wait_clocked(smem_u32(&sync->acc_done), 0, abort_flag, wait_limit);
@@ -587,11 +547,9 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       fence_proxy_async_smem();
       mbar_arrive(smem_u32(&sync->staged));
       if (tid == 0 && wait_clocked(smem_u32(&sync->staged), 0, abort_flag, wait_limit)) {
-        CTRACE(4);
         for (int bx = 0; bx < C::kBoxes; ++bx) tma_store_4d(&tm_dq, q_tile + bx * kBoxBytes, bx * 64, row0, h, b);
         tma_store_commit();
         tma_store_wait_read();
-        CTRACE(5);
       }
     }
   }
@@ -601,7 +559,6 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   if (warp == kMmaWarp) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
-    if (lane == 0) CTRACE(6);
   }
 }
 
@@ -944,14 +901,6 @@ int launch_tc(const BwdProblem& bp, float* lse2, float* delta, cudaStream_t stre
 
 }  // namespace
 
-#ifdef B200_TRACE
-extern "C" int b200_debug_read_cta(long long* host) {
-  return cudaMemcpyFromSymbol(host, g_cta, sizeof(long long) * 8192 * 8) != cudaSuccess;
-}
-extern "C" int b200_debug_read_btrace(long long* host) {
-  return cudaMemcpyFromSymbol(host, g_btrace, sizeof(long long) * 2 * 3 * 64 * 4) != cudaSuccess;
-}
-#endif
 
 bool bwd_tc_eligible(const BwdProblem& bp, int dtype, bool* alignment_only_failure) {
   const Problem& p = bp.f;

@@ -51,6 +51,7 @@ struct Problem {
   const float* rope_sin;
   int rope_stride;       // floats between positions
   int rope_interleaved;  // 0: pairs (i, i + D/2); 1: pairs (2i, 2i + 1)
+  int rope_positions;    // rows in the cos/sin tables (positions beyond use the last row)
 };
 
 // Backward: the forward's description (out and lse are inputs here) plus the upstream

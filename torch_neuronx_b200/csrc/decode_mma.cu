@@ -115,6 +115,14 @@ template <int D> __device__ __forceinline__ void rope_partner(int col, bool inte
   }
 }
 
+// Row of the cos/sin tables for the token being decoded: its position is the sequence's old length;
+// a length beyond the tables uses their last row (never a read past the end).
+__device__ __forceinline__ int rope_row(const Problem& p, int b) {
+  int len = p.kv_lens[b];
+  len = len < 0 ? 0 : len;
+  return len < p.rope_positions ? len : p.rope_positions - 1;
+}
+
 template <int D, bool BF16, bool PAGED, bool APPEND, bool ROPE>
 __global__ void __launch_bounds__(kThreads, 2) decode_mma_kernel(const Problem p, const int chunk, const int nsplit,
                                                                  float* __restrict__ part_o,
@@ -158,10 +166,9 @@ __global__ void __launch_bounds__(kThreads, 2) decode_mma_kernel(const Problem p
           const int64_t o = base + (h0 + row) * p.qs[1] + col * p.qs[3];
           if (ROPE) {
             // out[c] = x[c] cos + sign x[partner] sin at this step's position, in fp32, rounded once
-            int len = p.kv_lens[b];
-            len = len < 0 ? 0 : len;
-            const float* cs = p.rope_cos + static_cast<int64_t>(len) * p.rope_stride;
-            const float* sn = p.rope_sin + static_cast<int64_t>(len) * p.rope_stride;
+            const int at = rope_row(p, b);
+            const float* cs = p.rope_cos + static_cast<int64_t>(at) * p.rope_stride;
+            const float* sn = p.rope_sin + static_cast<int64_t>(at) * p.rope_stride;
             uint16_t outv[2];
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
@@ -199,6 +206,13 @@ __global__ void __launch_bounds__(kThreads, 2) decode_mma_kernel(const Problem p
     int len = p.kv_lens[b];
     len = len < 0 ? 0 : len;
     pos = len < p.S ? len : -1;
+    // a full cache drops the new row: say so once per sequence through the status word
+    if (pos < 0 && split == 0 && blockIdx.x == 0 && tid == 0 && p.status != nullptr &&
+        atomicCAS(p.status, 0, B200_SDPA_ERR_CACHE_FULL) == 0) {
+      p.status[1] = b;
+      p.status[2] = len;
+      p.status[3] = p.S;
+    }
     knew = reinterpret_cast<const char*>(p.k_new) + (b * p.kns[0] + hk * p.kns[1]) * 2;
     vnew = reinterpret_cast<const char*>(p.v_new) + (b * p.vns[0] + hk * p.vns[1]) * 2;
   }
@@ -230,8 +244,9 @@ __global__ void __launch_bounds__(kThreads, 2) decode_mma_kernel(const Problem p
         const uint4 vq = *reinterpret_cast<const uint4*>(vnew + ch * 16);
         if (ROPE) {
           // rotate the eight elements of this chunk (their partners sit in this chunk or in one other)
-          const float* cs = p.rope_cos + static_cast<int64_t>(pos) * p.rope_stride;
-          const float* sn = p.rope_sin + static_cast<int64_t>(pos) * p.rope_stride;
+          const int at = rope_row(p, b);
+          const float* cs = p.rope_cos + static_cast<int64_t>(at) * p.rope_stride;
+          const float* sn = p.rope_sin + static_cast<int64_t>(at) * p.rope_stride;
           const uint16_t* row16 = reinterpret_cast<const uint16_t*>(knew);
           uint16_t* kv16 = reinterpret_cast<uint16_t*>(&kq);
           uint16_t rot[8];

@@ -77,40 +77,6 @@ struct Sync {
 
 static_assert(sizeof(Sync) <= 272, "barrier block must fit its reserve (272 bytes + up to 1008 of alignment <= 1280)");
 
-// Optional phase timing (development builds only: -DB200_PHASE_TIMING).  One thread
-// per role adds the cycles it spent in each phase to a global table.
-#ifdef B200_TRACE
-// Development only: time stamps of one CTA.  g_trace[role][step][event]
-__device__ long long g_trace[6][64][4];
-#define TRACE(role, step, ev)                                                        \
-  do {                                                                               \
-    if (blockIdx.x == 0 && (step) < 64) g_trace[role][step][ev] = clock64();         \
-  } while (0)
-// per-CTA life-cycle stamps: [start, set-up done, first S (tile 0), last P (tile 0), staged, stored, end, smid]
-__device__ long long g_fcta[8192][8];
-#define CTRACE(ev)                                                                 \
-  do {                                                                             \
-    if (blockIdx.x < 8192) g_fcta[blockIdx.x][ev] = clock64();                     \
-  } while (0)
-#else
-#define TRACE(role, step, ev)
-#define CTRACE(ev)
-#endif
-
-#ifdef B200_PHASE_TIMING
-__device__ unsigned long long g_phase[32];
-#define PHASE_DECL long long ph_t0 = clock64(), ph_t1
-#define PHASE_ADD(slot, cond)                                                         \
-  do {                                                                                \
-    ph_t1 = clock64();                                                                \
-    if (cond) atomicAdd(&g_phase[slot], static_cast<unsigned long long>(ph_t1 - ph_t0)); \
-    ph_t0 = ph_t1;                                                                    \
-  } while (0)
-#else
-#define PHASE_DECL
-#define PHASE_ADD(slot, cond)
-#endif
-
 // Visible-key geometry of one 128-row tile.
 struct TileGeom {
   int row0;       // first query row
@@ -152,15 +118,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
-  if (tid == 0) TRACE(0, 63, 0);
-#ifdef B200_TRACE
-  if (tid == 0) {
-    CTRACE(0);
-    unsigned smid;
-    asm("mov.u32 %0, %smid;" : "=r"(smid));
-    if (blockIdx.x < 8192) g_fcta[blockIdx.x][7] = smid;
-  }
-#endif
 
   // Work item: longest (latest) query blocks first, heads of one kv group adjacent.
   // Two layouts of the CTA's two 128-row tiles:
@@ -253,8 +210,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = sync->tmem_base;
-  if (tid == 0) TRACE(0, 63, 1);
-  if (tid == 0) CTRACE(1);
 
   if (warp == kProducerWarp) {
     // ------------------------------------------------------------ TMA producer
@@ -357,14 +312,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
         commit(empty_bar(0));
       }
-      PHASE_DECL;
       for (int j = 0; j < n_iter && alive; ++j) {
         const int item_v = 2 * j + 1, item_kn = 2 * j + 2;
         const bool has_next = j + 1 < n_iter;
-        PHASE_ADD(22, lane == 0);                   // 22: loop overhead
         alive = wait_full(item_v);
         if (!alive) break;
-        PHASE_ADD(16, lane == 0);                   // 16: waiting for V(j)
         // one tile: P_t(j) V(j) in two halves as the halves of P arrive, then Q_t K(j+1)^T
         auto serve = [&](auto tile_const) {
           constexpr int t = decltype(tile_const)::value;
@@ -395,13 +347,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 return;
               }
               tc_fence_after_sync();
-              if (half == 0) {
-                if (lane == 0) TRACE(2 + t, j, 1);
-                PHASE_ADD(17 + 2 * t, lane == 0);   // 17 / 19: waiting for the first half of P_t(j)
-              }
               issue_pv_half(tile_const, stage_addr(item_v), half, j > 0);
             }
-            if (lane == 0) TRACE(2 + t, j, 2);
           }
           if (C::kSplitP) {
             if (j < nt) {
@@ -421,8 +368,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
               commit(smem_u32(&sync->o_done[t]));
             }
           }
-          if (lane == 0) TRACE(2 + t, j, 3);
-          PHASE_ADD(18 + 2 * t, lane == 0);         // 18 / 20: issue P V + (wait K) + Q K^T
         };
         serve(T0);
         if (!alive) break;
@@ -430,9 +375,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         if (!alive) break;
         commit(empty_bar(item_v));
         if (has_next) commit(empty_bar(item_kn));
-#ifdef B200_PHASE_TIMING
-        if (lane == 0) atomicAdd(&g_phase[31], 1ull);
-#endif
       }
       if (*abort_flag != 0) {
         // let whatever was issued retire before tensor memory is released
@@ -476,10 +418,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
     const bool bias_wide = BIAS && bias_rows_32b(p);
 
-    PHASE_DECL;
     if (tg.in_range) {
       for (int j = 0; j < tg.n_tiles; ++j) {
-        PHASE_ADD(8 + (j == 0 ? 0 : 1), r == 0);   // 8: prologue until the first wait, 9: arrive -> next wait
         uint4 bv[BIAS ? kBlockN / 8 : 1];
         if constexpr (BIAS) {
           // the bias of this key tile travels while the scores are awaited
@@ -493,10 +433,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           break;
         }
         tc_fence_after_sync();
-        if (r == 0) TRACE(t, j, 0);
-        if (tid == 0 && j == 0) CTRACE(2);
-        if (r == 96) TRACE(4 + t, j, 0);
-        PHASE_ADD(0, r == 0);                       // 0: waiting for S
         const int col0 = j * kBlockN;
         const bool need_mask = col0 + kBlockN > tg.min_lim;
 
@@ -527,7 +463,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           tc_fence_before_sync();
           mbar_arrive(smem_u32(&sync->s_free[t]));
         }
-        PHASE_ADD(1, r == 0);                       // 1: S TMEM -> registers (+ first half max)
         if constexpr (BIAS) {
 #pragma unroll
           for (int i = 8; i < 16; ++i) add_bias8<BF16>(&sv[8 * i], bv[i], sl2_in);
@@ -577,8 +512,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           tmem_st_wait();
         }
         const float nms = (m_run == -CUDART_INF_F) ? 0.f : -m_run * sl2;
-        if (r == 0) TRACE(t, j, 1);
-        PHASE_ADD(2, r == 0);                       // 2: mask, max, vote, (rescale)
 
         // probabilities, row sum (two packed accumulators), P -> TMEM over the first 64
         // columns of S.  (Measured alternatives that lost: a polynomial exp2 on the FMA
@@ -600,8 +533,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             tmem_st_wait();
             tc_fence_before_sync();
             mbar_arrive(smem_u32(&sync->p_ready[t][0]));
-            if (r == 0) TRACE(t, j, 3);
-            if (r == 96) TRACE(4 + t, j, 3);
           }
         }
         float sum4[4];
@@ -609,24 +540,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         f2_unpack(sum2[1], sum4[2], sum4[3]);
         const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
         l_run += sum;
-        PHASE_ADD(3, r == 0);                       // 3: exp, sum, pack, st issue
         tmem_st_wait();
         tc_fence_before_sync();
         mbar_arrive(smem_u32(&sync->p_ready[t][1]));
-        if (r == 0) TRACE(t, j, 2);
-        if (r == 96) TRACE(4 + t, j, 2);
-        PHASE_ADD(4, r == 0);                       // 4: st wait + arrive
-        if (r == 0) {
-#ifdef B200_PHASE_TIMING
-          atomicAdd(&g_phase[15], 1ull);            // tile iterations counted
-#endif
-        }
       }
-      PHASE_ADD(9, false);
 
       // ------------------------------------------------------------- epilogue
-      if (r == 0) TRACE(t, 62, 0);
-      if (tid == 0) CTRACE(3);
       if (alive && tg.n_tiles > 0) {
         bool ok = wait_clocked(smem_u32(&sync->o_done[t]), 0, abort_flag, wait_limit);
         ok = __all_sync(0xffffffffu, ok);
@@ -666,14 +585,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         // others at a barrier.
         fence_proxy_async_smem();
         mbar_arrive(smem_u32(&sync->o_staged[t]));
-        if (tid == 0) CTRACE(4);
         if (r == 0 && wait_clocked(smem_u32(&sync->o_staged[t]), 0, abort_flag, wait_limit)) {
           for (int bx = 0; bx < C::kBoxes; ++bx) tma_store_4d(&tm_o, q_smem[t] + bx * kBoxBytes, bx * 64, tg.row0, head_of_tile[t], b);
           tma_store_commit();
           tma_store_wait_read();
         }
-        if (tid == 0) CTRACE(5);
-        PHASE_ADD(10, r == 0);                      // 10: epilogue (wait O, scale, stage, store)
         if (p.lse != nullptr && row_g < p.L) {
           // one rounding at the magnitude of the maximum: m*scale + ln(l)
           const float lse = l_run > 0.f ? fmaf(m_run, BIAS ? 1.f : p.scale, lg2(l_run) * kLn2) : -CUDART_INF_F;
@@ -685,8 +601,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
   tc_fence_before_sync();
   __syncthreads();
-  if (tid == 0) TRACE(0, 63, 3);
-  if (tid == 0) CTRACE(6);
   if (warp == kMmaWarp) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
@@ -707,18 +621,11 @@ int launch_variant(const Problem& p, cudaStream_t stream) {
       !make_map(&tv, p.v, BF16, D, p.S, p.Hkv, p.B, p.vs) || !make_map(&to, p.out, BF16, D, p.L, p.Hq, p.B, p.os))
     return B200_SDPA_ERR_CUDA;
   auto kern = prefill_kernel<D, BF16, BIAS>;
-  static std::once_flag once;
-  static cudaError_t attr_rc = cudaSuccess;
-  std::call_once(once, [&] {
-    attr_rc = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
-  });
-  if (attr_rc != cudaSuccess) {
-    // the attribute is per device: retry once for processes that switch devices
-    attr_rc = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
-    if (attr_rc != cudaSuccess) {
-      cudaGetLastError();
-      return B200_SDPA_ERR_CUDA;
-    }
+  // the opt-in to more than 48 KB of dynamic shared memory is a per-device attribute: set on every
+  // launch (a cheap host-side call), so a process that drives several GPUs gets it on each of them
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess) {
+    cudaGetLastError();
+    return B200_SDPA_ERR_CUDA;
   }
   const int pair_heads = pair_heads_mode(p);
   const int rows = pair_heads ? kBlockM : kRowsPerCta;
@@ -734,26 +641,6 @@ int launch_variant(const Problem& p, cudaStream_t stream) {
 }
 
 }  // namespace
-
-#ifdef B200_TRACE
-extern "C" int b200_debug_read_fcta(long long* host) {
-  return cudaMemcpyFromSymbol(host, g_fcta, sizeof(long long) * 8192 * 8) != cudaSuccess;
-}
-extern "C" int b200_debug_read_trace(long long* host) {
-  return cudaMemcpyFromSymbol(host, g_trace, sizeof(long long) * 6 * 64 * 4) != cudaSuccess;
-}
-#endif
-
-#ifdef B200_PHASE_TIMING
-extern "C" int b200_debug_read_phases(unsigned long long* host32, int reset) {
-  if (cudaMemcpyFromSymbol(host32, g_phase, sizeof(unsigned long long) * 32) != cudaSuccess) return 1;
-  if (reset) {
-    unsigned long long z[32] = {};
-    if (cudaMemcpyToSymbol(g_phase, z, sizeof(z)) != cudaSuccess) return 1;
-  }
-  return 0;
-}
-#endif
 
 bool prefill_eligible(const Problem& p, int dtype, bool* alignment_only_failure) {
   if (p.E > 128) return prefill_wide_eligible(p, dtype, alignment_only_failure);

@@ -150,7 +150,7 @@ def _ring_forward(mesh, query, key, value, attn_bias=None, dropout_p=0.0, is_cau
     kw = {k: v for k, v in _block_functions.items() if k in ("attn_fn", "merge_fn")}
     out, lse = ring.ring_attention(query, key, value, group=mesh.get_group(), is_causal=is_causal, scale=scale,
                                    layout=_sequence_layout(), **kw)
-    zero = torch.zeros((), dtype=torch.int64, device=query.device)
+    zero = torch.zeros((), dtype=torch.int32, device=query.device)
     return out, lse, None, None, query.shape[2], key.shape[2], zero, zero, None
 
 

@@ -1,8 +1,9 @@
 """Structured-mask recognition: turn a dense boolean keep-mask that only expresses
 causality and/or right padding into ``is_causal`` / ``kv_lens``.
 
-A dense mask forces the generic CUDA-core kernel (the tensor-core kernels take no
-bias operand), exactly as a mask operand makes upstream's decomposition reject its
+A dense mask that is not recognised is served as an additive bias, which the tensor-core
+kernels read at about half the rate of their maskless form (and only for bias layouts they
+can load in 16-byte pieces), just as a mask operand makes upstream's decomposition reject its
 flash kernel; upstream removes such masks with an FX pass at trace time
 (``torch_neuronx/neuron_dynamo_backend/fx/passes/sdpa_causal_mask.py:1-37``).  Here
 the op runs eagerly, so the mask is examined when it is first seen: a candidate

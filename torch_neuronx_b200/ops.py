@@ -42,8 +42,9 @@ _DTYPE_CODE = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16:
 # ----------------------------------------------------------------------------
 
 _status_words: dict[int, torch.Tensor] = {}
-_zero_scalars: dict[int, torch.Tensor] = {}
+_zero_scalars: dict[int, tuple] = {}
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
+_retired_workspaces: list = []
 last_plan: dict = {}
 last_bwd_plan: dict = {}
 
@@ -60,23 +61,43 @@ def _status_word(dev: int) -> torch.Tensor:
     return w
 
 
-def _zero_scalar(dev: int) -> torch.Tensor:
+def _philox_zeros(dev: int):
+    """The philox seed / offset slots of the 9-tuple when dropout is off: int32 scalar zeros, as
+    upstream returns them (``decompositions.py:2310-2311``).  One pair per device."""
     z = _zero_scalars.get(dev)
     if z is None:
-        z = torch.zeros((), dtype=torch.int64, device=torch.device("cuda", dev))
+        d = torch.device("cuda", dev)
+        z = (torch.zeros((), dtype=torch.int32, device=d), torch.zeros((), dtype=torch.int32, device=d))
         _zero_scalars[dev] = z
     return z
 
 
 def _workspace(dev: int, nbytes: int) -> torch.Tensor:
-    """Scratch for the decode partials.  One buffer per (device, stream); it only
-    grows.  Work on one stream is ordered, so reuse across calls is safe."""
+    """Scratch for the decode partials and the backward's row statistics.
+
+    Eager calls share one buffer per (device, stream): work on one stream is ordered, so
+    reuse across calls is safe.  When a larger request arrives the old buffer is kept alive
+    (never handed back to the allocator) because a CUDA graph captured earlier on that
+    stream may have its address baked in.  While the stream is being captured the call gets
+    a buffer of its own from the graph's pool, and that buffer is not put into the eager
+    cache: memory of a graph's private pool must not be reused by eager work."""
+    if torch.cuda.is_current_stream_capturing():
+        return torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=torch.device("cuda", dev))
     key = (dev, torch.cuda.current_stream(dev).cuda_stream)
     w = _workspaces.get(key)
     if w is None or w.numel() < nbytes:
+        if w is not None:
+            _retired_workspaces.append(w)
         w = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=torch.device("cuda", dev))
         _workspaces[key] = w
     return w
+
+
+def release_workspaces() -> None:
+    """Drop every cached scratch buffer (also the retired ones).  Only safe when no CUDA graph
+    that was captured through this module will be replayed again."""
+    _workspaces.clear()
+    _retired_workspaces.clear()
 
 
 def check_device_status(device=None) -> None:
@@ -347,7 +368,7 @@ def paged_decode(
     p.block_table_stride = block_table.shape[1]
     p.page_size = page_size
     rope = (rope_cos, rope_sin, rope_interleaved) if rope_cos is not None else None
-    new_lens = _attach_new_rows(p, k_new, v_new, query, Hkv, kv_lens, rope)
+    new_lens = _attach_new_rows(p, k_new, v_new, query, Hkv, kv_lens, rope, capacity=int(p.S))
     _launch_decode(lib, p, dev, kv_chunk)
     return (out, lse) if new_lens is None else (out, lse, new_lens)
 
@@ -369,9 +390,10 @@ def _launch_decode(lib, p, dev: int, kv_chunk: int) -> None:
         raise RuntimeError(f"b200_sdpa_decode: {_lib.strerror(rc)}")
 
 
-def _attach_new_rows(p, k_new, v_new, query, Hkv, kv_lens, rope=None):
+def _attach_new_rows(p, k_new, v_new, query, Hkv, kv_lens, rope=None, capacity=None):
     """Fill the append (and rotary) fields of a parameter block; returns the tensor that will receive the
-    new lengths.  ``rope`` = ``(cos, sin, interleaved)`` with fp32 ``(positions, >= D/2)`` tables."""
+    new lengths.  ``rope`` = ``(cos, sin, interleaved)`` with fp32 ``(positions, >= D/2)`` tables that
+    must cover every position of the cache (``positions >= capacity``)."""
     if k_new is None and v_new is None:
         if rope is not None:
             raise RuntimeError("decode append: the rotary embedding is applied together with an appended row")
@@ -390,9 +412,14 @@ def _attach_new_rows(p, k_new, v_new, query, Hkv, kv_lens, rope=None):
         for name, t in (("rope_cos", cos), ("rope_sin", sin)):
             if t.dtype != torch.float32 or t.dim() != 2 or t.shape[1] < E // 2 or t.stride(1) != 1 or t.device != query.device:
                 raise RuntimeError(f"decode append: {name} must be an fp32 (positions, >= D/2) CUDA tensor with unit inner stride")
-        if cos.stride(0) != sin.stride(0):
-            raise RuntimeError("decode append: rope_cos and rope_sin must have the same row stride")
+        if cos.stride(0) != sin.stride(0) or cos.shape[0] != sin.shape[0]:
+            raise RuntimeError("decode append: rope_cos and rope_sin must have the same rows and row stride")
+        if cos.shape[0] < 1 or (capacity is not None and cos.shape[0] < capacity):
+            raise RuntimeError(
+                f"decode append: the rotary tables hold {cos.shape[0]} positions but the cache has room for {capacity}"
+            )
         p.rope_cos, p.rope_sin = cos.data_ptr(), sin.data_ptr()
+        p.rope_positions = cos.shape[0]
         p.rope_stride = cos.stride(0)
         p.rope_interleaved = 1 if interleaved else 0
     new_lens = torch.empty_like(kv_lens)
@@ -420,7 +447,8 @@ def decode_append(
     where key ``kv_lens[b]`` is the new row ``k_new[b]`` / ``v_new[b]`` (``(B, Hkv, D)``), and
     the CTA that reads that row also writes it into ``k_cache`` / ``v_cache`` at that position.
     Returns ``(out, lse, new_lens)`` with ``new_lens = min(kv_lens + 1, S)`` in a fresh tensor.
-    A sequence whose cache is full appends nothing.  With ``rope_cos`` / ``rope_sin`` (fp32
+    A sequence whose cache is full appends nothing (its new token is neither stored nor attended
+    to) and the device status word reports it: :func:`check_device_status` then raises.  With ``rope_cos`` / ``rope_sin`` (fp32
     ``(positions, >= D/2)``) the rotary embedding of position ``kv_lens[b]`` is applied to the query
     and to the new key inside the same kernel (fp32 arithmetic, one rounding; ``rope_interleaved``
     selects the (2i, 2i+1) pairing instead of (i, i + D/2)) and the key is cached rotated.  (Upstream's loop appends with separate ops
@@ -459,7 +487,7 @@ def decode_append(
     p.scale = float(scale)
     p.kv_lens = kv_lens.data_ptr()
     rope = (rope_cos, rope_sin, rope_interleaved) if rope_cos is not None else None
-    new_lens = _attach_new_rows(p, k_new, v_new, query, Hkv, kv_lens, rope)
+    new_lens = _attach_new_rows(p, k_new, v_new, query, Hkv, kv_lens, rope, capacity=S)
     _launch_decode(lib, p, dev, kv_chunk)
     return out, lse, new_lens
 
@@ -636,8 +664,8 @@ def fused_attention_overrideable(
     out, lse = sdpa_forward(query, key, value, attn_bias=bias, is_causal=is_causal, scale=scale, need_lse=True)
     if in_dtype == torch.float64:
         out = out.double()
-    zero = _zero_scalar(_device_index(query))
-    return out, lse, None, None, L, S, zero, zero, None
+    seed, offset = _philox_zeros(_device_index(query))
+    return out, lse, None, None, L, S, seed, offset, None
 
 
 def fused_attention_overrideable_backward(
@@ -660,7 +688,9 @@ def fused_attention_overrideable_backward(
     in_dtype = query.dtype
     if in_dtype == torch.float64:
         grad_out, query, key, value, out = (t.float() for t in (grad_out, query, key, value, out))
-    has_bias = attn_bias is not None and attn_bias.numel() > 1
+    # only None or an empty tensor mean "no bias" (upstream: scaled_dot_product_fused_attention.py:178);
+    # a one-element bias shifted every logit in the forward and is part of lse
+    has_bias = attn_bias is not None and attn_bias.numel() != 0
     bias = None
     if has_bias:
         bias = attn_bias.float() if attn_bias.dtype == torch.float64 else attn_bias
@@ -680,7 +710,7 @@ def _overrideable_backward_meta(
     dropout_p, is_causal, philox_seed, philox_offset, *, scale=None
 ):
     grad_bias = None
-    if attn_bias is not None and attn_bias.numel() > 1 and (len(grad_input_mask) < 4 or grad_input_mask[3]):
+    if attn_bias is not None and attn_bias.numel() != 0 and (len(grad_input_mask) < 4 or grad_input_mask[3]):
         grad_bias = query.new_empty((query.shape[0], query.shape[1], query.shape[2], key.shape[2]))
     return torch.empty_like(query), torch.empty_like(key), torch.empty_like(value), grad_bias
 
