@@ -180,3 +180,52 @@ def test_one_process_drives_two_devices_and_keeps_its_current_device():
         want = O.sdpa_backward(go, q, k, v, out.cpu(), lse.cpu(), is_causal=True, compute_dtype=torch.float32)
         for got, ref in zip((gq, gk, gv), want[:3]):
             torch.testing.assert_close(got.cpu().float(), ref, rtol=5e-2, atol=2e-2)
+
+
+def _long_context_worker(rank, world, port, out_dir):
+    """Configuration 5 at its own size (one causal 131072-token sequence) over two ranks: forward and backward
+    of the ring, then the sampled-row check the benchmark also runs (independent CUDA-core kernels on the
+    all-gathered tensors, a few rows on the CPU oracle, the negative guard)."""
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import math
+
+    import torch.distributed as dist
+
+    import bench
+    import torch_neuronx_b200 as T
+    from torch_neuronx_b200 import _lib, ring as R
+
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        S, Hq, Hkv, D = 131072, 64, 8, 128
+        n_local = S // world
+        g = torch.Generator(device=dev).manual_seed(4000 + rank)
+        q = torch.randn(1, Hq, n_local, D, generator=g, device=dev, dtype=torch.bfloat16)
+        k = torch.randn(1, Hkv, n_local, D, generator=g, device=dev, dtype=torch.bfloat16)
+        v = torch.randn(1, Hkv, n_local, D, generator=g, device=dev, dtype=torch.bfloat16)
+        go = torch.randn(q.shape, generator=g, device=dev, dtype=torch.bfloat16)
+        scale = 1.0 / math.sqrt(D)
+        out, lse = T.ring_attention(q, k, v, is_causal=True, scale=scale, layout="zigzag")
+        dq, dk, dv = T.ring_attention_backward(go, q, k, v, out, lse, is_causal=True, scale=scale, layout="zigzag")
+        torch.cuda.synchronize()
+        T.check_device_status()
+        res = bench.ring_check(T, R, _lib, dist, dev, rank, world, "zigzag", q, k, v, go, out, lse, dq, dk, dv, scale,
+                               True)
+        torch.save(res, os.path.join(out_dir, f"r{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_long_context_ring_at_full_size_on_two_gpus(tmp_path):
+    import torch.multiprocessing as mp
+
+    mp.spawn(_long_context_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    for r in range(2):
+        res = torch.load(tmp_path / f"r{r}.pt")
+        assert res["ok"], res
+        assert res["max_abs_out"] <= 2e-2 and res["max_abs_lse"] <= 1e-3 and res["guard_diff"] > 5e-2, res
+        assert res["max_abs_out_cpu"] <= 2e-2 and res["max_abs_lse_cpu"] <= 1e-3, res

@@ -206,7 +206,7 @@ __device__ __forceinline__ void drain_after_abort(BSync* sync, long long wait_li
   // let whatever was issued retire before tensor memory is released
   if (elect_one()) mma_commit(smem_u32(&sync->drain));
   const long long t0 = clock64();
-  while (!mbar_try_wait(smem_u32(&sync->drain), 0) && clock64() - t0 < wait_limit) {
+  while (!mbar_try_wait(smem_u32(&sync->drain), 0) && clock64() - t0 < kDrainCycles) {
   }
 }
 
@@ -444,7 +444,7 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     if (*abort_flag != 0) {
       if (elect_one()) mma_commit(smem_u32(&sync->drain));
       const long long t0 = clock64();
-      while (!mbar_try_wait(smem_u32(&sync->drain), 0) && clock64() - t0 < wait_limit) {
+      while (!mbar_try_wait(smem_u32(&sync->drain), 0) && clock64() - t0 < kDrainCycles) {
       }
     }
     __syncwarp();

@@ -157,6 +157,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   // barriers are initialised and tensor memory is allocated: the producer lane owns
   // the barriers of its own copies and starts Q and the first ring slots at once.
   int items_issued = 0;   // (producer lane) ring items already issued
+  bool q_armed = false;   // (producer lane) a copy into the Q slots is in flight or has landed
   if (warp == kProducerWarp && lane == 0) {
     mbar_init(smem_u32(&sync->q_full), 1);
     for (int s = 0; s < C::kStages; ++s) {
@@ -171,6 +172,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     if (tg1.n_tiles > 0) q_bytes += C::kTileBytes;
     const uint32_t qbar = smem_u32(&sync->q_full);
     if (q_bytes > 0) mbar_arrive_expect_tx(qbar, q_bytes);
+    q_armed = q_bytes > 0;
     for (int t = 0; t < 2; ++t) {
       const TileGeom& tg = t == 0 ? tg0 : tg1;
       if (tg.n_tiles == 0) continue;
@@ -231,10 +233,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         mbar_arrive_expect_tx(bar, C::kTileBytes);
         const CUtensorMap* map = (item & 1) ? &tm_v : &tm_k;
         for (int bx = 0; bx < C::kBoxes; ++bx) tma_load_4d(dst + bx * kBoxBytes, map, bar, bx * 64, j * kBlockN, hk, b);
-      }
-      if (*abort_flag != 0) {
-        // give copies already in flight time to land before shared memory goes away
-        for (int i = 0; i < 200; ++i) __nanosleep(1000);
+        items_issued = item + 1;
       }
     }
     __syncwarp();
@@ -375,13 +374,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         if (!alive) break;
         commit(empty_bar(item_v));
         if (has_next) commit(empty_bar(item_kn));
-      }
-      if (*abort_flag != 0) {
-        // let whatever was issued retire before tensor memory is released
-        commit(smem_u32(&sync->drain));
-        long long t0 = clock64();
-        while (!mbar_try_wait(smem_u32(&sync->drain), 0) && clock64() - t0 < wait_limit) {
-        }
       }
     }
     __syncwarp();
@@ -601,6 +593,24 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
   tc_fence_before_sync();
   __syncthreads();
+  if (sync->abort_flag != 0) {
+    // A role gave up.  Before shared and tensor memory are handed back, whatever this CTA already
+    // issued must have finished: the copies into the Q slots and the ring (their barriers complete
+    // when the bytes have landed) and every MMA (one more commit, which arrives when all earlier ones
+    // have retired).  These waits have their own generous bound, whatever the wait limit.
+    if (warp == kProducerWarp && lane == 0) {
+      if (q_armed) wait_drain(smem_u32(&sync->q_full), 0);
+      for (int s = 0; s < C::kStages && s < items_issued; ++s) {
+        const uint32_t last_round = static_cast<uint32_t>((items_issued - 1 - s) / C::kStages);
+        wait_drain(smem_u32(&sync->kv_full[s]), last_round & 1u);
+      }
+    }
+    if (warp == kMmaWarp) {
+      if (elect_one()) mma_commit(smem_u32(&sync->drain));
+      wait_drain(smem_u32(&sync->drain), 0);
+    }
+    __syncthreads();
+  }
   if (warp == kMmaWarp) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);

@@ -255,7 +255,7 @@ prefill_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     if (*abort_flag != 0) {
       if (elect_one()) mma_commit(smem_u32(&sync->drain));
       const long long t0 = clock64();
-      while (!mbar_try_wait(smem_u32(&sync->drain), 0) && clock64() - t0 < wait_limit) {
+      while (!mbar_try_wait(smem_u32(&sync->drain), 0) && clock64() - t0 < kDrainCycles) {
       }
     }
     __syncwarp();

@@ -64,21 +64,49 @@ template <bool BF16> __device__ __forceinline__ uint32_t pack2(float lo, float h
   return r;
 }
 
+// Limits below this many cycles are taken literally: the barrier is polled without suspending and
+// the clock is read after every poll, so a wait that is not satisfied within the limit gives up
+// after about that long.  (Used to exercise the give-up path; production limits are seconds.)
+constexpr long long kLiteralLimit = 1LL << 16;
+// How long an aborting CTA waits for work it already issued (copies, MMAs) before it lets go of
+// shared and tensor memory; independent of the wait limit.
+constexpr long long kDrainCycles = 1LL << 26;
+
 __device__ __forceinline__ bool wait_clocked(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                              long long limit_cycles) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  uint32_t spins = 0;
-  while (true) {
+  if (limit_cycles >= kLiteralLimit) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 15u) == 0u) {
-      if (*abort_flag != 0) return false;
-      if (clock64() - t0 > limit_cycles) {
-        *abort_flag = 1;
-        return false;
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while (true) {
+      if (mbar_try_wait(bar, parity)) return true;
+      if ((++spins & 15u) == 0u) {
+        if (*abort_flag != 0) return false;
+        if (clock64() - t0 > limit_cycles) {
+          *abort_flag = 1;
+          return false;
+        }
       }
     }
   }
+  const long long t0 = clock64();
+  while (true) {
+    if (mbar_test_wait(bar, parity)) return true;
+    if (*abort_flag != 0) return false;
+    if (clock64() - t0 > limit_cycles) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+
+// Wait (bounded by kDrainCycles, whatever the wait limit) for something this CTA issued itself.
+__device__ __forceinline__ bool wait_drain(uint32_t bar, uint32_t parity) {
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (clock64() - t0 > kDrainCycles) return false;
+  }
+  return true;
 }
 
 __device__ __forceinline__ void report(int* status, int role, int step, int extra) {

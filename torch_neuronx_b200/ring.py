@@ -166,16 +166,41 @@ class RankState:
         return out, lse
 
 
+def _mark(trace_row, name):
+    """Record a CUDA event on the current stream under ``name`` (timeline collection only)."""
+    if trace_row is not None:
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        trace_row.append((name, ev))
+
+
 def ring_step(state: RankState, kv_k: torch.Tensor, kv_v: torch.Tensor, rank: int, src: int, world: int,
-              layout: str, causal: bool, scale, attn_fn, merge_fn) -> int:
+              layout: str, causal: bool, scale, attn_fn, merge_fn, trace_row=None) -> int:
     """Attention of this rank's queries against one visiting block; returns the
     number of kernel calls made."""
     calls = ring_schedule(rank, src, world, state.q.shape[2], layout, causal)
     for c in calls:
+        _mark(trace_row, "attention")
         part, part_lse = attn_fn(state.q[:, :, c.q0 : c.q1], kv_k[:, :, c.k0 : c.k1], kv_v[:, :, c.k0 : c.k1],
                                  is_causal=c.causal, scale=scale, q_offset=c.q_offset, k_offset=c.k_offset)
+        _mark(trace_row, "merge")
         state.fold(c, part, part_lse, merge_fn)
     return len(calls)
+
+
+def trace_to_ms(trace) -> list:
+    """Turn the event rows collected by ``ring_attention(..., trace=[])`` into milliseconds per ring step:
+    time in the attention kernels, in the merges, and waiting for the next block to arrive after the
+    step's compute had finished (the part of the transfer that compute did not hide).  Call after a
+    device synchronisation."""
+    rows = []
+    for i, row in enumerate(trace):
+        acc = {"step": i, "attention_ms": 0.0, "merge_ms": 0.0, "wait_for_block_ms": 0.0, "finish_ms": 0.0}
+        key = {"attention": "attention_ms", "merge": "merge_ms", "wait": "wait_for_block_ms", "finish": "finish_ms"}
+        for (name, ev), (_, nxt) in zip(row[:-1], row[1:]):
+            acc[key[name]] += ev.elapsed_time(nxt)
+        rows.append(acc)
+    return rows
 
 
 # ----------------------------------------------------------------------------
@@ -194,25 +219,34 @@ def ring_attention(
     layout: str = ZIGZAG,
     attn_fn: Optional[Callable] = None,
     merge_fn: Optional[Callable] = None,
+    trace: Optional[list] = None,
 ):
     """Ring attention of this rank's sequence shard (see :func:`shard_sequence`)
     against every rank's keys and values.  Returns ``(out, lse)`` for the local rows.
 
     Each step posts the send of the block it holds and the receive of the next one
     before it computes, so the transfer runs beside the kernels; the received block
-    always lands in local memory first."""
+    always lands in local memory first.  ``trace`` (a list) collects CUDA events per step
+    for :func:`trace_to_ms` (CUDA tensors only)."""
     import torch.distributed as dist
 
     attn_fn = attn_fn or _default_attn
     merge_fn = merge_fn or _default_merge
-    world = dist.get_world_size(group)
-    rank = dist.get_rank(group)
+    # without a process group this is a ring of one: the same block calls, no transport
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
     state = RankState(q, v.shape[3], layout)
     if scale is None:
         scale = q.shape[3] ** -0.5
     if world == 1:
-        ring_step(state, k, v, 0, 0, 1, layout, is_causal, scale, attn_fn, merge_fn)
-        return state.finish(q.dtype)
+        row = [] if trace is not None else None
+        ring_step(state, k, v, 0, 0, 1, layout, is_causal, scale, attn_fn, merge_fn, row)
+        _mark(row, "finish")
+        res = state.finish(q.dtype)
+        _mark(row, "end")
+        if trace is not None:
+            trace.append(row)
+        return res
 
     same_d = k.shape[3] == v.shape[3]
     if same_d:  # one message per step
@@ -234,11 +268,22 @@ def ring_attention(
             reqs = dist.batch_isend_irecv(ops_)
         src = (rank - step) % world
         kk, vv = (cur[0], cur[1])
-        ring_step(state, kk, vv, rank, src, world, layout, is_causal, scale, attn_fn, merge_fn)
+        row = [] if trace is not None else None
+        ring_step(state, kk, vv, rank, src, world, layout, is_causal, scale, attn_fn, merge_fn, row)
+        _mark(row, "wait")
         for r in reqs:
             r.wait()
+        _mark(row, "end")
+        if trace is not None:
+            trace.append(row)
         cur, nxt = nxt, cur
-    return state.finish(q.dtype)
+    row = [] if trace is not None else None
+    _mark(row, "finish")
+    res = state.finish(q.dtype)
+    _mark(row, "end")
+    if trace is not None:
+        trace.append(row)
+    return res
 
 
 def ring_attention_virtual(
@@ -334,8 +379,8 @@ def ring_attention_backward(
     import torch.distributed as dist
 
     bwd_fn = bwd_fn or _default_bwd
-    world = dist.get_world_size(group)
-    rank = dist.get_rank(group)
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
     if scale is None:
         scale = q.shape[3] ** -0.5
     f32 = torch.float32
