@@ -1079,12 +1079,14 @@ def ring_check(T, R, _lib, dist, dev, rank, world, layout, q, k, v, go, out, lse
     rows_d, pos_d = rows.to(dev), pos.to(dev)
 
     # forward rows on the CUDA-core kernel: every sampled row is a "batch" of its own with its key count
+    # (fp32 copies of the operands: the reference is the fp32 result, as in the parity tests)
     q_rows = q[0][:, rows_d].permute(1, 0, 2).unsqueeze(2).contiguous()            # (rows, Hq, 1, D)
-    ke, ve = kg.expand(n_rows, Hkv, S, D), vg.expand(n_rows, Hkv, S, D)            # batch stride 0
-    want_o, want_l = T.sdpa_forward(q_rows, ke, ve, scale=scale, kv_lens=(pos_d + 1).to(torch.int32),
+    ke, ve = kg.float().expand(n_rows, Hkv, S, D), vg.float().expand(n_rows, Hkv, S, D)   # batch stride 0
+    want_o, want_l = T.sdpa_forward(q_rows.float(), ke, ve, scale=scale, kv_lens=(pos_d + 1).to(torch.int32),
                                     force_path=_lib.PATH_GENERIC)
     torch.cuda.synchronize()
     generic_path = T.ops.last_plan.get("path")
+    del ke, ve
     got_o = out[0][:, rows_d].permute(1, 0, 2)                                    # (rows, Hq, D)
     got_l = lse[0][:, rows_d].permute(1, 0)
     err_o = (got_o.float() - want_o[:, :, 0].float()).abs().max().item()
