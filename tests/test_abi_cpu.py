@@ -66,8 +66,16 @@ def _plan(p):
 def test_planner_picks_the_expected_kernel():
     rc, plan = _plan(_params(B=4, Hq=32, Hkv=8, L=4096, S=4096))
     assert rc == 0 and plan.path == _lib.PATH_PREFILL
-    assert plan.block_m == 256 and plan.block_n == 128 and plan.threads == 320
-    assert plan.grid_x == 16 * 32 * 4 and plan.smem_bytes > 190 * 1024 and plan.workspace_bytes == 0
+    # 16 * 32 * 4 = 2048 items of two 128-row tiles at head dim 128: the persistent form, one CTA per SM; 16 bytes
+    # of (optional) scratch hold the counter the items are drawn from
+    assert plan.block_m == 256 and plan.block_n == 128 and plan.threads == 512
+    assert plan.grid_x == 148 and 190 * 1024 < plan.smem_bytes <= 195 * 1024 and plan.workspace_bytes == 16
+    # fewer than three items per SM, or head dim 64: one item per CTA, no scratch
+    rc, small = _plan(_params(B=1, Hq=32, Hkv=8, L=2048, S=2048))
+    assert rc == 0 and small.path == _lib.PATH_PREFILL and small.threads == 320
+    assert small.grid_x == 8 * 32 and small.workspace_bytes == 0
+    rc, d64 = _plan(_params(B=4, Hq=32, Hkv=8, L=4096, S=4096, E=64, Dv=64))
+    assert rc == 0 and d64.path == _lib.PATH_PREFILL and d64.threads == 320 and d64.grid_x == 16 * 32 * 4
     rc, plan = _plan(_params(B=64, Hq=32, Hkv=8, L=1, S=8192))
     assert rc == 0 and plan.path == _lib.PATH_DECODE and plan.launches == 2
     assert plan.workspace_bytes == 64 * 32 * plan.kv_splits * (128 + 2) * 4

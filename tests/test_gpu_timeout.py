@@ -66,14 +66,17 @@ def _run_child(extra_env):
     return json.loads(line[len("RESULT "):])
 
 
-def test_a_wait_that_runs_out_is_reported_and_the_context_survives():
-    res = _run_child({"B200_SDPA_WAIT_LIMIT": "64"})
+@pytest.mark.parametrize("form", ["per_cta", "persistent"])
+def test_a_wait_that_runs_out_is_reported_and_the_context_survives(form):
+    # both forms of the prefill kernel (one item per CTA; persistent CTAs) have the same give-up path
+    res = _run_child({"B200_SDPA_WAIT_LIMIT": "64", "B200_SDPA_PREFILL": form})
     assert res["grid"][0] == 1 and res["prefill_launches"] == 1          # one CTA of the tensor-core kernel
     assert "device status 10" in res["status"] and "gave up" in res["status"], res
     assert res["torch_ok"] and res["generic_max_abs"] <= 1e-5, res       # the context kept working
 
 
-def test_the_same_call_with_the_default_limit_is_correct():
-    res = _run_child({})
+@pytest.mark.parametrize("form", ["per_cta", "persistent"])
+def test_the_same_call_with_the_default_limit_is_correct(form):
+    res = _run_child({"B200_SDPA_PREFILL": form})
     assert res["status"] == "ok" and res["prefill_launches"] == 1, res
     assert res["max_abs"] <= 2e-2, res

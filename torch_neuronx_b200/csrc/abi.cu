@@ -322,7 +322,7 @@ int b200_sdpa_fwd(const B200SdpaParams* params, void* stream) {
     bool unused = false;
     path = prefill_eligible(p, params->dtype, &unused) ? B200_SDPA_PATH_PREFILL : B200_SDPA_PATH_GENERIC;
   }
-  if (path == B200_SDPA_PATH_PREFILL) return launch_prefill(p, params->dtype, st);
+  if (path == B200_SDPA_PATH_PREFILL) return launch_prefill(p, params->dtype, params->workspace, params->workspace_bytes, st);
   return launch_generic(p, params->dtype, st);
 }
 

@@ -93,9 +93,14 @@ int launch_decode_partial_mma(const Problem& p, int dtype, int chunk, int nsplit
                               cudaStream_t stream);
 int launch_decode_static(const Problem& p, int dtype, int kv_chunk, cudaStream_t stream);
 
-int launch_prefill(const Problem& p, int dtype, cudaStream_t stream);
+// `workspace` (optional, >= 4 bytes): the counter from which the persistent CTAs draw their work items
+int launch_prefill(const Problem& p, int dtype, void* workspace, uint64_t workspace_bytes, cudaStream_t stream);
 int plan_prefill(const Problem& p, int dtype, B200SdpaPlan* plan);
 bool prefill_eligible(const Problem& p, int dtype, bool* alignment_only_failure);
+// persistent form of the prefill kernel (prefill_persistent_sm100.cu): head dimension 128, large problems
+bool prefill_persistent_wanted(const Problem& p);
+void plan_prefill_persistent(const Problem& p, B200SdpaPlan* plan);
+int launch_prefill_persistent(const Problem& p, int dtype, void* workspace, uint64_t workspace_bytes, cudaStream_t stream);
 // unequal head dimensions (E = 192, Dv = 128): prefill_wide_sm100.cu
 bool prefill_wide_eligible(const Problem& p, int dtype, bool* alignment_only_failure);
 int plan_prefill_wide(const Problem& p, int dtype, B200SdpaPlan* plan);

@@ -1,5 +1,7 @@
 // FlashAttention-style prefill kernel for sm_100a: TMA -> shared memory ->
-// tcgen05 tensor cores with accumulators in tensor memory (TMEM).
+// tcgen05 tensor cores with accumulators in tensor memory (TMEM).  One work item per CTA; large
+// problems at head dimension 128 run the persistent form of the same kernel
+// (prefill_persistent_sm100.cu), which produces the same bits.
 //
 // One CTA owns 256 query rows of one (batch, query head): two 128-row tiles
 // that take turns on the tensor cores while the other one is in its softmax.
@@ -671,6 +673,10 @@ bool prefill_eligible(const Problem& p, int dtype, bool* alignment_only_failure)
 int plan_prefill(const Problem& p, int dtype, B200SdpaPlan* plan) {
   if (p.E > 128) return plan_prefill_wide(p, dtype, plan);
   if (!prefill_eligible(p, dtype, nullptr)) return B200_SDPA_ERR_UNSUPPORTED;
+  if (prefill_persistent_wanted(p)) {
+    plan_prefill_persistent(p, plan);
+    return B200_SDPA_OK;
+  }
   const int pair_heads = pair_heads_mode(p);
   const int rows = pair_heads ? kBlockM : kRowsPerCta;
   const int n_qblk = (p.L + rows - 1) / rows;
@@ -689,9 +695,10 @@ int plan_prefill(const Problem& p, int dtype, B200SdpaPlan* plan) {
   return B200_SDPA_OK;
 }
 
-int launch_prefill(const Problem& p, int dtype, cudaStream_t stream) {
+int launch_prefill(const Problem& p, int dtype, void* workspace, uint64_t workspace_bytes, cudaStream_t stream) {
   if (p.E > 128) return launch_prefill_wide(p, dtype, stream);
   if (!prefill_eligible(p, dtype, nullptr)) return B200_SDPA_ERR_UNSUPPORTED;
+  if (prefill_persistent_wanted(p)) return launch_prefill_persistent(p, dtype, workspace, workspace_bytes, stream);
   const bool bf16 = dtype == B200_SDPA_BF16;
   if (p.bias != nullptr) {
     if (p.E == 128) return bf16 ? launch_variant<128, true, true>(p, stream) : launch_variant<128, false, true>(p, stream);

@@ -74,23 +74,36 @@ constexpr long long kDrainCycles = 1LL << 26;
 
 __device__ __forceinline__ bool wait_clocked(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                              long long limit_cycles) {
-  if (limit_cycles >= kLiteralLimit) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    uint32_t spins = 0;
-    while (true) {
-      if (mbar_try_wait(bar, parity)) return true;
-      if ((++spins & 15u) == 0u) {
-        if (*abort_flag != 0) return false;
-        if (clock64() - t0 > limit_cycles) {
-          *abort_flag = 1;
-          return false;
-        }
+  // production limits: suspending polls, the clock read every 16th; literal limits: non-suspending polls,
+  // the clock read after every one (one loop for both, to keep the many wait sites small)
+  const bool literal = limit_cycles < kLiteralLimit;
+  if (literal ? mbar_test_wait(bar, parity) : mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while (true) {
+    if (literal ? mbar_test_wait(bar, parity) : mbar_try_wait(bar, parity)) return true;
+    if (literal || (++spins & 15u) == 0u) {
+      if (*abort_flag != 0) return false;
+      if (clock64() - t0 > limit_cycles) {
+        *abort_flag = 1;
+        return false;
       }
     }
   }
+}
+
+// The same bounded wait for roles that are in no hurry (an epilogue waiting for a whole work item to
+// finish): between polls the thread sleeps, so that it does not take issue slots from the warps that
+// are on the critical path.
+#ifndef B200_RELAXED_SLEEP_NS
+#define B200_RELAXED_SLEEP_NS 256
+#endif
+__device__ __forceinline__ bool wait_relaxed(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                             long long limit_cycles) {
+  if (mbar_test_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (true) {
+    if (B200_RELAXED_SLEEP_NS > 0) __nanosleep(B200_RELAXED_SLEEP_NS);
     if (mbar_test_wait(bar, parity)) return true;
     if (*abort_flag != 0) return false;
     if (clock64() - t0 > limit_cycles) {
