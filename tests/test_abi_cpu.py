@@ -312,3 +312,18 @@ def test_bias_planning():
     assert rc == 0 and plan.path == _lib.PATH_GENERIC
     rc, plan = plan_with([8 * L * S, L * S, S, 1], E=192, Dv=128)
     assert rc == 0 and plan.path == _lib.PATH_PREFILL       # the wide kernel reads it the same way
+
+
+def test_cpp_operator_layer_loads_and_registers():
+    """The C++ operator layer is an in-tree shared library next to the kernel library; loading it registers the
+    CUDA kernels of the two ATen ops and the status-word accessor (no GPU needed to load)."""
+    import torch
+
+    import torch_neuronx_b200 as T
+
+    assert os.path.exists(_lib.OPS_LIB_PATH), "build it with python -m torch_neuronx_b200.build"
+    assert T.ops.native_op_layer()
+    assert hasattr(torch.ops.b200_sdpa_native, "status_word")
+    q = torch.randn(1, 2, 8, 16)
+    with pytest.raises(NotImplementedError):        # CPU tensors never reach the CUDA kernel
+        torch.ops.aten._scaled_dot_product_fused_attention_overrideable(q, q, q)

@@ -227,5 +227,5 @@ def test_long_context_ring_at_full_size_on_two_gpus(tmp_path):
     for r in range(2):
         res = torch.load(tmp_path / f"r{r}.pt")
         assert res["ok"], res
-        assert res["max_abs_out"] <= 2e-2 and res["max_abs_lse"] <= 1e-3 and res["guard_diff"] > 5e-2, res
+        assert res["max_abs_out"] <= 2e-2 and res["max_abs_lse"] <= 1e-3 and res["guard_diff"] > 0.1, res
         assert res["max_abs_out_cpu"] <= 2e-2 and res["max_abs_lse_cpu"] <= 1e-3, res

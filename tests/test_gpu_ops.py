@@ -254,3 +254,66 @@ def test_traced_training_step_runs_the_same_kernels():
     assert torch.equal(loss, eager)
     for t, w in zip((q, k, v), want):
         assert torch.equal(t.grad, w)
+
+
+def test_aten_ops_are_served_by_the_cpp_layer_with_upstream_error_behaviour():
+    # upstream checks in its native dispatcher (NeuronDispatcher.cpp:2380-2458); same messages and classes here
+    import torch_neuronx_b200 as T
+
+    assert T.ops.native_op_layer(), "libb200_sdpa_ops.so was not built / loaded"
+    op = torch.ops.aten._scaled_dot_product_fused_attention_overrideable
+    q, k, v = (t.to(DEV) for t in make_qkv(5, 1, 4, 2, 64, 64, 64, torch.bfloat16))
+    mask = torch.ones(64, 64, dtype=torch.bool, device=DEV)
+    with pytest.raises(RuntimeError, match="Explicit attn_mask should not be set when is_causal=True"):
+        op(q, k, v, mask, 0.0, True)
+    with pytest.raises(NotImplementedError, match="dropout_p != 0 is not supported"):
+        op(q, k, v, None, 0.1)
+    with pytest.raises(ValueError, match=r"outside \[0, 1\]"):
+        op(q, k, v, None, 1.5)
+    with pytest.raises(NotImplementedError, match="return_debug_mask=True is not supported"):
+        op(q, k, v, None, 0.0, False, True)
+    with pytest.raises(RuntimeError, match="Number of heads in key and value must divide the number of heads in query"):
+        op(q[:, :3], k, v)
+    with pytest.raises(RuntimeError, match="same dtype"):
+        op(q, k.float(), v)
+    with pytest.raises(RuntimeError, match="must be 4D tensors"):
+        op(q[0], k[0], v[0])
+    # float64 is computed in float32 and cast back; a bool mask becomes 0 / -inf
+    qd, kd, vd = (t.double() for t in (q, k, v))
+    out = op(qd, kd, vd, mask.tril())[0]
+    assert out.dtype == torch.float64
+    ref, _ = O.sdpa_forward(qd.cpu().float(), kd.cpu().float(), vd.cpu().float(), is_causal=True)
+    assert (out.cpu().float() - ref).abs().max().item() <= 1e-5
+    # the status word is the one the Python layer reads
+    assert T.ops._status_word(0).data_ptr() == torch.ops.b200_sdpa_native.status_word(0).data_ptr()
+
+
+def test_the_native_layer_runs_from_several_threads():
+    # dispatcher kernels run without the interpreter lock; concurrent callers on their own streams get their own
+    # scratch from the caching allocator
+    import threading
+
+    import torch_neuronx_b200  # noqa: F401
+
+    op = torch.ops.aten._scaled_dot_product_fused_attention_overrideable
+    q, k, v = make_qkv(6, 2, 8, 2, 256, 256, 128, torch.bfloat16)
+    ref, _ = O.sdpa_forward(q, k, v, is_causal=True, compute_dtype=torch.float32)
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    errs = [None] * 4
+
+    def work(i):
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.default_stream())
+        with torch.cuda.stream(s):
+            worst = 0.0
+            for _ in range(50):
+                out = op(qd, kd, vd, None, 0.0, True)[0]
+                worst = max(worst, (out.float().cpu() - ref).abs().max().item())
+        errs[i] = worst
+
+    threads = [threading.Thread(target=work, args=(i,)) for i in range(4)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert all(e is not None and e <= HALF_MAX_ABS for e in errs), errs

@@ -18,6 +18,7 @@ import threading
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libb200_sdpa.so")
+OPS_LIB_PATH = os.path.join(HERE, "libb200_sdpa_ops.so")   # C++ operator layer (dispatcher kernels of the ATen ops)
 
 ABI_VERSION = 5
 STATIC_SCRATCH_BYTES = 16 << 20  # B200_SDPA_STATIC_SCRATCH_BYTES
@@ -230,6 +231,30 @@ def load():
             raise RuntimeError(f"libb200_sdpa.so has ABI version {got}, this package expects {ABI_VERSION}")
         _lib = lib
     return _lib
+
+
+_ops_loaded = None
+
+
+def load_ops() -> bool:
+    """Load the C++ operator layer (``csrc_ops/aten_ops.cpp``): it registers the CUDA kernels of the two
+    ATen ops with the dispatcher, as upstream's native dispatcher does
+    (``torch_neuronx/csrc/core/dispatch/NeuronDispatcher.cpp:2370-2582``).  Returns False when the
+    library has not been built; the same kernels are then reached through the ctypes binding."""
+    global _ops_loaded
+    if _ops_loaded is not None:
+        return _ops_loaded
+    with _lock:
+        if _ops_loaded is None:
+            if os.path.exists(OPS_LIB_PATH) and os.path.exists(LIB_PATH):
+                import torch
+
+                C.CDLL(LIB_PATH, mode=C.RTLD_GLOBAL)   # the layer links against it by name
+                torch.ops.load_library(OPS_LIB_PATH)
+                _ops_loaded = True
+            else:
+                _ops_loaded = False
+    return _ops_loaded
 
 
 def strerror(code: int) -> str:

@@ -1,4 +1,6 @@
-"""In-tree build of ``libb200_sdpa.so`` (sm_100a only) with plain ``nvcc``.
+"""In-tree build of ``libb200_sdpa.so`` (sm_100a only) with plain ``nvcc``, and of the C++
+operator layer ``libb200_sdpa_ops.so`` (``csrc_ops/aten_ops.cpp``: the dispatcher kernels of the
+two ATen ops, linked against the first library and against torch) with ``g++``.
 
 ``python -m torch_neuronx_b200.build`` compiles every ``csrc/*.cu`` to an object
 file and links them into one shared library next to this file.  Objects are
@@ -23,6 +25,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ_DIR = os.path.join(CSRC, "build")
 LIB_PATH = os.path.join(HERE, "libb200_sdpa.so")
+OPS_SRC = os.path.join(HERE, "csrc_ops", "aten_ops.cpp")
+OPS_LIB_PATH = os.path.join(HERE, "libb200_sdpa_ops.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -94,9 +98,38 @@ def build(verbose: bool = False, force: bool = False) -> str:
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
+    build_ops(stamps, force=force or rebuilt, verbose=verbose)
     with open(stamp_path, "w") as f:
         json.dump(stamps, f)
     return LIB_PATH
+
+
+def build_ops(stamps: dict, force: bool = False, verbose: bool = False) -> str:
+    """Build (if needed) the C++ operator layer against the installed torch; returns its path."""
+    import torch
+    from torch.utils import cpp_extension
+
+    gxx = os.environ.get("CXX") or shutil.which("g++")
+    if gxx is None:
+        raise RuntimeError("g++ not found; set CXX")
+    torch_lib = os.path.join(os.path.dirname(torch.__file__), "lib")
+    cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    flags = ["-O2", "-std=c++17", "-fPIC", "-shared", "-Wno-deprecated-declarations",
+             f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}"]
+    for inc in cpp_extension.include_paths() + [os.path.join(cuda_home, "include")]:
+        flags += ["-isystem", inc]
+    key = _digest([OPS_SRC, os.path.join(HERE, "..", "include", "b200_sdpa.h")], " ".join(flags) + torch.__version__)
+    if not force and stamps.get("aten_ops.cpp") == key and os.path.exists(OPS_LIB_PATH):
+        return OPS_LIB_PATH
+    cmd = [gxx] + flags + [OPS_SRC, "-o", OPS_LIB_PATH, f"-L{torch_lib}", "-ltorch", "-ltorch_cpu", "-lc10", "-lc10_cuda",
+                           f"-L{HERE}", "-lb200_sdpa", "-Wl,-rpath,$ORIGIN"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"g++ failed for aten_ops.cpp:\n{res.stdout}\n{res.stderr}")
+    if verbose:
+        sys.stderr.write(f"--- aten_ops.cpp\n{res.stderr}\n")
+    stamps["aten_ops.cpp"] = key
+    return OPS_LIB_PATH
 
 
 if __name__ == "__main__":

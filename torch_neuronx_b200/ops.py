@@ -54,9 +54,13 @@ def _device_index(t: torch.Tensor) -> int:
 
 
 def _status_word(dev: int) -> torch.Tensor:
+    """The device's status word (int32[4]); one per device, shared with the C++ operator layer."""
     w = _status_words.get(dev)
     if w is None:
-        w = torch.zeros(4, dtype=torch.int32, device=torch.device("cuda", dev))
+        if _lib.load_ops():
+            w = torch.ops.b200_sdpa_native.status_word(dev)
+        else:
+            w = torch.zeros(4, dtype=torch.int32, device=torch.device("cuda", dev))
         _status_words[dev] = w
     return w
 
@@ -103,9 +107,12 @@ def release_workspaces() -> None:
 def check_device_status(device=None) -> None:
     """Synchronise and raise if any kernel reported a device-side error (a bounded
     wait that gave up).  Cheap enough for tests; not called on the hot path."""
-    devs = list(_status_words) if device is None else [torch.device(device).index or 0]
+    if device is None:
+        devs = list(range(torch.cuda.device_count())) if _lib.load_ops() else list(_status_words)
+    else:
+        devs = [torch.device(device).index or 0]
     for dev in devs:
-        w = _status_words.get(dev)
+        w = _status_word(dev) if _lib.load_ops() else _status_words.get(dev)
         if w is None:
             continue
         vals = w.cpu().tolist()
@@ -838,14 +845,22 @@ def register_aten_override() -> None:
     if _ATEN_IMPL is not None:
         return
     lib = torch.library.Library("aten", "IMPL")
-    lib.impl("_scaled_dot_product_fused_attention_overrideable", fused_attention_overrideable, "CUDA")
-    lib.impl(
-        "_scaled_dot_product_fused_attention_overrideable_backward", fused_attention_overrideable_backward, "CUDA"
-    )
+    if not _lib.load_ops():
+        # the C++ operator layer (which registers these two kernels natively, so that a call runs without
+        # the interpreter lock) has not been built: the same kernels through the ctypes binding
+        lib.impl("_scaled_dot_product_fused_attention_overrideable", fused_attention_overrideable, "CUDA")
+        lib.impl(
+            "_scaled_dot_product_fused_attention_overrideable_backward", fused_attention_overrideable_backward, "CUDA"
+        )
     # torch ships a meta kernel for the forward op only; tracing and DTensor's sharding propagation need
     # the backward's output shapes too
     lib.impl("_scaled_dot_product_fused_attention_overrideable_backward", _overrideable_backward_meta, "Meta")
     _ATEN_IMPL = lib
+
+
+def native_op_layer() -> bool:
+    """Whether the ATen ops are served by the C++ operator layer (``libb200_sdpa_ops.so``)."""
+    return _lib.load_ops()
 
 
 def _supported_by_fused_path(query, key, value, attn_mask, dropout_p, is_causal) -> bool:
