@@ -33,7 +33,7 @@
 extern "C" {
 #endif
 
-#define B200_SDPA_ABI_VERSION 5
+#define B200_SDPA_ABI_VERSION 6
 
 typedef enum b200_sdpa_status {
   B200_SDPA_OK = 0,
@@ -174,7 +174,25 @@ typedef struct B200SdpaParams {
   int32_t rope_stride;
   int32_t rope_interleaved;
   int32_t rope_positions;
-  int32_t reserved0;      /* keep 0                                                    */
+
+  /* Accumulating form (one step of a ring over key/value blocks): instead of writing `out` and
+   * `lse`, the kernel folds this call's result into a running fp32 result over earlier key
+   * blocks for the same query rows,
+   *     lse' = logaddexp(acc_lse, lse)
+   *     acc' = acc * exp(acc_lse - lse') + result * exp(lse - lse')
+   * in its epilogue, without the partial ever leaving the chip in the storage dtype.
+   * acc_mode 0 = off (acc, acc_lse ignored); 1 = first block (acc, acc_lse are overwritten);
+   * 2 = fold into acc, acc_lse.  acc is (B, Hq, L, Dv) fp32 with unit inner stride and
+   * 16-byte aligned rows, acc_lse (B, Hq, L) fp32; strides in elements.  `out` and `lse` may be
+   * NULL then.  Served by the persistent tensor-core prefill kernel only (f16/bf16, E = Dv =
+   * 128); b200_sdpa_query_plan() answers B200_SDPA_ERR_UNSUPPORTED otherwise and the caller
+   * merges with b200_sdpa_merge() instead.  Replaces the (out, lse) merge upstream's ring does
+   * between per-block calls (torch_neuronx/distributed/tensor/cp_ring_handler.py:308-318).  */
+  int32_t acc_mode;
+  float* acc;
+  float* acc_lse;
+  int64_t acc_stride[3];      /* (B, H, L)                                             */
+  int64_t acc_lse_stride[3];
 } B200SdpaParams;
 
 /* What the library would do (or did) for a parameter block. */
@@ -196,9 +214,10 @@ typedef struct B200SdpaPlan {
  * queries (one ring step):
  *     lse' = logaddexp(acc_lse, part_lse)
  *     acc' = acc * exp(acc_lse - lse') + part * exp(part_lse - lse')
- * `acc` (fp32, contiguous (rows, Dv)) and `acc_lse` (fp32, (rows)) are updated in
- * place; when `final_out` is non-NULL the merged rows are also written there in
- * `dtype` with the given strides.  rows = B * Hq * L.
+ * `acc` (fp32, (B, Hq, L, Dv) with unit inner stride) and `acc_lse` (fp32, (B, Hq, L)) are
+ * updated in place -- they may be views of larger accumulators, hence the strides; when
+ * `final_out` is non-NULL the merged rows are also written there in `dtype` with the given
+ * strides.
  *
  * Replaces the (out, lse) merge that upstream's templated ring attention does in
  * Python between per-block calls of the op
@@ -209,8 +228,8 @@ typedef struct B200SdpaMergeParams {
   int32_t dtype;           /* dtype of part and final_out                              */
   int32_t device;
   int32_t first;           /* != 0: acc is uninitialised, just take the partial        */
-  float* acc;              /* (B, Hq, L, Dv) fp32 contiguous                            */
-  float* acc_lse;          /* (B, Hq, L) fp32 contiguous                                */
+  float* acc;              /* (B, Hq, L, Dv) fp32, unit inner stride                    */
+  float* acc_lse;          /* (B, Hq, L) fp32                                           */
   const void* part;        /* (B, Hq, L, Dv) in dtype                                   */
   const float* part_lse;   /* (B, Hq, L) fp32                                           */
   void* final_out;         /* optional (B, Hq, L, Dv) in dtype                          */
@@ -218,6 +237,8 @@ typedef struct B200SdpaMergeParams {
   int64_t part_lse_stride[3];
   int64_t final_stride[4];
   int32_t B, Hq, L, Dv;
+  int64_t acc_stride[3];      /* (B, H, L) element strides of acc                      */
+  int64_t acc_lse_stride[3];
 } B200SdpaMergeParams;
 
 /*

@@ -327,3 +327,30 @@ def test_cpp_operator_layer_loads_and_registers():
     q = torch.randn(1, 2, 8, 16)
     with pytest.raises(NotImplementedError):        # CPU tensors never reach the CUDA kernel
         torch.ops.aten._scaled_dot_product_fused_attention_overrideable(q, q, q)
+
+
+def test_accumulating_form_planning():
+    """The accumulating form (one ring step folded into a running fp32 result) is served by the persistent
+    tensor-core prefill kernel only; everything else is declined so that the caller merges separately."""
+    acc = dict(acc_mode=2, acc=0x7F5000000000, acc_lse=0x7F5100000000)
+
+    def plan_acc(**kw):
+        p = _params(**{**dict(B=1, Hq=8, Hkv=2, L=512, S=512), **acc, **kw})
+        p.acc_stride[:] = [8 * 512 * 128, 512 * 128, 128]
+        p.acc_lse_stride[:] = [8 * 512, 512, 1]
+        return _plan(p)
+
+    rc, plan = plan_acc()
+    assert rc == 0 and plan.path == _lib.PATH_PREFILL and plan.threads == 512      # persistent, whatever the size
+    assert plan_acc(E=64, Dv=64)[0] == _lib.ERR_UNSUPPORTED
+    assert plan_acc(dtype=_lib.F32)[0] == _lib.ERR_UNSUPPORTED
+    assert plan_acc(L=1)[0] == 0                                                   # one row still goes to that kernel
+    assert plan_acc(acc=None)[0] == _lib.ERR_NULL
+    assert plan_acc(acc=0x7F5000000004)[0] == _lib.ERR_UNSUPPORTED                 # rows not 16-byte aligned
+    assert plan_acc(acc_mode=3)[0] == _lib.ERR_UNSUPPORTED
+    assert plan_acc(force_path=_lib.PATH_GENERIC)[0] == _lib.ERR_UNSUPPORTED
+    p = _params(B=1, Hq=8, Hkv=2, L=512, S=512, **acc)
+    p.out = None                                                                   # no output tensor in this form
+    p.acc_stride[:] = [8 * 512 * 128, 512 * 128, 128]
+    p.acc_lse_stride[:] = [8 * 512, 512, 1]
+    assert _plan(p)[0] == 0

@@ -109,3 +109,64 @@ def test_persistent_form_without_scratch_takes_items_in_a_fixed_order():
     assert rc == _lib.OK, _lib.strerror(rc)
     torch.cuda.synchronize()
     assert torch.equal(out.cpu(), ref_o) and torch.equal(lse.cpu(), ref_l)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_accumulating_form_folds_key_blocks_into_a_running_result(causal):
+    """Three key blocks attended one after the other with the merge done in the kernel's epilogue give the
+    attention over all keys (the ring step, ``cp_ring_handler.py:308-318``); rows that see nothing in a block
+    (causal: the block lies after them) keep what they had."""
+    import torch_neuronx_b200 as T
+    from oracle import sdpa_oracle as O
+
+    B, Hq, Hkv, L, S, D = 2, 8, 2, 384, 3 * 256, 128
+    q, k, v = make_qkv(21, B, Hq, Hkv, L, S, D, torch.bfloat16)
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    big = torch.full((B, Hq, L + 64, D), float("nan"), dtype=torch.float32, device=DEV)   # the accumulator is a view
+    acc, acc_lse = big[:, :, 32:32 + L], torch.full((B, Hq, L), float("nan"), dtype=torch.float32, device=DEV)
+    q_off = 300                                                     # global position of query row 0
+    T.reset_launch_counts()
+    for blk in range(3):
+        ok = T.sdpa_forward_accumulate(qd, kd[:, :, blk * 256:(blk + 1) * 256], vd[:, :, blk * 256:(blk + 1) * 256], acc,
+                                       acc_lse, first=blk == 0, is_causal=causal, scale=0.1, q_offset=q_off,
+                                       k_offset=blk * 256)
+        assert ok and T.ops.last_plan["threads"] == 512
+    torch.cuda.synchronize()
+    T.check_device_status()
+    assert T.launch_counts()["prefill"] == 3 and T.launch_counts()["merge"] == 0
+    ref_o, ref_l = O.sdpa_forward(q, k, v, is_causal=causal, scale=0.1, q_offset=q_off, compute_dtype=torch.float32)
+    assert torch.isnan(big[:, :, :32]).all() and torch.isnan(big[:, :, 32 + L:]).all()       # nothing outside the view
+    err = (acc.cpu() - ref_o).abs()
+    assert err.max().item() <= 2e-2 and err.mean().item() <= 2e-3, err.max().item()
+    assert (acc_lse.cpu() - ref_l).abs().max().item() <= 1e-3
+    # what the accumulating kernel does not serve is declined, not half done
+    q64, k64, v64 = (t.to(DEV) for t in make_qkv(22, 1, 4, 4, 256, 256, 64, torch.bfloat16))
+    a64 = torch.zeros(1, 4, 256, 64, device=DEV)
+    assert T.sdpa_forward_accumulate(q64, k64, v64, a64, torch.zeros(1, 4, 256, device=DEV), first=True) is False
+
+
+@pytest.mark.parametrize("layout", ["zigzag", "contiguous"])
+def test_ring_with_the_merge_fused_into_the_attention_kernel(layout):
+    """The ring driver with every step folded into the accumulator by the attention kernel itself (opt-in):
+    four virtual ranks on one GPU against full attention, no merge kernel launched."""
+    import torch_neuronx_b200 as T
+    from oracle import sdpa_oracle as O
+
+    world, S = 4, 2048
+    q, k, v = make_qkv(31, 1, 8, 2, S, S, 128, torch.bfloat16)
+    qs = [T.shard_sequence(q, r, world, layout).contiguous().to(DEV) for r in range(world)]
+    ks = [T.shard_sequence(k, r, world, layout).contiguous().to(DEV) for r in range(world)]
+    vs = [T.shard_sequence(v, r, world, layout).contiguous().to(DEV) for r in range(world)]
+    os.environ["B200_SDPA_RING_FUSED"] = "1"
+    try:
+        T.reset_launch_counts()
+        outs, lses, calls = T.ring_attention_virtual(qs, ks, vs, is_causal=True, layout=layout)
+        torch.cuda.synchronize()
+        T.check_device_status()
+    finally:
+        os.environ.pop("B200_SDPA_RING_FUSED", None)
+    counts = T.launch_counts()
+    assert counts["merge"] == 0 and counts["prefill"] == calls, (counts, calls)
+    out = T.unshard_sequence([o.cpu() for o in outs], layout)
+    lse = T.unshard_sequence([l.unsqueeze(-1).cpu() for l in lses], layout).squeeze(-1)
+    check_against_oracle(q, k, v, out, lse, is_causal=True, tag=f"fused ring {layout}")

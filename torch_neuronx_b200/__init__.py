@@ -26,6 +26,7 @@ from .ops import (
     set_mask_recognition,
     sdpa_backward,
     sdpa_forward,
+    sdpa_forward_accumulate,
 )
 from .masks import MaskStructure, classify_mask
 from .ring import (
@@ -49,5 +50,5 @@ __all__ = [
     "local_units", "merge_partials", "native_multi_head_attn_mid", "paged_decode", "partition_units", "register_aten_override", "reset_launch_counts",
     "ring_attention", "ring_attention_backward", "ring_attention_backward_virtual", "ring_attention_virtual", "scaled_dot_product_attention",
     "scaled_dot_product_attention_backward_kernel", "scaled_dot_product_attention_kernel", "sdpa_backward",
-    "sdpa_forward", "set_mask_recognition", "shard_sequence", "unshard_sequence",
+    "sdpa_forward", "sdpa_forward_accumulate", "set_mask_recognition", "shard_sequence", "unshard_sequence",
 ]

@@ -20,7 +20,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libb200_sdpa.so")
 OPS_LIB_PATH = os.path.join(HERE, "libb200_sdpa_ops.so")   # C++ operator layer (dispatcher kernels of the ATen ops)
 
-ABI_VERSION = 5
+ABI_VERSION = 6
 STATIC_SCRATCH_BYTES = 16 << 20  # B200_SDPA_STATIC_SCRATCH_BYTES
 
 # b200_sdpa_status
@@ -90,7 +90,11 @@ class Params(C.Structure):
         ("rope_stride", C.c_int32),
         ("rope_interleaved", C.c_int32),
         ("rope_positions", C.c_int32),
-        ("reserved0", C.c_int32),
+        ("acc_mode", C.c_int32),
+        ("acc", C.c_void_p),
+        ("acc_lse", C.c_void_p),
+        ("acc_stride", C.c_int64 * 3),
+        ("acc_lse_stride", C.c_int64 * 3),
     ]
 
 
@@ -133,6 +137,8 @@ class MergeParams(C.Structure):
         ("Hq", C.c_int32),
         ("L", C.c_int32),
         ("Dv", C.c_int32),
+        ("acc_stride", C.c_int64 * 3),
+        ("acc_lse_stride", C.c_int64 * 3),
     ]
 
 
@@ -246,14 +252,21 @@ def load_ops() -> bool:
         return _ops_loaded
     with _lock:
         if _ops_loaded is None:
+            _ops_loaded = False
             if os.path.exists(OPS_LIB_PATH) and os.path.exists(LIB_PATH):
                 import torch
 
-                C.CDLL(LIB_PATH, mode=C.RTLD_GLOBAL)   # the layer links against it by name
-                torch.ops.load_library(OPS_LIB_PATH)
-                _ops_loaded = True
-            else:
-                _ops_loaded = False
+                try:
+                    C.CDLL(LIB_PATH, mode=C.RTLD_GLOBAL)   # the layer links against it by name
+                    torch.ops.load_library(OPS_LIB_PATH)
+                    _ops_loaded = True
+                except OSError as exc:
+                    # a library from an interrupted or outdated build: importing the package must still work
+                    # (the build itself runs as a module of it); any compute call will report the real problem
+                    import warnings
+
+                    warnings.warn(f"libb200_sdpa_ops.so could not be loaded ({exc}); rebuild with "
+                                  "`python -m torch_neuronx_b200.build`")
     return _ops_loaded
 
 

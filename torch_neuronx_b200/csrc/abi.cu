@@ -17,7 +17,9 @@ int validate(const B200SdpaParams* a, Problem* p) {
   if (a->B <= 0 || a->Hq <= 0 || a->Hkv <= 0 || a->L <= 0 || a->S < 0 || a->E <= 0 || a->Dv <= 0)
     return B200_SDPA_ERR_SHAPE;
   if (a->Hq % a->Hkv != 0) return B200_SDPA_ERR_SHAPE;
-  if (a->q == nullptr || a->out == nullptr) return B200_SDPA_ERR_NULL;
+  if (a->acc_mode < 0 || a->acc_mode > 2) return B200_SDPA_ERR_UNSUPPORTED;
+  if (a->q == nullptr || (a->out == nullptr && a->acc_mode == 0)) return B200_SDPA_ERR_NULL;
+  if (a->acc_mode != 0 && (a->acc == nullptr || a->acc_lse == nullptr)) return B200_SDPA_ERR_NULL;
   if (a->S > 0 && (a->k == nullptr || a->v == nullptr)) return B200_SDPA_ERR_NULL;
   if (a->bias != nullptr && a->bias_dtype != B200_SDPA_F32 && a->bias_dtype != B200_SDPA_F16 &&
       a->bias_dtype != B200_SDPA_BF16)
@@ -66,6 +68,13 @@ int validate(const B200SdpaParams* a, Problem* p) {
   p->rope_interleaved = a->rope_interleaved != 0;
   p->rope_positions = a->rope_positions;
   if (a->rope_cos != nullptr && a->rope_positions < 1) return B200_SDPA_ERR_SHAPE;
+  p->acc_mode = a->acc_mode;
+  p->acc = a->acc;
+  p->acc_lse = a->acc_lse;
+  for (int i = 0; i < 3; ++i) {
+    p->as[i] = a->acc_stride[i];
+    p->als[i] = a->acc_lse_stride[i];
+  }
   if ((a->rope_cos == nullptr) != (a->rope_sin == nullptr)) return B200_SDPA_ERR_NULL;
   if (a->rope_cos != nullptr && (a->k_new == nullptr || a->rope_stride < a->E / 2)) return B200_SDPA_ERR_UNSUPPORTED;
   if ((a->k_new == nullptr) != (a->v_new == nullptr)) return B200_SDPA_ERR_NULL;
@@ -89,6 +98,15 @@ int choose(const B200SdpaParams* a, const Problem& p, int* path) {
   if (want != B200_SDPA_PATH_AUTO && want != B200_SDPA_PATH_GENERIC && want != B200_SDPA_PATH_PREFILL &&
       want != B200_SDPA_PATH_DECODE)
     return B200_SDPA_ERR_UNSUPPORTED;
+  if (p.acc_mode != 0) {
+    // the accumulating form exists in the persistent tensor-core prefill kernel only
+    bool unused = false;
+    if ((want != B200_SDPA_PATH_AUTO && want != B200_SDPA_PATH_PREFILL) || p.block_table != nullptr ||
+        p.k_new != nullptr || p.S < 1 || !prefill_eligible(p, a->dtype, &unused) || !prefill_accumulate_eligible(p))
+      return B200_SDPA_ERR_UNSUPPORTED;
+    *path = B200_SDPA_PATH_PREFILL;
+    return B200_SDPA_OK;
+  }
   if (p.block_table != nullptr || p.k_new != nullptr) {
     // a paged cache and the append of a new row are only understood by the split-KV decode kernel
     if ((want != B200_SDPA_PATH_AUTO && want != B200_SDPA_PATH_DECODE) || !decode_eligible(p, a->dtype))
@@ -234,6 +252,9 @@ int validate_bwd(const B200SdpaBwdParams* a, BwdProblem& bp) {
   p.rope_cos = nullptr;
   p.rope_sin = nullptr;
   p.rope_positions = 0;
+  p.acc_mode = 0;
+  p.acc = nullptr;
+  p.acc_lse = nullptr;
   if (a->force_path != B200_SDPA_PATH_AUTO && a->force_path != B200_SDPA_PATH_GENERIC &&
       a->force_path != B200_SDPA_PATH_PREFILL)
     return B200_SDPA_ERR_UNSUPPORTED;

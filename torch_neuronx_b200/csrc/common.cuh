@@ -52,6 +52,12 @@ struct Problem {
   int rope_stride;       // floats between positions
   int rope_interleaved;  // 0: pairs (i, i + D/2); 1: pairs (2i, 2i + 1)
   int rope_positions;    // rows in the cos/sin tables (positions beyond use the last row)
+  // Accumulating form (persistent prefill kernel only): fold the result into a running fp32 (acc, acc_lse)
+  // instead of writing out / lse.  0 = off, 1 = first block, 2 = merge.
+  int acc_mode;
+  float* acc;
+  float* acc_lse;
+  int64_t as[3], als[3];
 };
 
 // Backward: the forward's description (out and lse are inputs here) plus the upstream
@@ -99,6 +105,7 @@ int plan_prefill(const Problem& p, int dtype, B200SdpaPlan* plan);
 bool prefill_eligible(const Problem& p, int dtype, bool* alignment_only_failure);
 // persistent form of the prefill kernel (prefill_persistent_sm100.cu): head dimension 128, large problems
 bool prefill_persistent_wanted(const Problem& p);
+bool prefill_accumulate_eligible(const Problem& p);   // accumulating form: layout rules of (acc, acc_lse)
 void plan_prefill_persistent(const Problem& p, B200SdpaPlan* plan);
 int launch_prefill_persistent(const Problem& p, int dtype, void* workspace, uint64_t workspace_bytes, cudaStream_t stream);
 // unequal head dimensions (E = 192, Dv = 128): prefill_wide_sm100.cu

@@ -21,13 +21,14 @@ __global__ void __launch_bounds__(256) merge_kernel(const B200SdpaMergeParams m,
     const int h = static_cast<int>((row / m.L) % m.Hq);
     const int b = static_cast<int>(row / (static_cast<int64_t>(m.L) * m.Hq));
     const float lb = m.part_lse[b * m.part_lse_stride[0] + h * m.part_lse_stride[1] + i * m.part_lse_stride[2]];
+    const int64_t abase = b * m.acc_stride[0] + h * m.acc_stride[1] + i * m.acc_stride[2];
     float wa, wb, lnew;
     if (m.first) {
       wa = 0.f;
       wb = 1.f;
       lnew = lb;
     } else {
-      const float la = m.acc_lse[row];
+      const float la = m.acc_lse[b * m.acc_lse_stride[0] + h * m.acc_lse_stride[1] + i * m.acc_lse_stride[2]];
       const float mx = fmaxf(la, lb);
       if (mx == -CUDART_INF_F) {
         wa = wb = 0.f;
@@ -45,9 +46,9 @@ __global__ void __launch_bounds__(256) merge_kernel(const B200SdpaMergeParams m,
     for (int c = c0; c < c0 + 4; ++c) {
       if (c >= m.Dv) break;
       const float pv = to_f32<T>(part[pbase + c * m.part_stride[3]]);
-      const float av = m.first ? 0.f : m.acc[row * m.Dv + c];
+      const float av = m.first ? 0.f : m.acc[abase + c];
       const float r = av * wa + pv * wb;
-      m.acc[row * m.Dv + c] = r;
+      m.acc[abase + c] = r;
       if (fin != nullptr) fin[fbase + c * m.final_stride[3]] = from_f32<T>(r);
     }
     // acc_lse is only read here: several threads share a row, so the new
@@ -63,12 +64,13 @@ __global__ void __launch_bounds__(256) merge_lse_kernel(const B200SdpaMergeParam
     const int h = static_cast<int>((row / m.L) % m.Hq);
     const int b = static_cast<int>(row / (static_cast<int64_t>(m.L) * m.Hq));
     const float lb = m.part_lse[b * m.part_lse_stride[0] + h * m.part_lse_stride[1] + i * m.part_lse_stride[2]];
+    float* al = m.acc_lse + b * m.acc_lse_stride[0] + h * m.acc_lse_stride[1] + i * m.acc_lse_stride[2];
     if (m.first) {
-      m.acc_lse[row] = lb;
+      *al = lb;
     } else {
-      const float la = m.acc_lse[row];
+      const float la = *al;
       const float mx = fmaxf(la, lb);
-      m.acc_lse[row] = (mx == -CUDART_INF_F) ? -CUDART_INF_F : mx + logf(expf(la - mx) + expf(lb - mx));
+      *al = (mx == -CUDART_INF_F) ? -CUDART_INF_F : mx + logf(expf(la - mx) + expf(lb - mx));
     }
   }
 }

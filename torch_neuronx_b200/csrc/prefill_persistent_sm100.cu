@@ -79,11 +79,13 @@ template <int D> struct Cfg {
   static constexpr int kTileBytes = kBlockN * D * 2;
   static constexpr int kStages = (D == 128) ? 4 : 8;         // K/V ring slots
   static constexpr int kSmemTiles = (kTilesPerCta + kStages) * kTileBytes;
-  static constexpr int kStatBytes = kTilesPerCta * kBlockM * 4;       // 1 / (row sum) of every row of both tiles
+  static constexpr int kStatBytes = kTilesPerCta * kBlockM * 2 * 4;   // two output weights for every row of both tiles
   // Kept under 195 KB on purpose: with the 1 KB the system reserves per CTA the request must fit the
   // 196 KB shared-memory configuration of the SM, or the L1 cache (which holds the spilled registers of
-  // the softmax loop) shrinks from 60 KB to 28 KB and every spill turns into an L2 round trip.
-  static constexpr int kSmemBytes = kSmemTiles + kStatBytes + 1024 /*alignment slack*/ + 640 /*barriers, items*/;
+  // the softmax loop) shrinks from 60 KB to 28 KB and every spill turns into an L2 round trip.  That is
+  // why there is no slack for rounding the tile area up to 1024 bytes: the dynamic shared memory is
+  // declared with that alignment and the kernel checks it.
+  static constexpr int kSmemBytes = kSmemTiles + kStatBytes + 640 /*barriers, items*/;
   static_assert(kSmemBytes + 1024 <= 196 * 1024, "must fit the 196 KB shared-memory configuration");
   // With D = 64 the two O accumulators leave 128 tensor-memory columns free: P_t gets columns of its
   // own ([384,448) / [448,512)) instead of overwriting S_t, so Q_t K(j+1)^T no longer has to wait for
@@ -200,18 +202,24 @@ __device__ __forceinline__ ItemRec decode_item(const Problem& p, int idx, int n_
   return it;
 }
 
-template <int D, bool BF16, bool BIAS>
+// ACC: the accumulating form (a ring step folded into a running fp32 result).  A template parameter, not a
+// run-time branch: the softmax loop has no register to spare for state it does not use.
+template <int D, bool BF16, bool BIAS, bool ACC>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_persistent_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const Problem p, const int n_qblk, const int pair_heads,
                const int streams_per_wave, const int n_items, unsigned int* __restrict__ next_item,
                const long long wait_limit) {
   using C = Cfg<D>;
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t raw_addr = smem_u32(smem_raw);
-  const uint32_t tiles = (raw_addr + 1023u) & ~1023u;            // 1024-byte aligned tile area
-  float* stats = reinterpret_cast<float*>(smem_raw + (tiles - raw_addr) + C::kSmemTiles);   // [tile][row] 1 / sum
-  Sync* sync = reinterpret_cast<Sync*>(smem_raw + (tiles - raw_addr) + C::kSmemTiles + C::kStatBytes);
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t tiles = smem_u32(smem_raw);                     // tile area: 1024-byte aligned (swizzled TMA boxes)
+  if ((tiles & 1023u) != 0u) {                                   // uniform over the CTA; nothing has been started
+    if (threadIdx.x == 0) report(p.status, 0, -4, static_cast<int>(tiles & 1023u));
+    return;
+  }
+  // [tile][row][weight of the previous accumulator (accumulating form), weight of O]
+  float* stats = reinterpret_cast<float*>(smem_raw + C::kSmemTiles);
+  Sync* sync = reinterpret_cast<Sync*>(smem_raw + C::kSmemTiles + C::kStatBytes);
   volatile int* abort_flag = &sync->abort_flag;
 
   const int tid = threadIdx.x;
@@ -552,7 +560,9 @@ prefill_persistent_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
         const bool row_ok = row_g < p.L;
         uint16_t* orow = out16 + it.b * p.os[0] + static_cast<long long>(head) * p.os[1] +
                          static_cast<long long>(row_g) * p.os[2];
-        float inv = 0.f;
+        float* arow = p.acc + it.b * p.as[0] + static_cast<long long>(head) * p.as[1] + static_cast<long long>(row_g) * p.as[2];
+        if (ACC && nt == 0 && p.acc_mode == 2) continue;      // accumulating form: no visible key here, nothing to fold
+        float w_acc = 0.f, inv = 0.f;
         if (nt > 0) {
           bool ok = wait_relaxed(smem_u32(&sync->o_done[t]), n_e[t] & 1, abort_flag, wait_limit);
           ok = ok && wait_relaxed(smem_u32(&sync->stats_ready[t]), n_e[t] & 1, abort_flag, wait_limit);
@@ -564,7 +574,8 @@ prefill_persistent_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
           }
           tc_fence_after_sync();
           ++n_e[t];
-          inv = stats[t * kBlockM + r];
+          w_acc = stats[(t * kBlockM + r) * 2];
+          inv = stats[(t * kBlockM + r) * 2 + 1];
         }
         const uint32_t o_addr = tmem_base + lane_off + 256u + static_cast<uint32_t>(t) * D;
 #pragma unroll
@@ -574,7 +585,7 @@ prefill_persistent_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
             tmem_ld_32x32(o_addr + c * 32, v);
             tmem_ld_wait();
             if (c == D / 32 - 1) {
-              // O_t and the statistics are in registers: the next item may overwrite both
+              // O_t and the weights are in registers: the next item may overwrite both
               tc_fence_before_sync();
               mbar_arrive(smem_u32(&sync->o_free[t]));
             }
@@ -582,7 +593,20 @@ prefill_persistent_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = 0u;
           }
-          if (row_ok) {
+          if (ACC && row_ok) {
+            // running fp32 result: acc = acc * w_acc + O * w_o, four columns at a time
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              float4* dst = reinterpret_cast<float4*>(arow + c * 32 + u * 4);
+              float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (p.acc_mode == 2) a = *dst;
+              a.x = fmaf(a.x, w_acc, __uint_as_float(v[4 * u]) * inv);
+              a.y = fmaf(a.y, w_acc, __uint_as_float(v[4 * u + 1]) * inv);
+              a.z = fmaf(a.z, w_acc, __uint_as_float(v[4 * u + 2]) * inv);
+              a.w = fmaf(a.w, w_acc, __uint_as_float(v[4 * u + 3]) * inv);
+              *dst = a;
+            }
+          } else if (!ACC && row_ok) {
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
               uint4 w;
@@ -595,7 +619,10 @@ prefill_persistent_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
           }
         }
         // (rows that saw keys get their lse from the softmax thread that owns the row statistics)
-        if (nt == 0 && p.lse != nullptr && row_ok) p.lse[it.b * p.ls[0] + head * p.ls[1] + row_g * p.ls[2]] = -CUDART_INF_F;
+        if (nt == 0 && row_ok) {
+          if (ACC && p.acc_mode == 1) p.acc_lse[it.b * p.als[0] + head * p.als[1] + row_g * p.als[2]] = -CUDART_INF_F;
+          if (!ACC && p.lse != nullptr) p.lse[it.b * p.ls[0] + head * p.ls[1] + row_g * p.ls[2]] = -CUDART_INF_F;
+        }
       }
     }
   } else {
@@ -636,6 +663,15 @@ prefill_persistent_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
         lim = c < lim ? static_cast<int>(c < 0 ? 0 : c) : lim;
       }
       float m_run = -CUDART_INF_F, l_run = 0.f;
+      // accumulating form: the row's running lse is fetched now and used after the last key tile
+      float* acc_lse_row = nullptr;
+      float old_lse = -CUDART_INF_F;
+      if constexpr (ACC) {
+        if (row_g < p.L) {
+          acc_lse_row = p.acc_lse + b * p.als[0] + head * p.als[1] + row_g * p.als[2];
+          if (p.acc_mode == 2) old_lse = *acc_lse_row;
+        }
+      }
       // this row of the bias, 16-bit elements in the query's dtype, unit stride along the keys
       const uint4* bias_row = nullptr;
       if constexpr (BIAS) {
@@ -779,14 +815,30 @@ prefill_persistent_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
               break;
             }
           }
-          stats[t * kBlockM + r] = l_run > 0.f ? 1.f / l_run : 0.f;
+          // one rounding at the magnitude of the maximum: m*scale + ln(l)
+          const float lse = l_run > 0.f ? fmaf(m_run, BIAS ? 1.f : p.scale, lg2(l_run) * kLn2) : -CUDART_INF_F;
+          float w_acc = 0.f, w_o = l_run > 0.f ? 1.f / l_run : 0.f;
+          if (ACC && acc_lse_row != nullptr) {
+            // accumulating form: fold this block's (result, lse) into the running pair for the row
+            float* al = acc_lse_row;
+            const float old = old_lse;
+            const float hi = fmaxf(old, lse);
+            float merged = -CUDART_INF_F;
+            if (hi != -CUDART_INF_F) {
+              const float e_old = ex2((old - hi) * kLog2e), e_new = ex2((lse - hi) * kLog2e);   // -inf -> 0
+              merged = hi + lg2(e_old + e_new) * kLn2;
+              w_acc = ex2((old - merged) * kLog2e);
+              w_o *= ex2((lse - merged) * kLog2e);
+            } else {
+              w_o = 0.f;
+            }
+            *al = merged;
+          }
+          stats[(t * kBlockM + r) * 2] = w_acc;
+          stats[(t * kBlockM + r) * 2 + 1] = w_o;
           mbar_arrive(smem_u32(&sync->stats_ready[t]));
           ++n_done;
-          if (p.lse != nullptr && row_g < p.L) {
-            // one rounding at the magnitude of the maximum: m*scale + ln(l)
-            const float lse = l_run > 0.f ? fmaf(m_run, BIAS ? 1.f : p.scale, lg2(l_run) * kLn2) : -CUDART_INF_F;
-            p.lse[b * p.ls[0] + head * p.ls[1] + row_g * p.ls[2]] = lse;
-          }
+          if (!ACC && p.lse != nullptr && row_g < p.L) p.lse[b * p.ls[0] + head * p.ls[1] + row_g * p.ls[2]] = lse;
         }
         tmem_st_wait();
         tc_fence_before_sync();
@@ -857,14 +909,14 @@ PrefillGeom prefill_geometry(const Problem& p) {
   return g;
 }
 
-template <int D, bool BF16, bool BIAS>
+template <int D, bool BF16, bool BIAS, bool ACC>
 int launch_variant(const Problem& p, void* workspace, uint64_t workspace_bytes, cudaStream_t stream) {
   using C = Cfg<D>;
   CUtensorMap tq, tk, tv;
   if (!make_map(&tq, p.q, BF16, D, p.L, p.Hq, p.B, p.qs) || !make_map(&tk, p.k, BF16, D, p.S, p.Hkv, p.B, p.ks) ||
       !make_map(&tv, p.v, BF16, D, p.S, p.Hkv, p.B, p.vs))
     return B200_SDPA_ERR_CUDA;
-  auto kern = prefill_persistent_kernel<D, BF16, BIAS>;
+  auto kern = prefill_persistent_kernel<D, BF16, BIAS, ACC>;
   // the opt-in to more than 48 KB of dynamic shared memory is a per-device attribute: set on every
   // launch (a cheap host-side call), so a process that drives several GPUs gets it on each of them
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess) {
@@ -895,16 +947,32 @@ int launch_variant(const Problem& p, void* workspace, uint64_t workspace_bytes, 
 
 }  // namespace
 
-// How the two prefill kernels share the work: the persistent kernel pays off when every CTA gets several
-// items (its set-up is heavier, its item boundaries are cheaper) and, as measured, only at head dimension
-// 128; everything else keeps the one-item-per-CTA kernel.  B200_SDPA_PREFILL = "persistent" or "per_cta"
-// overrides the choice where both kernels can serve the request (for tests and measurements).
+// How the two prefill kernels share the work.  What the persistent kernel saves is the cost of going from
+// one work item to the next (no CTA launch, set-up or tear-down; the next item's Q and first key tile
+// already in flight; the epilogue on its own warps); what it pays is a heavier steady state (sixteen warps
+// share the register file, and under a power cap it clocks a little lower).  Measured on one B200: with up
+// to 32 key tiles per item it is 3-5 % faster in bursts (8-14 % with a bias) and about 2 % slower when the
+// GPU sits at its power cap for seconds; with 256 key tiles per item (32768 keys, and the blocks of a ring
+// over 131072) the per-CTA kernel is 5 % faster either way.  So: head dimension 128, at least three items
+// per SM, and at most 64 key tiles per item.  B200_SDPA_PREFILL = "persistent" or "per_cta" overrides the
+// choice where both kernels can serve the request (for tests and measurements).
+// (acc, acc_lse) of the accumulating form: fp32 rows read and written as 16-byte pieces
+bool prefill_accumulate_eligible(const Problem& p) {
+  if (p.E != 128 || p.Dv != 128 || p.acc == nullptr || p.acc_lse == nullptr || p.bias != nullptr) return false;
+  if (reinterpret_cast<uintptr_t>(p.acc) % 16 != 0) return false;
+  const int n[3] = {p.B, p.Hq, p.L};
+  for (int i = 0; i < 3; ++i)
+    if (n[i] > 1 && (p.as[i] <= 0 || p.as[i] % 4 != 0 || p.als[i] <= 0)) return false;
+  return true;
+}
+
 bool prefill_persistent_wanted(const Problem& p) {
   if (p.E != 128 || p.Dv != 128) return false;
+  if (p.acc_mode != 0) return true;            // only this kernel has the accumulating form
   const char* e = getenv("B200_SDPA_PREFILL");
   if (e != nullptr && e[0] == 'p' && e[1] == 'e' && e[2] == 'r' && e[3] == 's') return true;    // "persistent"
   if (e != nullptr && e[0] == 'p' && e[1] == 'e' && e[2] == 'r' && e[3] == '_') return false;   // "per_cta"
-  return prefill_geometry(p).n_items >= 3LL * kAssumedSms;
+  return prefill_geometry(p).n_items >= 3LL * kAssumedSms && (p.S + kBlockN - 1) / kBlockN <= 64;
 }
 
 void plan_prefill_persistent(const Problem& p, B200SdpaPlan* plan) {
@@ -926,11 +994,16 @@ void plan_prefill_persistent(const Problem& p, B200SdpaPlan* plan) {
 int launch_prefill_persistent(const Problem& p, int dtype, void* workspace, uint64_t workspace_bytes,
                               cudaStream_t stream) {
   const bool bf16 = dtype == B200_SDPA_BF16;
+  if (p.acc_mode != 0) {
+    if (p.bias != nullptr) return B200_SDPA_ERR_UNSUPPORTED;
+    return bf16 ? launch_variant<128, true, false, true>(p, workspace, workspace_bytes, stream)
+                : launch_variant<128, false, false, true>(p, workspace, workspace_bytes, stream);
+  }
   if (p.bias != nullptr)
-    return bf16 ? launch_variant<128, true, true>(p, workspace, workspace_bytes, stream)
-                : launch_variant<128, false, true>(p, workspace, workspace_bytes, stream);
-  return bf16 ? launch_variant<128, true, false>(p, workspace, workspace_bytes, stream)
-              : launch_variant<128, false, false>(p, workspace, workspace_bytes, stream);
+    return bf16 ? launch_variant<128, true, true, false>(p, workspace, workspace_bytes, stream)
+                : launch_variant<128, false, true, false>(p, workspace, workspace_bytes, stream);
+  return bf16 ? launch_variant<128, true, false, false>(p, workspace, workspace_bytes, stream)
+              : launch_variant<128, false, false, false>(p, workspace, workspace_bytes, stream);
 }
 
 }  // namespace b200

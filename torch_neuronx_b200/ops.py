@@ -292,6 +292,77 @@ def sdpa_forward(
     return out, lse
 
 
+def sdpa_forward_accumulate(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    acc: torch.Tensor,
+    acc_lse: torch.Tensor,
+    *,
+    first: bool,
+    is_causal: bool = False,
+    scale: Optional[float] = None,
+    q_offset: int = 0,
+    k_offset: int = 0,
+) -> bool:
+    """One step of a ring over key/value blocks with the merge fused into the attention kernel's
+    epilogue: the result of ``query`` against this block is folded into the running fp32 ``acc``
+    ``(B, Hq, L, Dv)`` / ``acc_lse`` ``(B, Hq, L)`` (overwritten when ``first``) -- no partial in the
+    storage dtype, no separate merge launch (upstream merges in Python between per-block calls,
+    ``cp_ring_handler.py:308-318``).  Returns False, having done nothing, when the request is not one
+    the accumulating kernel serves (it is the persistent tensor-core prefill kernel: f16/bf16, head
+    dim 128, TMA-legal strides); the caller then runs the plain forward and :func:`merge_partials`."""
+    if query.dtype not in (torch.float16, torch.bfloat16) or not query.is_cuda:
+        return False
+    lib = _lib.load()
+    dev = _device_index(query)
+    B, Hq, L, E = query.shape
+    Hkv, S, Dv = key.shape[1], key.shape[2], value.shape[3]
+    if acc.dtype != torch.float32 or tuple(acc.shape) != (B, Hq, L, Dv) or acc.stride(3) != 1:
+        raise RuntimeError("acc must be an fp32 (B, Hq, L, Dv) tensor with unit inner stride")
+    if acc_lse.dtype != torch.float32 or tuple(acc_lse.shape) != (B, Hq, L):
+        raise RuntimeError("acc_lse must be an fp32 (B, Hq, L) tensor")
+    if scale is None:
+        scale = 1.0 / math.sqrt(E)
+    p = _lib.Params()
+    p.struct_size = C.sizeof(_lib.Params)
+    p.dtype = _DTYPE_CODE[query.dtype]
+    p.device = dev
+    p.force_path = _lib.PATH_AUTO
+    p.q, p.k, p.v = query.data_ptr(), key.data_ptr(), value.data_ptr()
+    p.q_stride[:] = query.stride()
+    p.k_stride[:] = key.stride()
+    p.v_stride[:] = value.stride()
+    p.out_stride[:] = (Hq * L * Dv, L * Dv, Dv, 1)     # no output tensor in this form
+    p.B, p.Hq, p.Hkv, p.L, p.S, p.E, p.Dv = B, Hq, Hkv, L, S, E, Dv
+    p.scale = float(scale)
+    p.is_causal = 1 if is_causal else 0
+    p.q_offset, p.k_offset = int(q_offset), int(k_offset)
+    p.acc_mode = 1 if first else 2
+    p.acc, p.acc_lse = acc.data_ptr(), acc_lse.data_ptr()
+    p.acc_stride[:] = acc.stride()[:3]
+    p.acc_lse_stride[:] = acc_lse.stride()
+    p.status = _status_word(dev).data_ptr()
+    plan = _lib.Plan()
+    plan.struct_size = C.sizeof(_lib.Plan)
+    rc = lib.b200_sdpa_query_plan(C.byref(p), C.byref(plan))
+    if rc in (_lib.ERR_UNSUPPORTED, _lib.ERR_ALIGNMENT):
+        return False
+    if rc != _lib.OK:
+        raise RuntimeError(f"b200_sdpa_query_plan: {_lib.strerror(rc)}")
+    if plan.workspace_bytes:
+        ws = _workspace(dev, int(plan.workspace_bytes))
+        p.workspace = ws.data_ptr()
+        p.workspace_bytes = ws.numel()
+    rc = lib.b200_sdpa_fwd(C.byref(p), C.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+    if rc != _lib.OK:
+        raise RuntimeError(f"b200_sdpa_fwd: {_lib.strerror(rc)}")
+    last_plan.clear()
+    last_plan.update(path=_lib.PATH_NAMES.get(plan.path, str(plan.path)), grid=(plan.grid_x, plan.grid_y, plan.grid_z),
+                     threads=plan.threads, launches=plan.launches, accumulate=True)
+    return True
+
+
 def paged_decode(
     query: torch.Tensor,
     k_pages: torch.Tensor,
@@ -610,10 +681,10 @@ def merge_partials(acc, acc_lse, part, part_lse, *, first=False, final_out=None)
     to ``final_out`` in the partial's dtype."""
     lib = _lib.load()
     B, Hq, L, Dv = part.shape
-    if acc.dtype != torch.float32 or not acc.is_contiguous() or tuple(acc.shape) != (B, Hq, L, Dv):
-        raise RuntimeError("acc must be a contiguous fp32 tensor shaped like the partial")
-    if acc_lse.dtype != torch.float32 or not acc_lse.is_contiguous() or tuple(acc_lse.shape) != (B, Hq, L):
-        raise RuntimeError("acc_lse must be a contiguous fp32 tensor of shape (B, Hq, L)")
+    if acc.dtype != torch.float32 or acc.stride(3) != 1 or tuple(acc.shape) != (B, Hq, L, Dv):
+        raise RuntimeError("acc must be an fp32 tensor shaped like the partial with unit inner stride")
+    if acc_lse.dtype != torch.float32 or tuple(acc_lse.shape) != (B, Hq, L):
+        raise RuntimeError("acc_lse must be an fp32 tensor of shape (B, Hq, L)")
     m = _lib.MergeParams()
     m.struct_size = C.sizeof(_lib.MergeParams)
     m.dtype = _DTYPE_CODE[part.dtype]
@@ -627,6 +698,8 @@ def merge_partials(acc, acc_lse, part, part_lse, *, first=False, final_out=None)
         m.final_out = final_out.data_ptr()
         m.final_stride[:] = final_out.stride()
     m.B, m.Hq, m.L, m.Dv = B, Hq, L, Dv
+    m.acc_stride[:] = acc.stride()[:3]
+    m.acc_lse_stride[:] = acc_lse.stride()
     rc = lib.b200_sdpa_merge(C.byref(m), C.c_void_p(torch.cuda.current_stream(m.device).cuda_stream))
     if rc != _lib.OK:
         raise RuntimeError(f"b200_sdpa_merge: {_lib.strerror(rc)}")

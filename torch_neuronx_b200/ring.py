@@ -23,6 +23,7 @@ of virtual ranks.
 
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Callable, List, Optional, Sequence
 
@@ -131,29 +132,52 @@ def _default_merge(acc, acc_lse, part, part_lse, first):
     ops.merge_partials(acc, acc_lse, part, part_lse, first=first)
 
 
+def _default_accumulate(q, k, v, acc, acc_lse, *, first, is_causal, scale, q_offset, k_offset):
+    from . import ops
+
+    # Opt-in (B200_SDPA_RING_FUSED=1).  The fused step needs the persistent form of the prefill kernel, and
+    # for the long key blocks of a ring the per-CTA form plus a separate merge was the faster pair when
+    # measured (131072 tokens over two GPUs: 128.4 ms against 132.9 ms fused and 136.3 ms unfused persistent).
+    if not q.is_cuda or os.environ.get("B200_SDPA_RING_FUSED") != "1":
+        return False
+    return ops.sdpa_forward_accumulate(q, k, v, acc, acc_lse, first=first, is_causal=is_causal, scale=scale,
+                                       q_offset=q_offset, k_offset=k_offset)
+
+
 class RankState:
-    """Running fp32 accumulators of one rank, split at the chunk boundary so that
-    each accumulator is contiguous."""
+    """Running fp32 result of one rank: one accumulator for all local rows; the schedule folds into
+    it segment by segment (one segment per chunk the rank owns), each of which starts with the
+    first block that reaches it."""
 
     def __init__(self, q: torch.Tensor, dv: int, layout: str):
         B, Hq, n, _ = q.shape
         self.q = q
         self.cuts = [0, n] if layout == CONTIGUOUS else [0, n // 2, n]
+        self.acc_all = torch.empty((B, Hq, n, dv), dtype=torch.float32, device=q.device)
+        self.lse_all = torch.empty((B, Hq, n), dtype=torch.float32, device=q.device)
         self.acc, self.lse, self.started = [], [], []
         for a, b in zip(self.cuts[:-1], self.cuts[1:]):
-            self.acc.append(torch.empty((B, Hq, b - a, dv), dtype=torch.float32, device=q.device))
-            self.lse.append(torch.empty((B, Hq, b - a), dtype=torch.float32, device=q.device))
+            self.acc.append(self.acc_all[:, :, a:b])
+            self.lse.append(self.lse_all[:, :, a:b])
             self.started.append(False)
 
-    def fold(self, call: BlockCall, part: torch.Tensor, part_lse: torch.Tensor, merge_fn) -> None:
+    def segments(self, call: "BlockCall"):
+        """Indices of the accumulator segments a call covers (the schedule covers whole segments)."""
+        hit = []
         for i, (a, b) in enumerate(zip(self.cuts[:-1], self.cuts[1:])):
             lo, hi = max(a, call.q0), min(b, call.q1)
             if lo >= hi:
                 continue
             if (lo, hi) != (a, b):
                 raise AssertionError("schedule must cover whole accumulator segments")
-            merge_fn(self.acc[i], self.lse[i], part[:, :, lo - call.q0 : hi - call.q0],
-                     part_lse[:, :, lo - call.q0 : hi - call.q0], not self.started[i])
+            hit.append(i)
+        return hit
+
+    def fold(self, call: "BlockCall", part: torch.Tensor, part_lse: torch.Tensor, merge_fn) -> None:
+        for i in self.segments(call):
+            a, b = self.cuts[i], self.cuts[i + 1]
+            merge_fn(self.acc[i], self.lse[i], part[:, :, a - call.q0 : b - call.q0],
+                     part_lse[:, :, a - call.q0 : b - call.q0], not self.started[i])
             self.started[i] = True
 
     def finish(self, dtype):
@@ -161,9 +185,7 @@ class RankState:
             if not self.started[i]:  # rows that saw no key at all
                 self.acc[i].zero_()
                 self.lse[i].fill_(float("-inf"))
-        out = torch.cat(self.acc, dim=2).to(dtype)
-        lse = torch.cat(self.lse, dim=2)
-        return out, lse
+        return self.acc_all.to(dtype), self.lse_all
 
 
 def _mark(trace_row, name):
@@ -175,14 +197,27 @@ def _mark(trace_row, name):
 
 
 def ring_step(state: RankState, kv_k: torch.Tensor, kv_v: torch.Tensor, rank: int, src: int, world: int,
-              layout: str, causal: bool, scale, attn_fn, merge_fn, trace_row=None) -> int:
+              layout: str, causal: bool, scale, attn_fn, merge_fn, trace_row=None, accumulate_fn=None) -> int:
     """Attention of this rank's queries against one visiting block; returns the
-    number of kernel calls made."""
+    number of kernel calls made.  With ``accumulate_fn`` (the default block functions on CUDA) a call
+    whose segments are all at the same stage -- all fresh or all started -- is first offered to the
+    kernel that folds its result into the accumulator itself; what it declines runs as attention +
+    merge."""
     calls = ring_schedule(rank, src, world, state.q.shape[2], layout, causal)
     for c in calls:
         _mark(trace_row, "attention")
-        part, part_lse = attn_fn(state.q[:, :, c.q0 : c.q1], kv_k[:, :, c.k0 : c.k1], kv_v[:, :, c.k0 : c.k1],
-                                 is_causal=c.causal, scale=scale, q_offset=c.q_offset, k_offset=c.k_offset)
+        qs, ks, vs = state.q[:, :, c.q0 : c.q1], kv_k[:, :, c.k0 : c.k1], kv_v[:, :, c.k0 : c.k1]
+        if accumulate_fn is not None:
+            segs = state.segments(c)
+            fresh = [not state.started[i] for i in segs]
+            if segs and (all(fresh) or not any(fresh)):
+                if accumulate_fn(qs, ks, vs, state.acc_all[:, :, c.q0 : c.q1], state.lse_all[:, :, c.q0 : c.q1],
+                                 first=all(fresh), is_causal=c.causal, scale=scale, q_offset=c.q_offset,
+                                 k_offset=c.k_offset):
+                    for i in segs:
+                        state.started[i] = True
+                    continue
+        part, part_lse = attn_fn(qs, ks, vs, is_causal=c.causal, scale=scale, q_offset=c.q_offset, k_offset=c.k_offset)
         _mark(trace_row, "merge")
         state.fold(c, part, part_lse, merge_fn)
     return len(calls)
@@ -230,6 +265,8 @@ def ring_attention(
     for :func:`trace_to_ms` (CUDA tensors only)."""
     import torch.distributed as dist
 
+    # the fused form only with the library's own block functions (tests and CPU runs pass theirs)
+    accumulate_fn = _default_accumulate if (attn_fn is None and merge_fn is None and q.is_cuda) else None
     attn_fn = attn_fn or _default_attn
     merge_fn = merge_fn or _default_merge
     # without a process group this is a ring of one: the same block calls, no transport
@@ -240,7 +277,7 @@ def ring_attention(
         scale = q.shape[3] ** -0.5
     if world == 1:
         row = [] if trace is not None else None
-        ring_step(state, k, v, 0, 0, 1, layout, is_causal, scale, attn_fn, merge_fn, row)
+        ring_step(state, k, v, 0, 0, 1, layout, is_causal, scale, attn_fn, merge_fn, row, accumulate_fn)
         _mark(row, "finish")
         res = state.finish(q.dtype)
         _mark(row, "end")
@@ -269,7 +306,7 @@ def ring_attention(
         src = (rank - step) % world
         kk, vv = (cur[0], cur[1])
         row = [] if trace is not None else None
-        ring_step(state, kk, vv, rank, src, world, layout, is_causal, scale, attn_fn, merge_fn, row)
+        ring_step(state, kk, vv, rank, src, world, layout, is_causal, scale, attn_fn, merge_fn, row, accumulate_fn)
         _mark(row, "wait")
         for r in reqs:
             r.wait()
@@ -300,6 +337,7 @@ def ring_attention_virtual(
     """The same per-rank step logic with every rank living in this process and the
     rotation done by indexing: rank r at step s works on the block of rank
     (r - s) mod N.  Used to check the schedule and offsets on one device."""
+    accumulate_fn = _default_accumulate if (attn_fn is None and merge_fn is None and qs[0].is_cuda) else None
     attn_fn = attn_fn or _default_attn
     merge_fn = merge_fn or _default_merge
     world = len(qs)
@@ -311,7 +349,7 @@ def ring_attention_virtual(
         for rank in range(world):
             src = (rank - step) % world
             calls += ring_step(states[rank], ks[src], vs[src], rank, src, world, layout, is_causal, scale,
-                               attn_fn, merge_fn)
+                               attn_fn, merge_fn, None, accumulate_fn)
     outs = [st.finish(qs[0].dtype) for st in states]
     return [o for o, _ in outs], [l for _, l in outs], calls
 
