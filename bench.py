@@ -1255,7 +1255,7 @@ def run_dtensor_check(T, dist, dev, rank, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=300)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--profile", default=None, choices=["prefill", "decode", "gpt2", "bwd", "wide", "bias"],
                     help="bare kernel loop on one GPU for profiler captures")

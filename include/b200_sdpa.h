@@ -49,9 +49,14 @@ typedef enum b200_sdpa_status {
   B200_SDPA_ERR_DEVICE = 9,       /* not an sm_100 device                           */
   B200_SDPA_ERR_TIMEOUT = 10,     /* (status word only) a device-side wait gave up  */
   B200_SDPA_ERR_TOO_LARGE = 11,   /* exceeds a fixed-capacity entry point's limit   */
-  B200_SDPA_ERR_CACHE_FULL = 12   /* (status word only) decode with append met a
+  B200_SDPA_ERR_CACHE_FULL = 12,  /* (status word only) decode with append met a
                                      sequence whose cache is full: its new row was
                                      not stored and not attended to; [1] = batch    */
+  B200_SDPA_ERR_BOUNDS = 13       /* (status word only, checked build of the library)
+                                     an index left its tensor, a scratch slot its
+                                     buffer or a tensor-memory access its columns;
+                                     the access was skipped; [1] = site, [2] = index,
+                                     [3] = limit                                    */
 } b200_sdpa_status;
 
 typedef enum b200_sdpa_dtype {

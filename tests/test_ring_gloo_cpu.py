@@ -76,12 +76,16 @@ def _bwd_worker(rank, world, port, layout, causal, result_dir):
         want = O.sdpa_backward(go, q, k, v, out, lse, is_causal=causal, scale=0.3)
         loc = [ring.shard_sequence(t, rank, world, layout).contiguous() for t in (go, q, k, v, out)]
         lse_l = ring.shard_sequence(lse.unsqueeze(-1), rank, world, layout).squeeze(-1).contiguous()
+        before = [t.clone() for t in loc]
         dq, dk, dv = ring.ring_attention_backward(loc[0], loc[1], loc[2], loc[3], loc[4], lse_l, is_causal=causal,
                                                   scale=0.3, layout=layout, bwd_fn=_oracle_bwd)
         ok = all(
             (got - ring.shard_sequence(w, rank, world, layout)).abs().max().item() < 2e-5
             for got, w in zip((dq, dk, dv), want[:3])
         )
+        # the caller's tensors are inputs: with three or more ranks the exchange buffers swap roles, and a
+        # visiting block must never land in them
+        ok = ok and all(torch.equal(a, b) for a, b in zip(before, loc))
         torch.save(dict(ok=ok), os.path.join(result_dir, f"r{rank}.pt"))
     finally:
         dist.destroy_process_group()
@@ -134,12 +138,14 @@ def _worker(rank, world, port, layout, causal, result_dir):
         k = torch.rand(1, 2, S, 32, generator=g)
         v = torch.rand(1, 2, S, 32, generator=g)
         ql, kl, vl = (ring.shard_sequence(t, rank, world, layout).contiguous() for t in (q, k, v))
+        before = [t.clone() for t in (ql, kl, vl)]
         out, lse = ring.ring_attention(ql, kl, vl, is_causal=causal, scale=0.2, layout=layout,
                                        attn_fn=_oracle_attn, merge_fn=_oracle_merge)
+        unchanged = all(torch.equal(a, b) for a, b in zip(before, (ql, kl, vl)))
         ref_o, ref_l = O.sdpa_forward(q, k, v, is_causal=causal, scale=0.2)
         want_o = ring.shard_sequence(ref_o, rank, world, layout)
         want_l = ring.shard_sequence(ref_l.unsqueeze(-1), rank, world, layout).squeeze(-1)
-        ok = (out - want_o).abs().max().item() < 1e-5 and (lse - want_l).abs().max().item() < 1e-5
+        ok = unchanged and (out - want_o).abs().max().item() < 1e-5 and (lse - want_l).abs().max().item() < 1e-5
         local_o, _ = O.sdpa_forward(ql, kl, vl, is_causal=causal, scale=0.2)
         differs = (local_o - out).abs().max().item() > 1e-3  # negative guard: not local-only attention
         torch.save(dict(ok=ok, differs=differs), os.path.join(result_dir, f"r{rank}.pt"))

@@ -8,6 +8,7 @@
 // lse = max + log(sum); the only difference is that probabilities stay fp32 for
 // the second product (upstream rounds them to the input dtype first).
 #include "common.cuh"
+#include "debug.cuh"
 
 namespace b200 {
 
@@ -181,9 +182,10 @@ __global__ void __launch_bounds__(kThreads) generic_fwd_kernel(const Problem p, 
 #pragma unroll
     for (int c = 0; c < NC; ++c) {
       const int col = tx + 16 * c;
-      if (col < p.Dv) out[o_base + col * p.os[3]] = from_f32<T>(acc[i][c] * inv);
+      if (col < p.Dv && dbg_bhrc(p.status, DBG_GENERIC_FWD * 100 + 1, b, p.B, h, p.Hq, gi, p.L, col, 1, p.Dv))
+        out[o_base + col * p.os[3]] = from_f32<T>(acc[i][c] * inv);
     }
-    if (p.lse != nullptr && tx == 0) {
+    if (p.lse != nullptr && tx == 0 && dbg_bhrc(p.status, DBG_GENERIC_FWD * 100 + 2, b, p.B, h, p.Hq, gi, p.L, 0, 0, 1)) {
       const float m = row_m[r];
       p.lse[b * p.ls[0] + h * p.ls[1] + gi * p.ls[2]] = (m == -CUDART_INF_F) ? -CUDART_INF_F : m + logf(l);
     }

@@ -290,7 +290,9 @@ def ring_attention(
         cur = torch.stack([k, v]).contiguous()
         nxt = torch.empty_like(cur)
     else:
-        cur = [k.contiguous(), v.contiguous()]
+        # private copies: from the second exchange on, blocks are received into the buffers the first
+        # step sent from, which must therefore never be the caller's tensors
+        cur = [k.clone(memory_format=torch.contiguous_format), v.clone(memory_format=torch.contiguous_format)]
         nxt = [torch.empty_like(cur[0]), torch.empty_like(cur[1])]
     send_to = dist.get_global_rank(group, (rank + 1) % world) if group is not None else (rank + 1) % world
     recv_from = dist.get_global_rank(group, (rank - 1) % world) if group is not None else (rank - 1) % world
@@ -434,7 +436,9 @@ def ring_attention_backward(
 
     send_to = dist.get_global_rank(group, (rank + 1) % world) if group is not None else (rank + 1) % world
     recv_from = dist.get_global_rank(group, (rank - 1) % world) if group is not None else (rank - 1) % world
-    cur = [k.contiguous(), v.contiguous()]
+    # private copies of the key/value block: the two buffers swap roles every step, so with more than two
+    # ranks a visiting block is received into the buffer step 0 sent from -- never the caller's tensors
+    cur = [k.clone(memory_format=torch.contiguous_format), v.clone(memory_format=torch.contiguous_format)]
     nxt = [torch.empty_like(cur[0]), torch.empty_like(cur[1])]
     # three accumulator sets rotate through the roles (being sent, being received, being computed)
     sending, receiving, computing = kv_zeros(), kv_zeros(), kv_zeros()
