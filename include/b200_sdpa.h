@@ -399,6 +399,23 @@ int b200_sdpa_merge(const B200SdpaMergeParams* params, void* stream);
 uint64_t b200_sdpa_launch_count(int kernel_id);
 void b200_sdpa_reset_launch_counts(void);
 
+/*
+ * The checked build (the same sources compiled with -DB200_SDPA_DEBUG into
+ * libb200_sdpa_checked.so): every global store whose address a kernel computes from
+ * decoded indices, every scratch slot and every tensor-memory column range is verified
+ * first; a violation puts B200_SDPA_ERR_BOUNDS into the status word and skips the
+ * access -- the device never traps.  Upstream counterpart: the debug / bounds-checking
+ * runs of its kernels under the simulator; here it is a second library with the same ABI.
+ *   b200_sdpa_checked_build()   1 in the checked build, 0 otherwise
+ *   b200_sdpa_debug_selftest()  checked build only (B200_SDPA_ERR_UNSUPPORTED otherwise):
+ *                               launches one thread that offers the checker an index
+ *                               past its limit, so a caller can see the report arrive in
+ *                               `status` (device int32[4], zeroed) without any real
+ *                               access being wrong.
+ */
+int b200_sdpa_checked_build(void);
+int b200_sdpa_debug_selftest(int device, int32_t* status, void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -39,3 +39,17 @@ def golden_bwd():
 
     path = os.path.join(ROOT, "tests", "golden", "sdpa_bwd_golden.pt")
     return torch.load(path, weights_only=False)["cases"]
+
+
+@pytest.fixture(autouse=True)
+def _checked_build_verdict(request):
+    """Under ``B200_SDPA_CHECKED=1`` (the bounds-checking build of the library) every GPU test also
+    fails when a kernel recorded an index, scratch-slot or tensor-memory column violation."""
+    yield
+    if os.environ.get("B200_SDPA_CHECKED", "0") not in ("", "0") and "gpu" in request.keywords:
+        import torch
+
+        if torch.cuda.is_available():
+            import torch_neuronx_b200 as T
+
+            T.check_device_status()

@@ -29,11 +29,36 @@ def test_library_exports_every_declared_symbol():
     assert set(names) == set(_lib.EXPORTS), "python binding table and header disagree"
 
 
+def test_checked_build_exports_the_same_abi():
+    """The bounds-checking variant of the library is the same ABI with the checks compiled in."""
+    import os
+
+    checked = os.path.join(os.path.dirname(_lib.LIB_PATH), "libb200_sdpa_checked.so")
+    normal = C.CDLL(_lib.LIB_PATH)
+    normal.b200_sdpa_checked_build.restype = C.c_int
+    assert normal.b200_sdpa_checked_build() == 0
+    # without the checks the self-test entry point declines before touching any device
+    normal.b200_sdpa_debug_selftest.restype = C.c_int
+    normal.b200_sdpa_debug_selftest.argtypes = [C.c_int, C.c_void_p, C.c_void_p]
+    assert normal.b200_sdpa_debug_selftest(0, None, None) == _lib.ERR_UNSUPPORTED
+    if not os.path.exists(checked):
+        import pytest
+
+        pytest.skip("checked library not built (python -m torch_neuronx_b200.build --checked)")
+    lib = C.CDLL(checked)
+    for n in _declared_symbols():
+        assert hasattr(lib, n), f"{n} missing from the checked build"
+    lib.b200_sdpa_checked_build.restype = C.c_int
+    lib.b200_sdpa_abi_version.restype = C.c_int
+    assert lib.b200_sdpa_checked_build() == 1
+    assert lib.b200_sdpa_abi_version() == _lib.ABI_VERSION
+
+
 def test_abi_version_and_strerror():
     lib = _lib.load()
     assert lib.b200_sdpa_abi_version() == _lib.ABI_VERSION
     assert _lib.strerror(0) == "ok"
-    for code in range(1, 12):
+    for code in range(1, 14):
         assert _lib.strerror(code) not in ("ok", "unknown status")
     assert _lib.strerror(999) == "unknown status"
 

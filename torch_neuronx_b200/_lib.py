@@ -19,6 +19,12 @@ import threading
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libb200_sdpa.so")
 OPS_LIB_PATH = os.path.join(HERE, "libb200_sdpa_ops.so")   # C++ operator layer (dispatcher kernels of the ATen ops)
+# B200_SDPA_CHECKED=1 runs everything on the bounds-checking build of the library (csrc/debug.cuh;
+# `python -m torch_neuronx_b200.build --checked`); the C++ operator layer is linked against the normal library, so
+# the ATen ops then go through the Python implementations and the same checked kernels.
+CHECKED = os.environ.get("B200_SDPA_CHECKED", "0") not in ("", "0")
+if CHECKED:
+    LIB_PATH = os.path.join(HERE, "libb200_sdpa_checked.so")
 
 ABI_VERSION = 6
 STATIC_SCRATCH_BYTES = 16 << 20  # B200_SDPA_STATIC_SCRATCH_BYTES
@@ -26,7 +32,7 @@ STATIC_SCRATCH_BYTES = 16 << 20  # B200_SDPA_STATIC_SCRATCH_BYTES
 # b200_sdpa_status
 OK = 0
 ERR_NULL, ERR_STRUCT, ERR_DTYPE, ERR_SHAPE, ERR_UNSUPPORTED = 1, 2, 3, 4, 5
-ERR_WORKSPACE, ERR_ALIGNMENT, ERR_CUDA, ERR_DEVICE, ERR_TIMEOUT, ERR_TOO_LARGE, ERR_CACHE_FULL = 6, 7, 8, 9, 10, 11, 12
+ERR_WORKSPACE, ERR_ALIGNMENT, ERR_CUDA, ERR_DEVICE, ERR_TIMEOUT, ERR_TOO_LARGE, ERR_CACHE_FULL, ERR_BOUNDS = 6, 7, 8, 9, 10, 11, 12, 13
 
 # b200_sdpa_dtype
 F32, F16, BF16 = 0, 1, 2
@@ -204,6 +210,8 @@ EXPORTS = {
     "b200_sdpa_merge": (C.c_int, [C.POINTER(MergeParams), C.c_void_p]),
     "b200_sdpa_launch_count": (C.c_uint64, [C.c_int]),
     "b200_sdpa_reset_launch_counts": (None, []),
+    "b200_sdpa_checked_build": (C.c_int, []),
+    "b200_sdpa_debug_selftest": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p]),
 }
 
 _lib = None
@@ -253,7 +261,7 @@ def load_ops() -> bool:
     with _lock:
         if _ops_loaded is None:
             _ops_loaded = False
-            if os.path.exists(OPS_LIB_PATH) and os.path.exists(LIB_PATH):
+            if not CHECKED and os.path.exists(OPS_LIB_PATH) and os.path.exists(LIB_PATH):
                 import torch
 
                 try:

@@ -27,6 +27,10 @@ OBJ_DIR = os.path.join(CSRC, "build")
 LIB_PATH = os.path.join(HERE, "libb200_sdpa.so")
 OPS_SRC = os.path.join(HERE, "csrc_ops", "aten_ops.cpp")
 OPS_LIB_PATH = os.path.join(HERE, "libb200_sdpa_ops.so")
+# the checked build: the same sources with -DB200_SDPA_DEBUG (index, scratch-slot and tensor-memory column
+# checks that report through the status word; csrc/debug.cuh)
+CHECKED_OBJ_DIR = os.path.join(CSRC, "build_checked")
+CHECKED_LIB_PATH = os.path.join(HERE, "libb200_sdpa_checked.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -59,8 +63,15 @@ def _digest(paths, extra: str) -> str:
     return h.hexdigest()
 
 
-def build(verbose: bool = False, force: bool = False) -> str:
-    """Build (if needed) and return the path of the shared library."""
+def build(verbose: bool = False, force: bool = False, checked: bool = False) -> str:
+    """Build (if needed) and return the path of the shared library.  ``checked`` builds the bounds-checking
+    variant ``libb200_sdpa_checked.so`` instead (same ABI; loaded when ``B200_SDPA_CHECKED=1``)."""
+    if checked:
+        return _build(verbose, force, CHECKED_OBJ_DIR, CHECKED_LIB_PATH, ["-DB200_SDPA_DEBUG"], with_ops=False)
+    return _build(verbose, force, OBJ_DIR, LIB_PATH, [], with_ops=True)
+
+
+def _build(verbose: bool, force: bool, OBJ_DIR: str, LIB_PATH: str, extra_flags, with_ops: bool) -> str:
     nvcc = find_nvcc()
     version = subprocess.run([nvcc, "--version"], capture_output=True, text=True, check=True).stdout
     cu, hdrs = _sources()
@@ -71,7 +82,8 @@ def build(verbose: bool = False, force: bool = False) -> str:
             stamps = json.load(f)
     except (OSError, ValueError):
         stamps = {}
-    flag_key = " ".join(NVCC_FLAGS) + version
+    flags = NVCC_FLAGS + list(extra_flags)
+    flag_key = " ".join(flags) + version
 
     def compile_one(name: str):
         src = os.path.join(CSRC, name)
@@ -79,7 +91,7 @@ def build(verbose: bool = False, force: bool = False) -> str:
         key = _digest([src] + hdrs, flag_key)
         if not force and stamps.get(name) == key and os.path.exists(obj):
             return name, key, False, ""
-        cmd = [nvcc] + NVCC_FLAGS + ["-c", src, "-o", obj]
+        cmd = [nvcc] + flags + ["-c", src, "-o", obj]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"nvcc failed for {name}:\n{res.stdout}\n{res.stderr}")
@@ -94,11 +106,15 @@ def build(verbose: bool = False, force: bool = False) -> str:
                 sys.stderr.write(f"--- {name}\n{log}\n")
     objs = [os.path.join(OBJ_DIR, n[:-3] + ".o") for n in cu]
     if rebuilt or not os.path.exists(LIB_PATH):
-        cmd = [nvcc, "-shared", "-o", LIB_PATH] + objs + ["-cudart", "static", "-lpthread", "-ldl", "-lrt"]
+        # -Bsymbolic: the library's own calls (kernel launch stubs included) bind to its own definitions, so a
+        # process may hold the normal and the checked build side by side without one interposing on the other
+        cmd = [nvcc, "-shared", "-o", LIB_PATH] + objs + ["-cudart", "static", "-Xlinker", "-Bsymbolic",
+                                                          "-lpthread", "-ldl", "-lrt"]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
-    build_ops(stamps, force=force or rebuilt, verbose=verbose)
+    if with_ops:
+        build_ops(stamps, force=force or rebuilt, verbose=verbose)
     with open(stamp_path, "w") as f:
         json.dump(stamps, f)
     return LIB_PATH
@@ -133,5 +149,5 @@ def build_ops(stamps: dict, force: bool = False, verbose: bool = False) -> str:
 
 
 if __name__ == "__main__":
-    path = build(verbose="-v" in sys.argv, force="-f" in sys.argv)
+    path = build(verbose="-v" in sys.argv, force="-f" in sys.argv, checked="--checked" in sys.argv)
     print(path)

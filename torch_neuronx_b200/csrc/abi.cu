@@ -1,6 +1,7 @@
 // C ABI of the library: validation, kernel selection and launch bookkeeping.
 // See include/b200_sdpa.h for the contract of every entry point.
 #include "common.cuh"
+#include "debug.cuh"
 
 #include <atomic>
 
@@ -280,6 +281,15 @@ void count_launch(int kernel_id) {
 
 }  // namespace b200
 
+namespace b200 {
+// One thread offers the checker an index in range (accepted, nothing recorded) and one past its limit
+// (refused and recorded); nothing is accessed either way.
+__global__ void debug_selftest_kernel(int* status) {
+  if (!dbg_range(status, 9901, 5, 1, 8)) return;
+  if (dbg_range(status, 9902, 8, 1, 8)) status[1] = -1;   // must not happen in the checked build
+}
+}  // namespace b200
+
 using namespace b200;
 
 extern "C" {
@@ -298,6 +308,7 @@ const char* b200_sdpa_strerror(int status) {
     case B200_SDPA_ERR_ALIGNMENT: return "tensor-core path needs unit inner stride and 16-byte aligned bases/strides";
     case B200_SDPA_ERR_CUDA: return "a CUDA call failed";
     case B200_SDPA_ERR_DEVICE: return "device is not sm_100";
+    case B200_SDPA_ERR_BOUNDS: return "checked build: an index, scratch slot or tensor-memory column left its range (access skipped)";
     case B200_SDPA_ERR_TIMEOUT: return "a device-side wait gave up (kernel drained and returned)";
     case B200_SDPA_ERR_TOO_LARGE: return "request exceeds the fixed capacity of this entry point";
     case B200_SDPA_ERR_CACHE_FULL: return "decode with append: a sequence's cache is full, its new row was dropped";
@@ -416,6 +427,17 @@ uint64_t b200_sdpa_launch_count(int kernel_id) {
 
 void b200_sdpa_reset_launch_counts(void) {
   for (int i = 0; i < KID_COUNT; ++i) g_launches[i].store(0, std::memory_order_relaxed);
+}
+
+int b200_sdpa_checked_build(void) { return kChecked ? 1 : 0; }
+
+int b200_sdpa_debug_selftest(int device, int32_t* status, void* stream) {
+  if (!kChecked) return B200_SDPA_ERR_UNSUPPORTED;
+  if (status == nullptr) return B200_SDPA_ERR_NULL;
+  DeviceScope scope(device);
+  if (scope.status() != B200_SDPA_OK) return scope.status();
+  debug_selftest_kernel<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream)>>>(status);
+  return cudaGetLastError() == cudaSuccess ? B200_SDPA_OK : B200_SDPA_ERR_CUDA;
 }
 
 }  // extern "C"

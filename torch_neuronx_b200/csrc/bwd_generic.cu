@@ -14,6 +14,7 @@
 // (:161-163) adds up to; each CTA recomputes it for the rows it holds, so no scratch
 // is needed.
 #include "common.cuh"
+#include "debug.cuh"
 
 namespace b200 {
 
@@ -203,7 +204,8 @@ __global__ void __launch_bounds__(kThreads) bwd_dq_kernel(const BwdProblem bp, c
       for (int j = 0; j < R; ++j) {
         const int c = tx + 16 * j;
         Ds[r * LDS + c] = ds[i][j];
-        if (gb != nullptr && gi < p.L && j0 + c < p.S) {
+        if (gb != nullptr && gi < p.L && j0 + c < p.S &&
+            dbg_bhrc(p.status, DBG_GENERIC_BWD * 100 + 1, b, p.B, h, p.Hq, gi, p.L, j0 + c, 1, p.S)) {
           gb[b * bp.dbs[0] + h * bp.dbs[1] + gi * bp.dbs[2] + (j0 + c) * bp.dbs[3]] = from_f32<T>(ds[i][j]);
         }
       }
@@ -234,7 +236,8 @@ __global__ void __launch_bounds__(kThreads) bwd_dq_kernel(const BwdProblem bp, c
 #pragma unroll
     for (int c = 0; c < NC; ++c) {
       const int col = tx + 16 * c;
-      if (col < p.E) gq[base + col * bp.dqs[3]] = from_f32<T>(acc[i][c] * p.scale);
+      if (col < p.E && dbg_bhrc(p.status, DBG_GENERIC_BWD * 100 + 2, b, p.B, h, p.Hq, gi, p.L, col, 1, p.E))
+        gq[base + col * bp.dqs[3]] = from_f32<T>(acc[i][c] * p.scale);
     }
   }
 }
@@ -331,8 +334,10 @@ __global__ void __launch_bounds__(kThreads) bwd_dkv_kernel(const BwdProblem bp, 
 #pragma unroll
     for (int c = 0; c < NC; ++c) {
       const int col = tx + 16 * c;
-      if (col < p.E) gk[kb + col * bp.dks[3]] = from_f32<T>(acc_k[i][c] * p.scale);
-      if (col < p.Dv) gv[vb + col * bp.dvs[3]] = from_f32<T>(acc_v[i][c]);
+      if (col < p.E && dbg_bhrc(p.status, DBG_GENERIC_BWD * 100 + 3, b, p.B, hk, p.Hkv, gj, p.S, col, 1, p.E))
+        gk[kb + col * bp.dks[3]] = from_f32<T>(acc_k[i][c] * p.scale);
+      if (col < p.Dv && dbg_bhrc(p.status, DBG_GENERIC_BWD * 100 + 4, b, p.B, hk, p.Hkv, gj, p.S, col, 1, p.Dv))
+        gv[vb + col * bp.dvs[3]] = from_f32<T>(acc_v[i][c]);
     }
   }
 }

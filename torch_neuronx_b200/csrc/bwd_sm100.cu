@@ -33,6 +33,7 @@
 // whole 128-column tiles instead (layout and pipeline described at the kernel).
 // Every wait is bounded (see tc_common.cuh).
 #include "tc_common.cuh"
+#include "debug.cuh"
 
 namespace b200 {
 
@@ -119,7 +120,7 @@ __global__ void __launch_bounds__(256) bwd_prep_kernel(const BwdProblem bp, floa
     const float l = p.lse[b * p.ls[0] + h * p.ls[1] + i * p.ls[2]];
     l2 = (l == -CUDART_INF_F) ? CUDART_INF_F : l * kLog2e;
   }
-  if (in_range && sub == 0) {
+  if (in_range && sub == 0 && dbg_range(p.status, DBG_BWD_TC * 100 + 1, row_id, 1, total)) {
     lse2[row_id] = l2;
     delta[row_id] = live ? d : 0.f;
   }
@@ -457,6 +458,10 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const uint32_t dp_addr = tmem_base + lane_off + kColDP + half * 64;
     const uint32_t op_addr = tmem_base + lane_off + kColOp + half * 32;
     const uint32_t dq_addr = tmem_base + lane_off + kColDQ;
+    // checked build: the column ranges of this thread's tensor-memory traffic; a violation drains the CTA
+    if (!dbg_tmem(p.status, DBG_BWD_TC * 100 + 2, s_addr, tmem_base, 64, kTmemCols) || !dbg_tmem(p.status, DBG_BWD_TC * 100 + 3, dp_addr, tmem_base, 64, kTmemCols) ||
+        !dbg_tmem(p.status, DBG_BWD_TC * 100 + 4, op_addr, tmem_base, 32, kTmemCols) || !dbg_tmem(p.status, DBG_BWD_TC * 100 + 5, dq_addr, tmem_base, D, kTmemCols))
+      *abort_flag = 1;
     const int row_g = row0 + r;
     int lim = kv_limit;
     if (p.causal) {
@@ -464,8 +469,9 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       lim = c < lim ? static_cast<int>(c < 0 ? 0 : c) : lim;
     }
     const long long stat_idx = (static_cast<long long>(b) * p.Hq + h) * l_pad + row_g;
-    const float neg_l2 = -lse2[stat_idx];      // -inf for rows without a visible key
-    const float dl = delta[stat_idx];
+    const bool stat_ok = dbg_range(p.status, DBG_BWD_TC * 100 + 6, stat_idx, 1, static_cast<long long>(p.B) * p.Hq * l_pad);
+    const float neg_l2 = stat_ok ? -lse2[stat_idx] : -CUDART_INF_F;      // -inf for rows without a visible key
+    const float dl = stat_ok ? delta[stat_idx] : 0.f;
     const float sl2 = p.scale * kLog2e;
     bool alive = true;
     // this row of the forward's additive bias (the query's dtype, unit stride along the keys)
@@ -658,8 +664,10 @@ bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       const int qrow0 = (i_first + it % per_head) * kT;
       const long long src = (static_cast<long long>(b) * p.Hq + h) * l_pad + qrow0;
       float4* dst = reinterpret_cast<float4*>(stats + stage * 2 * kT);
-      dst[lane] = reinterpret_cast<const float4*>(lse2 + src)[lane];
-      dst[32 + lane] = reinterpret_cast<const float4*>(delta + src)[lane];
+      if (dbg_range(p.status, DBG_BWD_TC * 100 + 10, src, kT, static_cast<long long>(p.B) * p.Hq * l_pad)) {
+        dst[lane] = reinterpret_cast<const float4*>(lse2 + src)[lane];
+        dst[32 + lane] = reinterpret_cast<const float4*>(delta + src)[lane];
+      }
       __syncwarp();
       if (lane == 0) {
         const uint32_t bar = smem_u32(&sync->ring_full[stage]);
@@ -730,6 +738,11 @@ bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t s_addr = tmem_base + lane_off + kColS + half * 32;
     const uint32_t dp_addr = tmem_base + lane_off + kColDP + half * 32;
+    // checked build: both buffers of the score-shaped units and the two accumulators
+    if (!dbg_tmem(p.status, DBG_BWD_TC * 100 + 7, s_addr, tmem_base, kU + 32, kTmemCols) ||
+        !dbg_tmem(p.status, DBG_BWD_TC * 100 + 8, dp_addr, tmem_base, kU + 32, kTmemCols) ||
+        !dbg_tmem(p.status, DBG_BWD_TC * 100 + 9, tmem_base + lane_off + kColDK, tmem_base, D, kTmemCols))
+      *abort_flag = 1;
     const int key_g = j0 + r;
     // query rows i >= i_min see this key; a padded key is seen by nobody
     int i_min = 0;

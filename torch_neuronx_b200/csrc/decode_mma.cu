@@ -22,6 +22,7 @@
 // statistics, the running maximum raised lazily (threshold 2^8) so O is rarely
 // rescaled; P rounded to the cache dtype once (torch_neuronx/_sdpa_math.py:94).
 #include "common.cuh"
+#include "debug.cuh"
 
 namespace b200 {
 
@@ -228,7 +229,10 @@ __global__ void __launch_bounds__(kThreads, 2) decode_mma_kernel(const Problem p
       const int srow = ok ? key0 + row : s0;
       int64_t k_off, v_off;
       if (PAGED) {
-        const int64_t page = table[srow >> p.page_shift];
+        // (checked build: the block-table slot of this row exists; page numbers themselves are the caller's)
+        const int64_t page = dbg_range(p.status, DBG_DECODE_MMA * 100 + 1, srow >> p.page_shift, 1, p.table_stride)
+                                 ? table[srow >> p.page_shift]
+                                 : 0;
         const int in_page = srow & page_mask;
         k_off = (page * p.ks[0]) * 2 + in_page * k_row;
         v_off = (page * p.vs[0]) * 2 + in_page * v_row;
@@ -268,8 +272,11 @@ __global__ void __launch_bounds__(kThreads, 2) decode_mma_kernel(const Problem p
                        : "memory");
           k_by_copy = false;
         }
-        *reinterpret_cast<uint4*>(const_cast<char*>(ksrc)) = kq;
-        *reinterpret_cast<uint4*>(const_cast<char*>(vsrc)) = vq;
+        // the append: this thread's 16 bytes of the new row go into the cache at position `pos`
+        if (dbg_bhrc(p.status, DBG_DECODE_MMA * 100 + 2, b, p.B, hk, p.Hkv, srow, p.S, ch * 8, 8, D)) {
+          *reinterpret_cast<uint4*>(const_cast<char*>(ksrc)) = kq;
+          *reinterpret_cast<uint4*>(const_cast<char*>(vsrc)) = vq;
+        }
         ksrc = knew + ch * 16;
         vsrc = vnew + ch * 16;
       }
@@ -419,6 +426,9 @@ __global__ void __launch_bounds__(kThreads, 2) decode_mma_kernel(const Problem p
       lsum = fmaf(sm_ml[(w * 16 + row) * 2 + 1], wgt, lsum);
     }
     const int64_t slot = (static_cast<int64_t>(b) * p.Hq + (h0 + row)) * nsplit + split;
+    if (!dbg_range(p.status, DBG_DECODE_MMA * 100 + 3, slot, 1, static_cast<int64_t>(p.B) * p.Hq * nsplit) ||
+        !dbg_range(p.status, DBG_DECODE_MMA * 100 + 4, h0 + row, 1, p.Hq))
+      continue;
     part_o[slot * D + d] = o;
     if (d == 0) {
       part_ml[slot * 2] = mx;

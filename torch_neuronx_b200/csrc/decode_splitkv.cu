@@ -16,6 +16,7 @@
 // Arithmetic restates torch_neuronx/_sdpa_math.py:79-95 for a single query row
 // with a key-length mask; dead rows (no visible key) give out = 0, lse = -inf.
 #include "common.cuh"
+#include "debug.cuh"
 
 #include <cstdlib>
 #include <mutex>
@@ -209,6 +210,9 @@ __global__ void __launch_bounds__(kThreads) decode_partial_kernel(const Problem 
       lsum = fmaf(sm_ml[s_][g][1], w, lsum);
     }
     const int64_t slot = (static_cast<int64_t>(b) * p.Hq + (h0 + g)) * nsplit + split;
+    if (!dbg_range(p.status, DBG_DECODE_SIMT * 100 + 1, slot, 1, static_cast<int64_t>(p.B) * p.Hq * nsplit) ||
+        !dbg_range(p.status, DBG_DECODE_SIMT * 100 + 2, h0 + g, 1, p.Hq))
+      continue;
     part_o[slot * D + d] = o;
     if (d == 0) {
       part_ml[slot * 2] = mx;
@@ -229,6 +233,9 @@ __global__ void __launch_bounds__(D) decode_combine_kernel(const Problem p, cons
   int used = (n_keys + chunk - 1) / chunk;
   used = used < 1 ? 1 : (used > nsplit ? nsplit : used);
   const int64_t slot0 = (static_cast<int64_t>(b) * p.Hq + h) * nsplit;
+  if (!dbg_range(p.status, DBG_DECODE_SIMT * 100 + 3, slot0, used, static_cast<int64_t>(p.B) * p.Hq * nsplit) ||
+      !dbg_bhrc(p.status, DBG_DECODE_SIMT * 100 + 4, b, p.B, h, p.Hq, 0, 1, d, 1, p.Dv))
+    return;
   float mx = -CUDART_INF_F;
   for (int s = 0; s < used; ++s) mx = fmaxf(mx, part_ml[(slot0 + s) * 2]);
   const float ms = (mx == -CUDART_INF_F) ? 0.f : mx;

@@ -40,6 +40,7 @@
 // other role drains, the CTA waits for the copies and MMAs it issued, tensor memory is freed and
 // the status word reports B200_SDPA_ERR_TIMEOUT.
 #include "tc_common.cuh"
+#include "debug.cuh"
 
 #include <cstdlib>
 #include <type_traits>
@@ -371,7 +372,7 @@ prefill_persistent_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
         const uint64_t qd = t == 0 ? q_desc0 : q_desc1;
         const uint64_t kd = kv_desc_k + static_cast<uint64_t>(stage * (C::kTileBytes >> 4));
         const uint32_t d_addr = tmem_base + static_cast<uint32_t>(t * 128);
-        if (elect_one()) {
+        if (elect_one() && dbg_tmem(p.status, DBG_PREFILL_PERSISTENT * 100 + 1, d_addr, tmem_base, 128, kTmemCols)) {
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk) {
             const uint64_t off = static_cast<uint64_t>(((kk >> 2) * kBoxBytes + (kk & 3) * 32) >> 4);
@@ -386,7 +387,8 @@ prefill_persistent_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
         const uint32_t d_addr = tmem_base + static_cast<uint32_t>(256 + t * D);
         const uint32_t a_addr = tmem_base + static_cast<uint32_t>(C::kSplitP ? 384 + t * 64 + half * 32 : t * 128 + half * 32);
         const uint32_t acc0 = (accumulate || half > 0) ? 1u : 0u;
-        if (elect_one()) {
+        if (elect_one() && dbg_tmem(p.status, DBG_PREFILL_PERSISTENT * 100 + 2, d_addr, tmem_base, D, kTmemCols) &&
+            dbg_tmem(p.status, DBG_PREFILL_PERSISTENT * 100 + 3, a_addr, tmem_base, 32, kTmemCols)) {
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
             mma_ts(d_addr, a_addr + static_cast<uint32_t>(kk * 8), vd + static_cast<uint64_t>(kk * (2048 >> 4)), idesc_pv,
@@ -578,6 +580,9 @@ prefill_persistent_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
           inv = stats[(t * kBlockM + r) * 2 + 1];
         }
         const uint32_t o_addr = tmem_base + lane_off + 256u + static_cast<uint32_t>(t) * D;
+        // checked build: the columns drained below, and the row this thread is about to store
+        if (!dbg_tmem(p.status, DBG_PREFILL_PERSISTENT * 100 + 4, o_addr, tmem_base, D, kTmemCols)) *abort_flag = 1;
+        const bool store_ok = dbg_bhrc(p.status, DBG_PREFILL_PERSISTENT * 100 + 5, it.b, p.B, head, p.Hq, row_ok ? row_g : 0, p.L, 0, D, p.Dv);
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
           uint32_t v[32];
@@ -593,7 +598,7 @@ prefill_persistent_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = 0u;
           }
-          if (ACC && row_ok) {
+          if (ACC && row_ok && store_ok) {
             // running fp32 result: acc = acc * w_acc + O * w_o, four columns at a time
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
@@ -606,7 +611,7 @@ prefill_persistent_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
               a.w = fmaf(a.w, w_acc, __uint_as_float(v[4 * u + 3]) * inv);
               *dst = a;
             }
-          } else if (!ACC && row_ok) {
+          } else if (!ACC && row_ok && store_ok) {
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
               uint4 w;
@@ -619,7 +624,7 @@ prefill_persistent_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
           }
         }
         // (rows that saw keys get their lse from the softmax thread that owns the row statistics)
-        if (nt == 0 && row_ok) {
+        if (nt == 0 && row_ok && store_ok) {
           if (ACC && p.acc_mode == 1) p.acc_lse[it.b * p.als[0] + head * p.als[1] + row_g * p.als[2]] = -CUDART_INF_F;
           if (!ACC && p.lse != nullptr) p.lse[it.b * p.ls[0] + head * p.ls[1] + row_g * p.ls[2]] = -CUDART_INF_F;
         }
@@ -635,6 +640,11 @@ prefill_persistent_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
     const uint32_t s_addr = tmem_base + lane_off + static_cast<uint32_t>(t) * 128u;
     const uint32_t o_addr = tmem_base + lane_off + 256u + static_cast<uint32_t>(t) * D;
     const uint32_t p_addr = C::kSplitP ? tmem_base + lane_off + 384u + static_cast<uint32_t>(t) * 64u : s_addr;
+    // checked build: the three column ranges this thread reads and writes; a violation drains the CTA
+    if (!dbg_tmem(p.status, DBG_PREFILL_PERSISTENT * 100 + 6, s_addr, tmem_base, 128, kTmemCols) ||
+        !dbg_tmem(p.status, DBG_PREFILL_PERSISTENT * 100 + 7, o_addr, tmem_base, D, kTmemCols) ||
+        !dbg_tmem(p.status, DBG_PREFILL_PERSISTENT * 100 + 8, p_addr, tmem_base, 64, kTmemCols))
+      *abort_flag = 1;
     // With an additive bias the logits s * scale + bias are formed when the scores are read;
     // everything after that then works on them with scale 1 (log2 e in the exponent).
     const float sl2_in = BIAS ? p.scale : p.scale * kLog2e;
@@ -838,7 +848,9 @@ prefill_persistent_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
           stats[(t * kBlockM + r) * 2 + 1] = w_o;
           mbar_arrive(smem_u32(&sync->stats_ready[t]));
           ++n_done;
-          if (!ACC && p.lse != nullptr && row_g < p.L) p.lse[b * p.ls[0] + head * p.ls[1] + row_g * p.ls[2]] = lse;
+          if (!ACC && p.lse != nullptr && row_g < p.L &&
+              dbg_bhrc(p.status, DBG_PREFILL_PERSISTENT * 100 + 9, b, p.B, head, p.Hq, row_g, p.L, 0, 0, 1))
+            p.lse[b * p.ls[0] + head * p.ls[1] + row_g * p.ls[2]] = lse;
         }
         tmem_st_wait();
         tc_fence_before_sync();

@@ -30,6 +30,7 @@
 // other role drains, tensor memory is freed and the status word reports
 // B200_SDPA_ERR_TIMEOUT.
 #include "tc_common.cuh"
+#include "debug.cuh"
 
 #include <type_traits>
 
@@ -258,7 +259,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const uint64_t qd = t == 0 ? q_desc0 : q_desc1;
         const uint64_t kd = kv_desc_k + static_cast<uint64_t>(stage * (C::kTileBytes >> 4));
         const uint32_t d_addr = tmem_base + static_cast<uint32_t>(t * 128);
-        if (elect_one()) {
+        if (elect_one() && dbg_tmem(p.status, DBG_PREFILL * 100 + 1, d_addr, tmem_base, 128, 512)) {
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk) {
             const uint64_t off = static_cast<uint64_t>(((kk >> 2) * kBoxBytes + (kk & 3) * 32) >> 4);
@@ -273,7 +274,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const uint32_t d_addr = tmem_base + static_cast<uint32_t>(256 + t * D);
         const uint32_t a_addr = tmem_base + static_cast<uint32_t>(C::kSplitP ? 384 + t * 64 + half * 32 : t * 128 + half * 32);
         const uint32_t acc0 = (accumulate || half > 0) ? 1u : 0u;
-        if (elect_one()) {
+        if (elect_one() && dbg_tmem(p.status, DBG_PREFILL * 100 + 2, d_addr, tmem_base, D, 512) &&
+            dbg_tmem(p.status, DBG_PREFILL * 100 + 3, a_addr, tmem_base, 32, 512)) {
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
             mma_ts(d_addr, a_addr + static_cast<uint32_t>(kk * 8), vd + static_cast<uint64_t>(kk * (2048 >> 4)), idesc_pv,
@@ -389,6 +391,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const uint32_t s_addr = tmem_base + lane_off + static_cast<uint32_t>(t) * 128u;
     const uint32_t o_addr = tmem_base + lane_off + 256u + static_cast<uint32_t>(t) * D;
     const uint32_t p_addr = C::kSplitP ? tmem_base + lane_off + 384u + static_cast<uint32_t>(t) * 64u : s_addr;
+    // checked build: the three column ranges this thread reads and writes; a violation drains the CTA
+    if (!dbg_tmem(p.status, DBG_PREFILL * 100 + 4, s_addr, tmem_base, 128, 512) ||
+        !dbg_tmem(p.status, DBG_PREFILL * 100 + 5, o_addr, tmem_base, D, 512) ||
+        !dbg_tmem(p.status, DBG_PREFILL * 100 + 6, p_addr, tmem_base, 64, 512))
+      *abort_flag = 1;
     const int row_g = tg.row0 + r;
     int lim = kv_limit;                      // keys [0, lim) are visible to this row
     if (p.causal) {
@@ -587,7 +594,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         if (p.lse != nullptr && row_g < p.L) {
           // one rounding at the magnitude of the maximum: m*scale + ln(l)
           const float lse = l_run > 0.f ? fmaf(m_run, BIAS ? 1.f : p.scale, lg2(l_run) * kLn2) : -CUDART_INF_F;
-          p.lse[b * p.ls[0] + head_of_tile[t] * p.ls[1] + row_g * p.ls[2]] = lse;
+          if (dbg_bhrc(p.status, DBG_PREFILL * 100 + 7, b, p.B, head_of_tile[t], p.Hq, row_g, p.L, 0, 0, 1))
+            p.lse[b * p.ls[0] + head_of_tile[t] * p.ls[1] + row_g * p.ls[2]] = lse;
         }
       }
     }

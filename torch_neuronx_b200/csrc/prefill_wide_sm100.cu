@@ -11,6 +11,7 @@
 // tiles (P overwrites the first 64 columns of its buffer as 16-bit pairs), [256,256+Dv) O.  With
 // two score buffers Q K^T of the next key tile runs under the softmax of this one.
 #include "tc_common.cuh"
+#include "debug.cuh"
 
 namespace b200 {
 
@@ -265,6 +266,10 @@ prefill_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
     const uint32_t s_base = tmem_base + lane_off + kColS;
     const uint32_t o_addr = tmem_base + lane_off + kColO;
+    // checked build: both score buffers and the accumulator stay inside the allocation
+    if (!dbg_tmem(p.status, DBG_PREFILL_WIDE * 100 + 1, s_base, tmem_base, 2 * kN, C::kTmemCols) ||
+        !dbg_tmem(p.status, DBG_PREFILL_WIDE * 100 + 2, o_addr, tmem_base, DV, C::kTmemCols))
+      *abort_flag = 1;
     const int row_g = row0 + r;
     int lim = kv_limit;                      // keys [0, lim) are visible to this row
     if (p.causal) {
@@ -440,7 +445,8 @@ prefill_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       }
       if (p.lse != nullptr && row_g < p.L) {
         const float lse = l_run > 0.f ? fmaf(m_run, BIAS ? 1.f : p.scale, lg2(l_run) * kLn2) : -CUDART_INF_F;
-        p.lse[b * p.ls[0] + h * p.ls[1] + row_g * p.ls[2]] = lse;
+        if (dbg_bhrc(p.status, DBG_PREFILL_WIDE * 100 + 3, b, p.B, h, p.Hq, row_g, p.L, 0, 0, 1))
+          p.lse[b * p.ls[0] + h * p.ls[1] + row_g * p.ls[2]] = lse;
       }
     }
   }
