@@ -137,7 +137,8 @@ def _default_accumulate(q, k, v, acc, acc_lse, *, first, is_causal, scale, q_off
 
     # Opt-in (B200_SDPA_RING_FUSED=1).  The fused step needs the persistent form of the prefill kernel, and
     # for the long key blocks of a ring the per-CTA form plus a separate merge was the faster pair when
-    # measured (131072 tokens over two GPUs: 128.4 ms against 132.9 ms fused and 136.3 ms unfused persistent).
+    # measured (131072 tokens over two GPUs: 128.4 ms against 132.9 ms fused and 136.3 ms unfused persistent;
+    # with the block sizes of eight ranks, all ranks' work on one GPU: 281.6 ms against 288.3 ms fused).
     if not q.is_cuda or os.environ.get("B200_SDPA_RING_FUSED") != "1":
         return False
     return ops.sdpa_forward_accumulate(q, k, v, acc, acc_lse, first=first, is_causal=is_causal, scale=scale,
