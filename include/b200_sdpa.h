@@ -189,8 +189,8 @@ typedef struct B200SdpaParams {
    * acc_mode 0 = off (acc, acc_lse ignored); 1 = first block (acc, acc_lse are overwritten);
    * 2 = fold into acc, acc_lse.  acc is (B, Hq, L, Dv) fp32 with unit inner stride and
    * 16-byte aligned rows, acc_lse (B, Hq, L) fp32; strides in elements.  `out` and `lse` may be
-   * NULL then.  Served by the persistent tensor-core prefill kernel only (f16/bf16, E = Dv =
-   * 128); b200_sdpa_query_plan() answers B200_SDPA_ERR_UNSUPPORTED otherwise and the caller
+   * NULL then.  Served by the tensor-core prefill kernels (f16/bf16, E = Dv = 128, no
+   * bias); b200_sdpa_query_plan() answers B200_SDPA_ERR_UNSUPPORTED otherwise and the caller
    * merges with b200_sdpa_merge() instead.  Replaces the (out, lse) merge upstream's ring does
    * between per-block calls (torch_neuronx/distributed/tensor/cp_ring_handler.py:308-318).  */
   int32_t acc_mode;

@@ -355,8 +355,9 @@ def test_cpp_operator_layer_loads_and_registers():
 
 
 def test_accumulating_form_planning():
-    """The accumulating form (one ring step folded into a running fp32 result) is served by the persistent
-    tensor-core prefill kernel only; everything else is declined so that the caller merges separately."""
+    """The accumulating form (one ring step folded into a running fp32 result) is served by the tensor-core
+    prefill kernels at head dim 128 (the one with one item per CTA unless B200_SDPA_PREFILL says otherwise);
+    everything else is declined so that the caller merges separately."""
     acc = dict(acc_mode=2, acc=0x7F5000000000, acc_lse=0x7F5100000000)
 
     def plan_acc(**kw):
@@ -366,7 +367,11 @@ def test_accumulating_form_planning():
         return _plan(p)
 
     rc, plan = plan_acc()
-    assert rc == 0 and plan.path == _lib.PATH_PREFILL and plan.threads == 512      # persistent, whatever the size
+    assert rc == 0 and plan.path == _lib.PATH_PREFILL and plan.threads == 320      # a small problem: one item per CTA
+    rc, plan = plan_acc(B=4, Hq=32, Hkv=8, L=4096, S=4096)
+    assert rc == 0 and plan.threads == 320          # also where the plain call would take persistent CTAs: ring
+    rc, plan = plan_acc(Hq=64, Hkv=8, L=16384, S=16384)                            # steps run under the power cap,
+    assert rc == 0 and plan.threads == 320                                         # where one item per CTA is faster
     assert plan_acc(E=64, Dv=64)[0] == _lib.ERR_UNSUPPORTED
     assert plan_acc(dtype=_lib.F32)[0] == _lib.ERR_UNSUPPORTED
     assert plan_acc(L=1)[0] == 0                                                   # one row still goes to that kernel

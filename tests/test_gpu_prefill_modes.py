@@ -125,15 +125,27 @@ def test_accumulating_form_folds_key_blocks_into_a_running_result(causal):
     big = torch.full((B, Hq, L + 64, D), float("nan"), dtype=torch.float32, device=DEV)   # the accumulator is a view
     acc, acc_lse = big[:, :, 32:32 + L], torch.full((B, Hq, L), float("nan"), dtype=torch.float32, device=DEV)
     q_off = 300                                                     # global position of query row 0
-    T.reset_launch_counts()
-    for blk in range(3):
-        ok = T.sdpa_forward_accumulate(qd, kd[:, :, blk * 256:(blk + 1) * 256], vd[:, :, blk * 256:(blk + 1) * 256], acc,
-                                       acc_lse, first=blk == 0, is_causal=causal, scale=0.1, q_offset=q_off,
-                                       k_offset=blk * 256)
-        assert ok and T.ops.last_plan["threads"] == 512
-    torch.cuda.synchronize()
-    T.check_device_status()
-    assert T.launch_counts()["prefill"] == 3 and T.launch_counts()["merge"] == 0
+    results = {}
+    for form, threads in (("per_cta", 320), ("persistent", 512)):   # both prefill kernels have the form
+        os.environ["B200_SDPA_PREFILL"] = form
+        try:
+            big.fill_(float("nan"))
+            acc_lse.fill_(float("nan"))
+            T.reset_launch_counts()
+            for blk in range(3):
+                ok = T.sdpa_forward_accumulate(qd, kd[:, :, blk * 256:(blk + 1) * 256], vd[:, :, blk * 256:(blk + 1) * 256],
+                                               acc, acc_lse, first=blk == 0, is_causal=causal, scale=0.1, q_offset=q_off,
+                                               k_offset=blk * 256)
+                assert ok and T.ops.last_plan["threads"] == threads
+            torch.cuda.synchronize()
+            T.check_device_status()
+        finally:
+            os.environ.pop("B200_SDPA_PREFILL", None)
+        assert T.launch_counts()["prefill"] == 3 and T.launch_counts()["merge"] == 0
+        results[form] = (acc.clone(), acc_lse.clone())
+    # the same arithmetic in both kernels
+    assert torch.equal(results["per_cta"][0], results["persistent"][0])
+    assert torch.equal(results["per_cta"][1], results["persistent"][1])
     ref_o, ref_l = O.sdpa_forward(q, k, v, is_causal=causal, scale=0.1, q_offset=q_off, compute_dtype=torch.float32)
     assert torch.isnan(big[:, :, :32]).all() and torch.isnan(big[:, :, 32 + L:]).all()       # nothing outside the view
     err = (acc.cpu() - ref_o).abs()

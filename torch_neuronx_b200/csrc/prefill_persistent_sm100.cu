@@ -980,10 +980,13 @@ bool prefill_accumulate_eligible(const Problem& p) {
 
 bool prefill_persistent_wanted(const Problem& p) {
   if (p.E != 128 || p.Dv != 128) return false;
-  if (p.acc_mode != 0) return true;            // only this kernel has the accumulating form
   const char* e = getenv("B200_SDPA_PREFILL");
   if (e != nullptr && e[0] == 'p' && e[1] == 'e' && e[2] == 'r' && e[3] == 's') return true;    // "persistent"
   if (e != nullptr && e[0] == 'p' && e[1] == 'e' && e[2] == 'r' && e[3] == '_') return false;   // "per_cta"
+  // The accumulating form (ring steps) runs for seconds with the GPU at its power cap, where the kernel with
+  // one item per CTA was the faster one at every block size measured (eight ranks' blocks: 272.7 ms against
+  // 291.5 ms for this kernel).
+  if (p.acc_mode != 0) return false;
   return prefill_geometry(p).n_items >= 3LL * kAssumedSms && (p.S + kBlockN - 1) / kBlockN <= 64;
 }
 

@@ -107,7 +107,7 @@ __device__ __forceinline__ TileGeom tile_geometry(const Problem& p, int row0, in
   return g;
 }
 
-template <int D, bool BF16, bool BIAS>
+template <int D, bool BF16, bool BIAS, bool ACC>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o, const Problem p,
@@ -408,6 +408,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const float sl2 = BIAS ? kLog2e : sl2_in;
     float m_run = -CUDART_INF_F, l_run = 0.f;
     bool alive = true;
+    // accumulating form: the row's running lse is fetched now and used in the epilogue
+    float old_lse = -CUDART_INF_F;
+    if constexpr (ACC) {
+      if (row_g < p.L && p.acc_mode == 2)
+        old_lse = p.acc_lse[b * p.als[0] + head_of_tile[t] * p.als[1] + row_g * p.als[2]];
+    }
     // this row of the bias, 16-bit elements in the query's dtype, unit stride along the keys
     const uint4* bias_row = nullptr;
     if constexpr (BIAS) {
@@ -556,7 +562,55 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
         tc_fence_after_sync();
       }
-      if (alive) {
+      if constexpr (ACC) {
+        // Accumulating form (a ring step): fold this block's result into the row's running fp32 pair
+        // (acc, acc_lse) in place -- acc = acc * w_acc + O * w_o -- instead of writing out / lse.  Same
+        // arithmetic as the persistent kernel's accumulating epilogue.  A tile without a visible key
+        // leaves a started accumulator alone.
+        if (alive && !(tg.n_tiles == 0 && p.acc_mode == 2)) {
+          const bool row_ok = row_g < p.L &&
+                              dbg_bhrc(p.status, DBG_PREFILL * 100 + 8, b, p.B, head_of_tile[t], p.Hq, row_g, p.L, 0, D, p.Dv);
+          const float lse = l_run > 0.f ? fmaf(m_run, p.scale, lg2(l_run) * kLn2) : -CUDART_INF_F;
+          float w_acc = 0.f, w_o = l_run > 0.f ? 1.f / l_run : 0.f;
+          const float hi = fmaxf(old_lse, lse);
+          float merged = -CUDART_INF_F;
+          if (hi != -CUDART_INF_F) {
+            const float e_old = ex2((old_lse - hi) * kLog2e), e_new = ex2((lse - hi) * kLog2e);   // -inf -> 0
+            merged = hi + lg2(e_old + e_new) * kLn2;
+            w_acc = ex2((old_lse - merged) * kLog2e);
+            w_o *= ex2((lse - merged) * kLog2e);
+          } else {
+            w_o = 0.f;
+          }
+          float* arow = p.acc + b * p.as[0] + static_cast<long long>(head_of_tile[t]) * p.as[1] +
+                        static_cast<long long>(row_g) * p.as[2];
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t v[32];
+            if (tg.n_tiles > 0) {   // (uniform over the warp: tensor-memory loads stay outside per-lane conditions)
+              tmem_ld_32x32(o_addr + c * 32, v);
+              tmem_ld_wait();
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = 0u;
+            }
+            if (row_ok) {
+#pragma unroll
+              for (int u = 0; u < 8; ++u) {
+                float4* dst = reinterpret_cast<float4*>(arow + c * 32 + u * 4);
+                float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (p.acc_mode == 2) a = *dst;
+                a.x = fmaf(a.x, w_acc, __uint_as_float(v[4 * u]) * w_o);
+                a.y = fmaf(a.y, w_acc, __uint_as_float(v[4 * u + 1]) * w_o);
+                a.z = fmaf(a.z, w_acc, __uint_as_float(v[4 * u + 2]) * w_o);
+                a.w = fmaf(a.w, w_acc, __uint_as_float(v[4 * u + 3]) * w_o);
+                *dst = a;
+              }
+            }
+          }
+          if (row_ok) p.acc_lse[b * p.als[0] + head_of_tile[t] * p.als[1] + row_g * p.als[2]] = merged;
+        }
+      } else if (alive) {
         const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
         uint8_t* o_stage = smem_raw + (q_smem[t] - raw_addr);   // the Q tile is no longer needed
 #pragma unroll
@@ -633,14 +687,19 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 // mask is causal (that is where the row-block layout leaves one tile idle at the end).
 int pair_heads_mode(const Problem& p) { return (p.causal && p.group % 2 == 0) ? 1 : 0; }
 
-template <int D, bool BF16, bool BIAS>
+template <int D, bool BF16, bool BIAS, bool ACC = false>
 int launch_variant(const Problem& p, cudaStream_t stream) {
   using C = Cfg<D>;
   CUtensorMap tq, tk, tv, to;
   if (!make_map(&tq, p.q, BF16, D, p.L, p.Hq, p.B, p.qs) || !make_map(&tk, p.k, BF16, D, p.S, p.Hkv, p.B, p.ks) ||
-      !make_map(&tv, p.v, BF16, D, p.S, p.Hkv, p.B, p.vs) || !make_map(&to, p.out, BF16, D, p.L, p.Hq, p.B, p.os))
+      !make_map(&tv, p.v, BF16, D, p.S, p.Hkv, p.B, p.vs))
     return B200_SDPA_ERR_CUDA;
-  auto kern = prefill_kernel<D, BF16, BIAS>;
+  if (ACC) {
+    to = tq;   // the accumulating form stores through plain pointers; the map is never used
+  } else if (!make_map(&to, p.out, BF16, D, p.L, p.Hq, p.B, p.os)) {
+    return B200_SDPA_ERR_CUDA;
+  }
+  auto kern = prefill_kernel<D, BF16, BIAS, ACC>;
   // the opt-in to more than 48 KB of dynamic shared memory is a per-device attribute: set on every
   // launch (a cheap host-side call), so a process that drives several GPUs gets it on each of them
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess) {
@@ -708,6 +767,10 @@ int launch_prefill(const Problem& p, int dtype, void* workspace, uint64_t worksp
   if (!prefill_eligible(p, dtype, nullptr)) return B200_SDPA_ERR_UNSUPPORTED;
   if (prefill_persistent_wanted(p)) return launch_prefill_persistent(p, dtype, workspace, workspace_bytes, stream);
   const bool bf16 = dtype == B200_SDPA_BF16;
+  if (p.acc_mode != 0) {
+    if (!prefill_accumulate_eligible(p)) return B200_SDPA_ERR_UNSUPPORTED;
+    return bf16 ? launch_variant<128, true, false, true>(p, stream) : launch_variant<128, false, false, true>(p, stream);
+  }
   if (p.bias != nullptr) {
     if (p.E == 128) return bf16 ? launch_variant<128, true, true>(p, stream) : launch_variant<128, false, true>(p, stream);
     return bf16 ? launch_variant<64, true, true>(p, stream) : launch_variant<64, false, true>(p, stream);

@@ -135,11 +135,12 @@ def _default_merge(acc, acc_lse, part, part_lse, first):
 def _default_accumulate(q, k, v, acc, acc_lse, *, first, is_causal, scale, q_offset, k_offset):
     from . import ops
 
-    # Opt-in (B200_SDPA_RING_FUSED=1).  The fused step needs the persistent form of the prefill kernel, and
-    # for the long key blocks of a ring the per-CTA form plus a separate merge was the faster pair when
-    # measured (131072 tokens over two GPUs: 128.4 ms against 132.9 ms fused and 136.3 ms unfused persistent;
-    # with the block sizes of eight ranks, all ranks' work on one GPU: 281.6 ms against 288.3 ms fused).
-    if not q.is_cuda or os.environ.get("B200_SDPA_RING_FUSED") != "1":
+    # On by default (B200_SDPA_RING_FUSED=0 turns it off): the attention kernel folds the step into the running
+    # fp32 result in its epilogue, so no partial output, no partial lse and no merge launch exist.  Measured as
+    # all ranks' work of a 131072-token causal ring run back to back on one GPU: 8 ranks 284.7 -> 272.7 ms,
+    # 4 ranks 264.2 -> 261.8 ms, 2 ranks 257.4 -> 255.4 ms.  What the kernel declines (head dims other than
+    # 128, fp32 inputs, a bias) runs as attention + merge.
+    if not q.is_cuda or os.environ.get("B200_SDPA_RING_FUSED", "1") == "0":
         return False
     return ops.sdpa_forward_accumulate(q, k, v, acc, acc_lse, first=first, is_causal=is_causal, scale=scale,
                                        q_offset=q_offset, k_offset=k_offset)
