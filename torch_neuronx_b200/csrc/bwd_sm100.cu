@@ -507,6 +507,9 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       const int col0 = j * kT + half * 64;
       const bool need_mask = j * kT + kT > min_lim;
       uint32_t pk[32];
+      // two columns per instruction (packed fp32 pairs) wherever the arithmetic allows: the loop is bound by
+      // what the eight warps can issue beside their 64 exponentials each
+      const uint64_t sl2_2 = f2_pack(sl2, sl2), neg_dl2 = f2_pack(-dl, -dl);
 #pragma unroll
       for (int i = 0; i < 64; i += 2) {
         float off0 = neg_l2, off1 = neg_l2;
@@ -514,13 +517,17 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           off0 = fmaf(bias_to_f32<BF16>(bw[i >> 1] & 0xffffu), kLog2e, neg_l2);
           off1 = fmaf(bias_to_f32<BF16>(bw[i >> 1] >> 16), kLog2e, neg_l2);
         }
-        float p0 = ex2(fmaf(__uint_as_float(sv[i]), sl2, off0));
-        float p1 = ex2(fmaf(__uint_as_float(sv[i + 1]), sl2, off1));
+        float a0, a1;
+        f2_unpack(f2_fma(f2_pack(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])), sl2_2, f2_pack(off0, off1)), a0, a1);
+        float p0 = ex2(a0);
+        float p1 = ex2(a1);
         if (need_mask) {
           p0 = (col0 + i < lim) ? p0 : 0.f;
           p1 = (col0 + i + 1 < lim) ? p1 : 0.f;
         }
-        pk[i >> 1] = pack2<BF16>(p0 * (__uint_as_float(dv[i]) - dl), p1 * (__uint_as_float(dv[i + 1]) - dl));
+        float d0, d1;
+        f2_unpack(f2_mul(f2_pack(p0, p1), f2_add(f2_pack(__uint_as_float(dv[i]), __uint_as_float(dv[i + 1])), neg_dl2)), d0, d1);
+        pk[i >> 1] = pack2<BF16>(d0, d1);
       }
       if (j >= 2) {   // the product that read this operand buffer two tiles ago must have retired
         ok = wait_clocked(smem_u32(&sync->op_empty[buf]), ((j >> 1) - 1) & 1, abort_flag, wait_limit);
@@ -765,6 +772,7 @@ bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     if (key_g >= n_keys) i_min = 1 << 30;
     const bool tile_has_padding = j0 + kT > n_keys;
     const float sl2 = p.scale * kLog2e;
+    const uint64_t sl2_2 = f2_pack(sl2, sl2);
     bool alive = true;
     for (int u = 0; u < n_units; ++u) {
       const int it = u >> 1, hh = u & 1, buf = u & 1;
@@ -805,14 +813,25 @@ bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const float ds_[4] = {d4.x, d4.y, d4.z, d4.w};
         float pr[4], dsv[4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
+        for (int e = 0; e < 4; e += 2) {   // two query columns per instruction (packed fp32 pairs)
           const int i = q4 * 4 + e;
-          float off = -ls[e];
-          if constexpr (BIAS) off = fmaf(bias_to_f32<BF16>(bq[i]), kLog2e, off);
-          float pe = ex2(fmaf(__uint_as_float(sv[i]), sl2, off));
-          if (need_mask) pe = (qrow0 + i >= i_min) ? pe : 0.f;
-          pr[e] = pe;
-          dsv[e] = pe * (__uint_as_float(dv[i]) - ds_[e]);
+          float off0 = -ls[e], off1 = -ls[e + 1];
+          if constexpr (BIAS) {
+            off0 = fmaf(bias_to_f32<BF16>(bq[i]), kLog2e, off0);
+            off1 = fmaf(bias_to_f32<BF16>(bq[i + 1]), kLog2e, off1);
+          }
+          float a0, a1;
+          f2_unpack(f2_fma(f2_pack(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])), sl2_2, f2_pack(off0, off1)), a0, a1);
+          float p0 = ex2(a0), p1 = ex2(a1);
+          if (need_mask) {
+            p0 = (qrow0 + i >= i_min) ? p0 : 0.f;
+            p1 = (qrow0 + i + 1 >= i_min) ? p1 : 0.f;
+          }
+          pr[e] = p0;
+          pr[e + 1] = p1;
+          f2_unpack(f2_mul(f2_pack(p0, p1), f2_add(f2_pack(__uint_as_float(dv[i]), __uint_as_float(dv[i + 1])),
+                                                    f2_pack(-ds_[e], -ds_[e + 1]))),
+                    dsv[e], dsv[e + 1]);
         }
         pkp[q4 * 2] = pack2<BF16>(pr[0], pr[1]);
         pkp[q4 * 2 + 1] = pack2<BF16>(pr[2], pr[3]);

@@ -788,14 +788,17 @@ prefill_persistent_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
         // probabilities, row sum (two packed accumulators), P -> TMEM over the first 64
         // columns of S.  (Measured alternatives that lost: a polynomial exp2 on the FMA
         // pipe for part of the row, and ex2 on packed 16-bit pairs.)
+        const uint64_t sl2_2 = f2_pack(sl2, sl2), nms_2 = f2_pack(nms, nms);
         uint64_t sum2[2] = {0ull, 0ull};           // two packed accumulators = four chains
 #pragma unroll
         for (int c = 0; c < kBlockN / 32; ++c) {
           uint32_t pk[16];
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            const float p0 = ex2(fmaf(__uint_as_float(sv[c * 32 + i]), sl2, nms));
-            const float p1 = ex2(fmaf(__uint_as_float(sv[c * 32 + i + 1]), sl2, nms));
+            float a0, a1;   // both exponents with one packed fma
+            f2_unpack(f2_fma(f2_pack(__uint_as_float(sv[c * 32 + i]), __uint_as_float(sv[c * 32 + i + 1])), sl2_2, nms_2), a0, a1);
+            const float p0 = ex2(a0);
+            const float p1 = ex2(a1);
             sum2[(i >> 1) & 1] = f2_add(sum2[(i >> 1) & 1], f2_pack(p0, p1));
             pk[i >> 1] = pack2<BF16>(p0, p1);
           }
