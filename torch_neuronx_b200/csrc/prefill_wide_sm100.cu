@@ -374,14 +374,17 @@ prefill_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       }
       const float nms = (m_run == -CUDART_INF_F) ? 0.f : -m_run * sl2;
 
+      const uint64_t sl2_2 = f2_pack(sl2, sl2), nms_2 = f2_pack(nms, nms);
       uint64_t sum2[2] = {0ull, 0ull};
 #pragma unroll
       for (int c = 0; c < kN / 32; ++c) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const float p0 = ex2(fmaf(__uint_as_float(sv[c * 32 + i]), sl2, nms));
-          const float p1 = ex2(fmaf(__uint_as_float(sv[c * 32 + i + 1]), sl2, nms));
+          float a0, a1;   // both exponents with one packed fma
+          f2_unpack(f2_fma(f2_pack(__uint_as_float(sv[c * 32 + i]), __uint_as_float(sv[c * 32 + i + 1])), sl2_2, nms_2), a0, a1);
+          const float p0 = ex2(a0);
+          const float p1 = ex2(a1);
           sum2[(i >> 1) & 1] = f2_add(sum2[(i >> 1) & 1], f2_pack(p0, p1));
           pk[i >> 1] = pack2<BF16>(p0, p1);
         }
