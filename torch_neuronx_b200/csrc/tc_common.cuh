@@ -195,7 +195,8 @@ inline bool strides_ok(const void* base, const int64_t* s, int rows, int heads, 
 // One thread's 8 N bias elements (16-bit) of a key tile: N 16-byte pieces, fetched as N / 2
 // 32-byte loads when the row allows it (`wide`: the row start and the key offset on a 32-byte
 // boundary) -- every thread reads its own row, so the number of load instructions is what the
-// load/store unit feels.  Pieces at or beyond `n_cols` (a multiple of 8) read as zero.
+// load/store unit feels.  Pieces at or beyond `n_cols` (a multiple of 8) read as zero.  The loads bypass L1
+// (every byte is read once): the softmax loop's spilled registers live there and must not be evicted.
 template <int N>
 __device__ __forceinline__ void load_bias_row(uint4 (&bv)[N], const uint4* row, const int col0, const int n_cols,
                                               const bool wide) {
@@ -207,7 +208,7 @@ __device__ __forceinline__ void load_bias_row(uint4 (&bv)[N], const uint4* row, 
   if (wide && col0 + 8 * N <= n_cols) {
 #pragma unroll
     for (int i = 0; i < N / 2; ++i) {
-      asm volatile("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+      asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
                    : "=r"(bv[2 * i].x), "=r"(bv[2 * i].y), "=r"(bv[2 * i].z), "=r"(bv[2 * i].w), "=r"(bv[2 * i + 1].x),
                      "=r"(bv[2 * i + 1].y), "=r"(bv[2 * i + 1].z), "=r"(bv[2 * i + 1].w)
                    : "l"(row + (col0 >> 3) + 2 * i));
@@ -217,7 +218,11 @@ __device__ __forceinline__ void load_bias_row(uint4 (&bv)[N], const uint4* row, 
 #pragma unroll
   for (int i = 0; i < N; ++i) {
     const int c = col0 + 8 * i;
-    bv[i] = c < n_cols ? __ldg(row + (c >> 3)) : make_uint4(0u, 0u, 0u, 0u);
+    bv[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (c < n_cols)
+      asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(bv[i].x), "=r"(bv[i].y), "=r"(bv[i].z), "=r"(bv[i].w)
+                   : "l"(row + (c >> 3)));
   }
 }
 
