@@ -70,7 +70,8 @@ def test_tensor_core_kernels_under_background_traffic(seed):
         live = torch.isfinite(ref_l)
         for o, l in outs:
             assert torch.equal(torch.isfinite(l), live), tag
-            assert (o.float() - ref_o.float()).abs().max().item() <= 3e-2, tag
+            # (two 16-bit results may differ by a unit in the last place, which grows with the magnitude)
+            assert (o.float() - ref_o.float()).abs().max().item() <= 3e-2 * max(1.0, ref_o.float().abs().max().item() / 2), tag
             if live.any():
                 assert (l[live] - ref_l[live]).abs().max().item() <= 2e-3, tag
             assert torch.equal(o, outs[0][0]) and torch.equal(l, outs[0][1]), tag + " (forward not reproducible)"
