@@ -159,7 +159,7 @@ def test_accumulating_form_folds_key_blocks_into_a_running_result(causal):
 
 @pytest.mark.parametrize("layout", ["zigzag", "contiguous"])
 def test_ring_with_the_merge_fused_into_the_attention_kernel(layout):
-    """The ring driver with every step folded into the accumulator by the attention kernel itself (opt-in):
+    """The ring driver with every step folded into the accumulator by the attention kernel itself (the default):
     four virtual ranks on one GPU against full attention, no merge kernel launched."""
     import torch_neuronx_b200 as T
     from oracle import sdpa_oracle as O

@@ -310,8 +310,8 @@ def sdpa_forward_accumulate(
     ``(B, Hq, L, Dv)`` / ``acc_lse`` ``(B, Hq, L)`` (overwritten when ``first``) -- no partial in the
     storage dtype, no separate merge launch (upstream merges in Python between per-block calls,
     ``cp_ring_handler.py:308-318``).  Returns False, having done nothing, when the request is not one
-    the accumulating kernel serves (it is the persistent tensor-core prefill kernel: f16/bf16, head
-    dim 128, TMA-legal strides); the caller then runs the plain forward and :func:`merge_partials`."""
+    the accumulating kernels serve (the tensor-core prefill kernels: f16/bf16, head dim 128, no bias,
+    TMA-legal strides); the caller then runs the plain forward and :func:`merge_partials`."""
     if query.dtype not in (torch.float16, torch.bfloat16) or not query.is_cuda:
         return False
     lib = _lib.load()
