@@ -393,6 +393,9 @@ __global__ void __launch_bounds__(kThreads, 3) decode_mma_kernel(const Problem p
     __syncthreads();   // the stage may be refilled from here on
   }
   cp_async_wait<0>();
+  // the cache has been streamed: the combine kernel (a programmatic dependent launch) may be placed now;
+  // it still waits for this grid to complete before it reads a partial
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   // ---- quad-reduce the row sums, then merge the four warps through shared memory
   l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);

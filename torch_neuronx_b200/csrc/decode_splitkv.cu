@@ -229,6 +229,9 @@ __global__ void __launch_bounds__(D) decode_combine_kernel(const Problem p, cons
   const int b = blockIdx.x / p.Hq;
   const int d = threadIdx.x;
   const int n_keys = valid_keys(p, b);
+  // launched as a programmatic dependent of the partial kernel: nothing that kernel wrote may be read
+  // before it has completed
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   if (p.lens_out != nullptr && h == 0 && d == 0) p.lens_out[b] = n_keys;   // lengths after the append
   int used = (n_keys + chunk - 1) / chunk;
   used = used < 1 ? 1 : (used > nsplit ? nsplit : used);
@@ -285,8 +288,25 @@ DecodeGeom geometry(const Problem& p, int kv_chunk) {
 
 template <typename T, int D>
 int launch_combine(const Problem& p, const DecodeGeom& gm, float* po, float* pml, cudaStream_t stream) {
-  decode_combine_kernel<T, D><<<p.B * p.Hq, D, 0, stream>>>(p, gm.chunk, gm.nsplit, po, pml);
-  if (cudaGetLastError() != cudaSuccess) return B200_SDPA_ERR_CUDA;
+  // Programmatic dependent launch: the combine grid may be placed while the partial kernel's last CTAs
+  // are finishing; its threads wait (griddepcontrol.wait) until that grid has completed and its stores
+  // are visible before they read a partial.
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(p.B * p.Hq);
+  cfg.blockDim = dim3(D);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const float* cpo = po;
+  const float* cpml = pml;
+  if (cudaLaunchKernelEx(&cfg, decode_combine_kernel<T, D>, p, gm.chunk, gm.nsplit, cpo, cpml) != cudaSuccess) {
+    cudaGetLastError();
+    return B200_SDPA_ERR_CUDA;
+  }
   count_launch(KID_COMBINE);
   return B200_SDPA_OK;
 }
