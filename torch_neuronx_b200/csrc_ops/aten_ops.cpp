@@ -15,10 +15,13 @@
 #include <c10/cuda/CUDAStream.h>
 #include <torch/library.h>
 
+#include <algorithm>
 #include <array>
 #include <cmath>
 #include <limits>
 #include <mutex>
+#include <string>
+#include <tuple>
 #include <vector>
 
 #include "../../include/b200_sdpa.h"
@@ -33,21 +36,20 @@ struct PerDevice {
   at::Tensor philox_offset;
 };
 
-std::mutex g_mutex;
+std::once_flag g_once[kMaxDevices];
 PerDevice g_dev[kMaxDevices];
 
+// Created once per device, by whichever thread gets there first (calls arrive without the interpreter
+// lock, so several threads may race here).
 PerDevice& device_state(int dev) {
   TORCH_CHECK(dev >= 0 && dev < kMaxDevices, "b200_sdpa: device index out of range");
   PerDevice& d = g_dev[dev];
-  if (!d.status.defined()) {
-    std::lock_guard<std::mutex> lock(g_mutex);
-    if (!d.status.defined()) {
-      const auto opts = at::TensorOptions().device(at::kCUDA, dev).dtype(at::kInt);
-      d.philox_seed = at::zeros({}, opts);
-      d.philox_offset = at::zeros({}, opts);
-      d.status = at::zeros({4}, opts);
-    }
-  }
+  std::call_once(g_once[dev], [&] {
+    const auto opts = at::TensorOptions().device(at::kCUDA, dev).dtype(at::kInt);
+    d.philox_seed = at::zeros({}, opts);
+    d.philox_offset = at::zeros({}, opts);
+    d.status = at::zeros({4}, opts);
+  });
   return d;
 }
 
