@@ -567,6 +567,11 @@ bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     }
   }
 
+  // Launched as a programmatic dependent of the dK/dV kernel, of which it reads nothing.  One CTA -- the last
+  // of the grid, which is also the last to be placed -- waits for that grid before it exits, so that this grid
+  // cannot complete before it and work queued behind finds both done; the others must not wait (a finished CTA
+  // parked on its SM would keep the next one from starting).
+  if (blockIdx.x == gridDim.x - 1) asm volatile("griddepcontrol.wait;" ::: "memory");
   tc_fence_before_sync();
   __syncthreads();
   if (warp == kMmaWarp) {
@@ -594,6 +599,10 @@ bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
+
+  // the dQ kernel (a programmatic dependent launch that does not read anything this kernel writes) may be
+  // placed on SMs as soon as every CTA of this grid is resident
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   // Earliest key blocks (seen by the most query tiles under a causal mask) first, within waves of
   // `streams_per_wave` (batch, kv head) groups whose query-side operands fit in L2 together.
@@ -932,14 +941,32 @@ int launch_tc(const BwdProblem& bp, float* lse2, float* delta, cudaStream_t stre
   // the dQ kernel streams keys and values; the dK/dV kernel the queries, dO and row statistics of a group
   const int wave_q = kv_streams_per_wave(static_cast<long long>(p.S) * 2 * D * 2, n_streams);
   const int wave_kv = kv_streams_per_wave(static_cast<long long>(p.L) * p.group * (2 * D * 2 + 8), n_streams);
-  kq<<<static_cast<unsigned>(grid_q), kThreads, ACfg<D>::kSmemBytes, stream>>>(tq, tk, tv, tdo, tdq, p, lse2, delta, l_pad,
-                                                                        n_qblk, wave_q, limit);
-  if (cudaGetLastError() != cudaSuccess) return B200_SDPA_ERR_CUDA;
-  count_launch(KID_BWD_DQ);
+  // The two kernels are independent of each other (both read the row statistics of the kernel before them).
+  // The dK/dV kernel, whose CTAs are long, goes first and releases its dependents as soon as its last CTA is
+  // resident; the dQ kernel is a programmatic dependent launch, so its CTAs take the SMs the first kernel's
+  // tail leaves idle.  It waits for the first kernel's completion only before it exits (stream order for
+  // whatever follows).
   kkv<<<static_cast<unsigned>(grid_kv), kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, tdk, tdv, p, lse2, delta,
                                                                           l_pad, n_kblk, wave_kv, limit);
   if (cudaGetLastError() != cudaSuccess) return B200_SDPA_ERR_CUDA;
   count_launch(KID_BWD_DKV);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid_q));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = ACfg<D>::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const float* c_lse2 = lse2;
+  const float* c_delta = delta;
+  if (cudaLaunchKernelEx(&cfg, kq, tq, tk, tv, tdo, tdq, p, c_lse2, c_delta, l_pad, n_qblk, wave_q, limit) != cudaSuccess) {
+    cudaGetLastError();
+    return B200_SDPA_ERR_CUDA;
+  }
+  count_launch(KID_BWD_DQ);
   return B200_SDPA_OK;
 }
 
